@@ -1,0 +1,14 @@
+"""gpurs_b200: the dense matrix-multiply path of gpurs, rebuilt for NVIDIA B200 (sm_100a).
+
+The product is the C-ABI library `libgpurs_b200.so` (declared in include/gpurs_b200.h) and the CUDA
+kernels embedded in it; this package is the Python mirror of the reference's host surface over that
+ABI, used by the tests and the benchmark.
+"""
+from ._ffi import ALGO_AUTO, ALGO_CTA_PAIR, ALGO_SINGLE_CTA
+from .host import (BF16, E4M3, F16, F32, I8, I32, DeviceBuffer, Event, Gpu, GpursError, Kernel, LaunchConfig,
+                   MatmulOptions, Module, Stream, matmul)
+
+__all__ = [
+    "ALGO_AUTO", "ALGO_CTA_PAIR", "ALGO_SINGLE_CTA", "BF16", "E4M3", "F16", "F32", "I8", "I32", "DeviceBuffer", "Event",
+    "Gpu", "GpursError", "Kernel", "LaunchConfig", "MatmulOptions", "Module", "Stream", "matmul",
+]

@@ -1,0 +1,79 @@
+// Internal definitions of the opaque handles behind include/gpurs_b200.h.
+#pragma once
+#include "../../../include/gpurs_b200.h"
+#include "driver_api.hpp"
+
+#include <map>
+#include <string>
+
+struct gpurs_module {
+    gpurs_gpu *gpu;
+    CUmodule handle;
+};
+
+struct gpurs_kernel {
+    gpurs_module *module;
+    CUfunction function;
+    std::string name;
+    uint32_t reserved_shared = 0;
+};
+
+struct gpurs_gpu {
+    const driver::Api *api;
+    CUdevice device;
+    CUcontext context;
+    int major, minor, multiprocessors;
+    size_t total_bytes;
+    CUstream transfer;                 // internal stream for upload / zeros / download
+    CUdeviceptr status;                // 4 x u32 written by bounded device waits that give up
+    gpurs_module *builtin = nullptr;   // the embedded sm_100a image, loaded on first use
+    std::map<std::string, gpurs_kernel *> kernels;
+    uint64_t launches = 0;
+};
+
+struct gpurs_stream {
+    gpurs_gpu *gpu;
+    CUstream handle;
+    bool owned;
+};
+
+struct gpurs_event {
+    gpurs_gpu *gpu;
+    CUevent handle;
+};
+
+namespace runtime {
+
+// Makes a gpu's context current for the lifetime of the guard and restores the previous one after,
+// like `Context::enter` in the reference (crates/driver/src/context.rs:117-129).
+class Enter {
+  public:
+    explicit Enter(gpurs_gpu *gpu) : gpu_(gpu) { pushed_ = gpu_->api->cuCtxPushCurrent(gpu_->context) == CUDA_SUCCESS; }
+    ~Enter() {
+        CUcontext previous;
+        if (pushed_) gpu_->api->cuCtxPopCurrent(&previous);
+    }
+    Enter(const Enter &) = delete;
+    Enter &operator=(const Enter &) = delete;
+
+  private:
+    gpurs_gpu *gpu_;
+    bool pushed_;
+};
+
+// Records the failure detail for gpurs_last_error and returns `code` unchanged.
+int fail_driver(const driver::Api *api, const char *operation, CUresult code);
+int fail(const char *operation, int code, const char *description);
+
+// The built-in kernel with the given entry name, with `shared_bytes` of dynamic shared memory reserved.
+int builtin_kernel(gpurs_gpu *gpu, const char *name, uint32_t shared_bytes, gpurs_kernel **out);
+
+int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params);
+
+}  // namespace runtime
+
+#define GPURS_TRY(api, call)                                                     \
+    do {                                                                         \
+        CUresult gpurs_result_ = (api)->call;                                    \
+        if (gpurs_result_ != CUDA_SUCCESS) return runtime::fail_driver((api), #call, gpurs_result_); \
+    } while (0)

@@ -1,0 +1,55 @@
+// Types shared by the GEMM kernels and the host code that launches them: the kernel parameter block,
+// the shared-memory layout of a pipeline, and the status codes of the bounded device waits.
+#pragma once
+#include <cstdint>
+
+namespace gemm {
+
+// Output element types.
+enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2, OUT_I32 = 3 };
+
+// Device status codes written to the status word when a bounded wait gives up.
+enum : uint32_t {
+    STATUS_OK = 0,
+    STATUS_PRODUCER_TIMEOUT = 1,
+    STATUS_MMA_TIMEOUT = 2,
+    STATUS_EPILOGUE_TIMEOUT = 3,
+};
+
+struct Params {
+    void *c;                 // output, row-major M x N with row pitch ldc (elements)
+    long long ldc;
+    int m, n, k;
+    int tiles_m, tiles_n;    // in units of (128 * CTA_GROUP) x BLOCK_N tiles
+    int raster_rows;         // tile rows walked together so concurrent tiles share operands in L2
+    int vector_stores;       // 1 when every output row start is 16-byte aligned
+    unsigned int *status;    // [0] first failure code, [1] block, [2] tile, [3] K-block
+    const float *scale_a;    // block-scaled FP8 only: [M][ceil(K/128)]
+    const float *scale_b;    // block-scaled FP8 only: [ceil(N/128)][ceil(K/128)]
+};
+
+constexpr int BLOCK_M = 128;       // rows per CTA (= TMEM lanes)
+constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swizzle span
+constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
+constexpr int NUM_THREADS = 192;
+constexpr int EPILOGUE_WARPS = 4;
+constexpr int BLOCK_N = 256;       // columns per tile
+constexpr int STAGES_SINGLE = 4;   // pipeline depth of the one-CTA kernels (48 KiB per stage)
+constexpr int STAGES_PAIR = 6;     // pipeline depth of the CTA-pair kernels (32 KiB per stage and CTA)
+
+template <int BLOCK_N, int CTA_GROUP, int STAGES>
+struct SharedLayout {
+    static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
+    static constexpr int B_ROWS = BLOCK_N / CTA_GROUP;   // rows of the B tile this CTA loads
+    static constexpr int B_BYTES = B_ROWS * ROW_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
+    // full[STAGES], empty[STAGES], accumulator_full[2], accumulator_empty[2], then the TMEM base word
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+    static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
+    static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
+    static constexpr int TOTAL = ABORT_OFFSET + 4;
+    static constexpr int DYNAMIC_BYTES = TOTAL + 1024;   // slack to align the stages to 1024 bytes
+};
+
+}  // namespace gemm

@@ -1,0 +1,26 @@
+// Entry points of the tcgen05 GEMM family.  Each is an `extern "C"` kernel so that the host side can
+// find it by name in the module it loads with cuModuleLoadData, which is also how the reference's
+// interop layer would load it (crates/gpurs/src/raw/module.rs:64-92).
+#include "gemm_tcgen05.cuh"
+
+#define GPURS_GEMM_KERNEL(NAME, KIND, FORMAT, ACC, OUT, BLOCK_N, GROUP, STAGES)                                   \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                           \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                   \
+         const __grid_constant__ gemm::Params params) {                                                          \
+        gemm::gemm_body<KIND, FORMAT, ACC, OUT, BLOCK_N, GROUP, STAGES>(&map_a, &map_b, params);                 \
+    }
+
+// Operand format codes inside each kind: f16 = 0, bf16 = 1, tf32 = 2 (kind f16 / tf32); signed int8 = 1
+// (kind i8); e4m3 = 0 (kind f8f6f4).  Accumulator: 1 = f32, 2 = s32.
+#define GPURS_GEMM_PAIR(STEM, KIND, FORMAT, ACC, OUT)                                  \
+    GPURS_GEMM_KERNEL(STEM##_cg1, KIND, FORMAT, ACC, OUT, gemm::BLOCK_N, 1, gemm::STAGES_SINGLE)                   \
+    GPURS_GEMM_KERNEL(STEM##_cg2, KIND, FORMAT, ACC, OUT, gemm::BLOCK_N, 2, gemm::STAGES_PAIR)
+
+GPURS_GEMM_PAIR(gpurs_gemm_f16_f32, ptx::KIND_F16, 0, 1, gemm::OUT_F32)
+GPURS_GEMM_PAIR(gpurs_gemm_f16_f16, ptx::KIND_F16, 0, 1, gemm::OUT_F16)
+GPURS_GEMM_PAIR(gpurs_gemm_bf16_f32, ptx::KIND_F16, 1, 1, gemm::OUT_F32)
+GPURS_GEMM_PAIR(gpurs_gemm_bf16_bf16, ptx::KIND_F16, 1, 1, gemm::OUT_BF16)
+GPURS_GEMM_PAIR(gpurs_gemm_tf32_f32, ptx::KIND_TF32, 2, 1, gemm::OUT_F32)
+GPURS_GEMM_PAIR(gpurs_gemm_i8_i32, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
+GPURS_GEMM_PAIR(gpurs_gemm_e4m3_f32, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_F32)
+GPURS_GEMM_PAIR(gpurs_gemm_e4m3_bf16, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)

@@ -1,0 +1,298 @@
+// The dense GEMM of the gpurs matrix-multiply path, rebuilt for sm_100a:
+//
+//     C[m, n] = sum_k A[m, k] * B[n, k]          A is M x K, B is N x K, both K-major,
+//
+// the operand convention of the reference's tensor-core examples
+// (examples/blackwell/examples/blackwell_matrix.rs:32-56, crates/gpurs/src/gpu/tensor/layout.rs:1-2).
+//
+// Structure (one persistent CTA, or CTA pair, per SM):
+//   warp 0      producer: waits for a free stage, arms its barrier and issues the two TMA tile loads
+//   warp 1      MMA issuer: waits for a full stage, issues 4 tcgen05.mma (32 bytes of K each) into one
+//               of two TMEM accumulators, commits the stage back to the producer, and after the last
+//               K-block commits the accumulator to the epilogue
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (warp w owns TMEM lanes 32*(w%4)..+31),
+//               round to the output type, store 16 bytes per instruction; then hand the accumulator back
+// so the tensor pipe never waits for a TMA round trip or for the epilogue of the previous tile.  The
+// reference's kernel does all three jobs with one thread and one accumulator
+// (crates/gpurs/src/gpu/tensor/hopper/ring.rs:144-209, blackwell/tensor_memory.rs:91-121,232-278).
+//
+// With CTA_GROUP == 2 two CTAs of a cluster share one 256 x BLOCK_N tile: each loads its own 128 rows
+// of A and its own half of the B tile, and the leader (cluster rank 0) issues tcgen05.mma.cta_group::2,
+// which reads B from both CTAs' shared memory and writes each CTA's 128 accumulator rows into that
+// CTA's own tensor memory.  No TMA load is multicast; every CTA fetches its own operands.
+#pragma once
+#include "gemm_params.hpp"
+#include "sm100_ptx.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace gemm {
+
+// Instruction descriptor: accumulator format (1 = f32, 2 = s32) at bit 4, A and B element formats at
+// bits 7 and 10, both operands K-major, N/8 at bit 17, M/16 at bit 24 (M counts both CTAs of a pair).
+__host__ __device__ constexpr uint32_t instruction_descriptor(int accumulator_format, int element_format, int mma_m, int mma_n) {
+    return (uint32_t(accumulator_format) << 4) | (uint32_t(element_format) << 7) | (uint32_t(element_format) << 10) |
+           (uint32_t(mma_n >> 3) << 17) | (uint32_t(mma_m >> 4) << 24);
+}
+
+// Tile index -> (tile row, tile column): bands of `raster_rows` tile rows are walked column by column,
+// the same idea as the reference's Swizzle<8> raster (crates/gpurs/src/gpu/tensor/schedule/grid.rs:55-82).
+__device__ __forceinline__ void tile_position(int tile, const Params &p, int &tile_m, int &tile_n) {
+    int band_tiles = p.raster_rows * p.tiles_n;
+    int band = tile / band_tiles;
+    int first_row = band * p.raster_rows;
+    int rows = min(p.raster_rows, p.tiles_m - first_row);
+    int local = tile - band * band_tiles;
+    tile_m = first_row + local % rows;
+    tile_n = local / rows;
+}
+
+__device__ __forceinline__ void report(const Params &p, volatile uint32_t *abort_flag, uint32_t code, int tile, int k_block) {
+    *abort_flag = code;
+    if (atomicCAS(p.status, 0u, code) == 0u) {
+        p.status[1] = blockIdx.x;
+        p.status[2] = uint32_t(tile);
+        p.status[3] = uint32_t(k_block);
+    }
+}
+
+template <int OUT>
+__device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&acc)[32], int row, int column) {
+    if (row >= p.m || column >= p.n) return;
+    const bool whole = column + 32 <= p.n && p.vector_stores;
+    if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
+        uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + size_t(row) * p.ldc + column;
+        if (whole) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                reinterpret_cast<uint4 *>(out)[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n) out[i] = acc[i];
+        }
+    } else {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            float lo = __uint_as_float(acc[2 * i]), hi = __uint_as_float(acc[2 * i + 1]);
+            if constexpr (OUT == OUT_BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                packed[i] = *reinterpret_cast<uint32_t *>(&v);
+            } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                packed[i] = *reinterpret_cast<uint32_t *>(&v);
+            }
+        }
+        uint16_t *out = reinterpret_cast<uint16_t *>(p.c) + size_t(row) * p.ldc + column;
+        if (whole) {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                reinterpret_cast<uint4 *>(out)[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n) out[i] = uint16_t(packed[i / 2] >> (16 * (i & 1)));
+        }
+    }
+}
+
+// KIND: ptx::KIND_*; ELEMENT_FORMAT: the 3-bit format code of the operands for that kind;
+// ACC_FORMAT: 1 = f32, 2 = s32; OUT: OUT_*.
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES>
+__device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const Params &p) {
+    using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
+    static_assert(BLOCK_N == 128 || BLOCK_N == 256, "two accumulators of BLOCK_N columns must fit 512 TMEM columns");
+    constexpr uint32_t TMEM_COLUMNS = 2 * BLOCK_N;
+    constexpr uint32_t IDESC = instruction_descriptor(ACC_FORMAT, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, BLOCK_N);
+
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (ptx::smem_u32(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - ptx::smem_u32(raw_shared));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(aligned + L::TMEM_SLOT_OFFSET);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(aligned + L::ABORT_OFFSET);
+
+    auto stage_a = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES; };
+    auto stage_b = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES; };
+    auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
+    auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
+    auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 2 + a) * 8; };
+
+    const int warp = threadIdx.x / 32;
+    const uint32_t lane = ptx::lane_id();
+    const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int cluster_count = gridDim.x / CTA_GROUP;
+    const int tile_count = p.tiles_m * p.tiles_n;
+    const int element_bytes = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
+    const int block_k = ROW_BYTES / element_bytes;
+    const int k_blocks = (p.k + block_k - 1) / block_k;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            ptx::mbarrier_init(full_bar(s), 1);
+            ptx::mbarrier_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            ptx::mbarrier_init(acc_full_bar(a), 1);
+            ptx::mbarrier_init(acc_empty_bar(a), EPILOGUE_WARPS * CTA_GROUP);
+        }
+        ptx::fence_mbarrier_init();
+        ptx::prefetch_tensor_map(map_a);
+        ptx::prefetch_tensor_map(map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+        ptx::tmem_relinquish<CTA_GROUP>();
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        // The peer's TMA loads and the leader's commits signal barriers of this CTA: both CTAs must
+        // have initialised theirs before either starts.
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                int tile_m, tile_n;
+                tile_position(tile, p, tile_m, tile_n);
+                const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
+                const int row_b = tile_n * BLOCK_N + int(cta_rank) * L::B_ROWS;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+                        ptx::tma_load_2d(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage));
+                        ptx::tma_load_2d(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage));
+                    } else {
+                        // Both CTAs' loads are counted on the leader's barrier, which the leader arms
+                        // for the bytes of the pair.
+                        if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+                        const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
+                        ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
+                        ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * block_k, row_b, leader_bar);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            // Before leaving, see every stage released once more, so that no commit can arrive on a
+            // barrier of a CTA that has already exited.
+            for (int s = 0; s < STAGES && ok; s++) {
+                ok = ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && leader) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
+                    report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
+                    break;
+                }
+                ptx::tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(acc) * BLOCK_N;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
+                        report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after();
+                    const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
+                    const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
+#pragma unroll
+                    for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++) {
+                        // advancing the start address by 32 bytes steps through K inside the swizzle span
+                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
+                                                          b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC,
+                                                          uint32_t((kb | j) != 0));
+                    }
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(acc));
+                else ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quadrant = warp % 4;   // the TMEM lanes this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
+            int tile_m, tile_n;
+            tile_position(tile, p, tile_m, tile_n);
+            // Every lane waits (each needs the barrier's acquire); the vote keeps the warp together
+            // for the warp-wide tcgen05.ld that follows.
+            const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, -1);
+                break;
+            }
+            ptx::tcgen05_fence_after();
+            const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
+            const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BLOCK_N;
+#pragma unroll 1
+            for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+                uint32_t values[32];
+                ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
+                ptx::tmem_load_wait();
+                store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+            }
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            }
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0 && threadIdx.x == 0) {
+        // A wait gave up: give copies that may still be in flight a bounded time to land before the
+        // shared memory they target is released.
+        const unsigned long long start = ptx::global_timer();
+        while (ptx::global_timer() - start < 2000000ull) __nanosleep(1000);
+    }
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc<CTA_GROUP>(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+}  // namespace gemm

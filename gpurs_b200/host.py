@@ -1,0 +1,314 @@
+"""The host surface of the matrix-multiply path, named after the reference's:
+
+    gpu = Gpu(0)                       Gpu::new(0)              crates/gpurs/src/host/context.rs:69
+    stream = gpu.stream()              gpu.stream()             context.rs:125
+    a = gpu.upload(host_array)         gpu.upload(&host)        context.rs:132
+    c = gpu.zeros(np.float32, n)       gpu.zeros::<f32>(n)      context.rs:151
+    matmul(stream, a, b, c, [m, n, k]) the launcher             crates/macros/src/launcher.rs:110-223
+    c.download()                       output.download()        crates/gpurs/src/host/memory/buffer.rs:251-271
+
+Everything here is a thin object layer over the C ABI (include/gpurs_b200.h) through ctypes: no
+computation happens in Python and there is no fallback when the native library is absent.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import _ffi
+
+# Element types of the operands.  16-bit and 8-bit float formats have no numpy dtype: buffers of those
+# carry their bit patterns in uint16 / uint8 arrays and name the format explicitly.
+F16, F32, BF16, I8, I32, E4M3 = _ffi.F16, _ffi.F32, _ffi.BF16, _ffi.I8, _ffi.I32, _ffi.E4M3
+ELEMENT_BYTES = {F16: 2, F32: 4, BF16: 2, I8: 1, I32: 4, E4M3: 1}
+_STORAGE = {F16: np.uint16, BF16: np.uint16, F32: np.float32, I8: np.int8, I32: np.int32, E4M3: np.uint8}
+_FROM_NUMPY = {np.dtype(np.float32): F32, np.dtype(np.float16): F16, np.dtype(np.int8): I8, np.dtype(np.int32): I32}
+
+
+class GpursError(RuntimeError):
+    """A failed call: `code` is the CUresult or the GPURS_E_* value (the reference's `gpurs::Error`,
+    crates/gpurs/src/error.rs:13-71, and `driver::Error`, crates/driver/src/error.rs:8-16)."""
+
+    def __init__(self, code: int):
+        operation, name, description = C.c_char_p(), C.c_char_p(), C.c_char_p()
+        _ffi.load().gpurs_last_error(C.byref(operation), C.byref(name), C.byref(description))
+        self.code = code
+        self.operation = (operation.value or b"").decode()
+        self.name = (name.value or b"").decode()
+        self.description = (description.value or b"").decode()
+        super().__init__(f"`{self.operation}` failed: {self.name} ({self.description}, code {code})")
+
+
+def _check(code: int) -> None:
+    if code != _ffi.OK:
+        raise GpursError(code)
+
+
+@dataclass
+class LaunchConfig:
+    """`LaunchConfig` (crates/gpurs/src/host/stream.rs:28-52) with the cluster dimension added."""
+
+    grid: tuple = (1, 1, 1)
+    block: tuple = (1, 1, 1)
+    shared_bytes: int = 0
+    cluster: tuple = (1, 1, 1)
+
+    def _struct(self) -> _ffi.LaunchConfigStruct:
+        s = _ffi.LaunchConfigStruct()
+        for i in range(3):
+            s.grid[i] = self.grid[i] if i < len(self.grid) else 1
+            s.block[i] = self.block[i] if i < len(self.block) else 1
+            s.cluster[i] = self.cluster[i] if i < len(self.cluster) else 1
+        s.shared_bytes = self.shared_bytes
+        return s
+
+
+class Event:
+    def __init__(self, gpu: "Gpu", handle):
+        self._gpu, self._handle = gpu, handle
+
+    def synchronize(self) -> None:
+        _check(self._gpu._lib.gpurs_event_synchronize(self._handle))
+
+    def elapsed_ms(self, later: "Event") -> float:
+        """Milliseconds from this event to `later` (`Event::elapsed`)."""
+        ms = C.c_float()
+        _check(self._gpu._lib.gpurs_event_elapsed_ms(self._handle, later._handle, C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and self._gpu._handle:
+            self._gpu._lib.gpurs_event_free(self._handle)
+            self._handle = None
+
+
+class Stream:
+    """`Stream` (crates/gpurs/src/host/stream.rs): launches are asynchronous, `synchronize` waits."""
+
+    def __init__(self, gpu: "Gpu", handle):
+        self.gpu, self._handle = gpu, handle
+
+    def synchronize(self) -> None:
+        _check(self.gpu._lib.gpurs_stream_synchronize(self._handle))
+
+    def record_timed(self) -> Event:
+        handle = C.c_void_p()
+        _check(self.gpu._lib.gpurs_event_record_timed(self._handle, C.byref(handle)))
+        return Event(self.gpu, handle)
+
+    @property
+    def raw(self) -> int:
+        return self.gpu._lib.gpurs_stream_raw(self._handle) or 0
+
+    def copy_to_device(self, destination: "DeviceBuffer", host_pointer: int, nbytes: int) -> None:
+        _check(self.gpu._lib.gpurs_copy_to_device(self._handle, destination.pointer, host_pointer, nbytes))
+
+    def copy_to_host(self, host_pointer: int, source: "DeviceBuffer", nbytes: int) -> None:
+        _check(self.gpu._lib.gpurs_copy_to_host(self._handle, host_pointer, source.pointer, nbytes))
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and self.gpu._handle:
+            self.gpu._lib.gpurs_stream_free(self._handle)
+            self._handle = None
+
+
+class DeviceBuffer:
+    """A typed device allocation or a view of one: the `DeviceSlice` / `DeviceSliceMut` of the
+    reference (crates/gpurs/src/host/memory/buffer.rs:23-83).  `len` counts elements."""
+
+    def __init__(self, gpu: "Gpu", pointer: int, length: int, element: int, owner: "DeviceBuffer | None" = None, owned: bool = True):
+        self.gpu, self.pointer, self.len, self.element = gpu, pointer, length, element
+        self._owner, self._owned = owner, owned and owner is None
+
+    @property
+    def nbytes(self) -> int:
+        return self.len * ELEMENT_BYTES[self.element]
+
+    def slice(self, start: int, stop: int) -> "DeviceBuffer":
+        """Elements [start, stop) of this buffer, sharing its storage."""
+        if not (0 <= start <= stop <= self.len):
+            raise ValueError("slice out of range")
+        return DeviceBuffer(self.gpu, self.pointer + start * ELEMENT_BYTES[self.element], stop - start, self.element, owner=self._owner or self)
+
+    def download(self) -> np.ndarray:
+        """Copy back to the host and wait (`DeviceSlice::download`).  16-bit and 8-bit float formats come
+        back as their bit patterns."""
+        out = np.empty(self.len, dtype=_STORAGE[self.element])
+        _check(self.gpu._lib.gpurs_download(self.gpu._handle, self.pointer, out.ctypes.data, out.nbytes))
+        return out
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self.pointer and self.gpu._handle:
+            self.gpu._lib.gpurs_free(self.gpu._handle, self.pointer)
+            self.pointer = 0
+
+
+class Kernel:
+    """`raw::Kernel` (crates/gpurs/src/raw/module.rs:86-207)."""
+
+    def __init__(self, module: "Module", handle, name: str):
+        self.module, self._handle, self.name = module, handle, name
+
+    def reserve_shared(self, nbytes: int) -> None:
+        _check(self.module.gpu._lib.gpurs_kernel_reserve_shared(self._handle, nbytes))
+
+    @property
+    def registers(self) -> int:
+        value = C.c_int()
+        _check(self.module.gpu._lib.gpurs_kernel_registers(self._handle, C.byref(value)))
+        return value.value
+
+    def launch(self, stream: Stream, config: LaunchConfig, params: list) -> None:
+        """`params` are ctypes objects; their addresses form the driver's parameter array."""
+        array = (C.c_void_p * len(params))(*[C.cast(C.pointer(p), C.c_void_p) for p in params])
+        struct = config._struct()
+        _check(self.module.gpu._lib.gpurs_kernel_launch(self._handle, stream._handle, C.byref(struct), array))
+
+
+class Module:
+    """`raw::Module` (crates/gpurs/src/raw/module.rs:36-92)."""
+
+    def __init__(self, gpu: "Gpu", handle, image: bytes):
+        self.gpu, self._handle, self._image = gpu, handle, image
+
+    def kernel(self, name: str) -> Kernel:
+        handle = C.c_void_p()
+        _check(self.gpu._lib.gpurs_module_kernel(self._handle, name.encode(), C.byref(handle)))
+        return Kernel(self, handle, name)
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and self.gpu._handle:
+            self.gpu._lib.gpurs_module_free(self._handle)
+            self._handle = None
+
+
+class Gpu:
+    """`Gpu` (crates/gpurs/src/host/context.rs:26-168): one device's primary context."""
+
+    def __init__(self, ordinal: int = 0):
+        self._lib = _ffi.load()
+        self._handle = C.c_void_p()
+        _check(self._lib.gpurs_gpu_new(ordinal, C.byref(self._handle)))
+        major, minor, sms, total = C.c_int(), C.c_int(), C.c_int(), C.c_size_t()
+        _check(self._lib.gpurs_gpu_properties(self._handle, C.byref(major), C.byref(minor), C.byref(sms), C.byref(total)))
+        self.ordinal = ordinal
+        self.compute_capability = (major.value, minor.value)
+        self.multiprocessors = sms.value
+        self.total_bytes = total.value
+
+    def stream(self) -> Stream:
+        handle = C.c_void_p()
+        _check(self._lib.gpurs_stream_new(self._handle, C.byref(handle)))
+        return Stream(self, handle)
+
+    def borrow_stream(self, raw: int) -> Stream:
+        """Wrap a CUstream made elsewhere (for example `torch.cuda.current_stream().cuda_stream`)."""
+        handle = C.c_void_p()
+        _check(self._lib.gpurs_stream_borrow(self._handle, C.c_void_p(raw), C.byref(handle)))
+        return Stream(self, handle)
+
+    def upload(self, host: np.ndarray, element: int | None = None) -> DeviceBuffer:
+        """Allocate, copy `host` and wait for the copy.  `element` names the format when the array holds
+        bit patterns (uint16 for F16 / BF16, uint8 for E4M3)."""
+        host = np.ascontiguousarray(host)
+        if element is None:
+            element = _FROM_NUMPY.get(host.dtype)
+            if element is None:
+                raise TypeError(f"name the element format of a {host.dtype} array")
+        if host.dtype.itemsize != ELEMENT_BYTES[element]:
+            raise TypeError("array item size does not match the element format")
+        pointer = C.c_uint64()
+        _check(self._lib.gpurs_upload(self._handle, host.ctypes.data, host.nbytes, C.byref(pointer)))
+        return DeviceBuffer(self, pointer.value, host.size, element)
+
+    def zeros(self, element: int, length: int) -> DeviceBuffer:
+        pointer = C.c_uint64()
+        _check(self._lib.gpurs_zeros(self._handle, length * ELEMENT_BYTES[element], C.byref(pointer)))
+        return DeviceBuffer(self, pointer.value, length, element)
+
+    def allocate(self, element: int, length: int) -> DeviceBuffer:
+        """Uninitialised storage (`Gpu::allocate`, crates/gpurs/src/raw/allocation.rs:54-74)."""
+        pointer = C.c_uint64()
+        _check(self._lib.gpurs_alloc(self._handle, length * ELEMENT_BYTES[element], C.byref(pointer)))
+        return DeviceBuffer(self, pointer.value, length, element)
+
+    def import_allocation(self, pointer: int, length: int, element: int) -> DeviceBuffer:
+        """Borrow device memory owned by someone else (`Gpu::import_allocation`)."""
+        return DeviceBuffer(self, pointer, length, element, owned=False)
+
+    def load_module(self, image: bytes) -> Module:
+        handle = C.c_void_p()
+        _check(self._lib.gpurs_module_load(self._handle, image, len(image), C.byref(handle)))
+        return Module(self, handle, image)
+
+    def kernel_image(self) -> bytes:
+        size = C.c_size_t()
+        pointer = self._lib.gpurs_kernel_image(C.byref(size))
+        return C.string_at(pointer, size.value)
+
+    def status(self) -> list[int]:
+        words = (C.c_uint32 * 4)()
+        _check(self._lib.gpurs_status_read(self._handle, words))
+        return list(words)
+
+    @property
+    def launches(self) -> int:
+        return self._lib.gpurs_launch_count(self._handle)
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.gpurs_gpu_free(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        # Buffers and streams may be finalised after the gpu: they check `_handle` before freeing.
+        pass
+
+
+@dataclass
+class MatmulOptions:
+    """Optional arguments of `matmul`: row pitches in elements (0 = contiguous), tile algorithm, CTA
+    limit, and the two fp32 scale arrays of a block-scaled E4M3 product."""
+
+    lda: int = 0
+    ldb: int = 0
+    ldc: int = 0
+    algorithm: int = _ffi.ALGO_AUTO
+    max_ctas: int = 0
+    scale_a: DeviceBuffer | None = None
+    scale_b: DeviceBuffer | None = None
+    extra: dict = field(default_factory=dict)
+
+
+def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, shape, options: MatmulOptions | None = None) -> None:
+    """C[m, n] = sum_k A[m, k] * B[n, k], enqueued on `stream`; shape = [m, n, k].
+
+    `a` is the m x k left operand, `b` the n x k "right_transposed" operand of the reference's examples
+    (examples/blackwell/examples/blackwell_matrix.rs:32-36), `c` the m x n row-major output.  Like a
+    launcher generated by the reference's `#[gpu]` macro it validates before it submits and does not
+    wait for the kernel."""
+    options = options or MatmulOptions()
+    if a.gpu is not stream.gpu or b.gpu is not stream.gpu or c.gpu is not stream.gpu:
+        raise GpursErrorLocal(_ffi.E_CONTEXT_MISMATCH, "buffers and stream belong to different Gpu handles")
+    if a.element != b.element:
+        raise GpursErrorLocal(_ffi.E_INVALID_ARGUMENT, "A and B must have the same element format")
+    m, n, k = (int(x) for x in shape)
+    desc = _ffi.MatmulDesc()
+    desc.a_type, desc.c_type = a.element, c.element
+    desc.m, desc.n, desc.k = m, n, k
+    desc.lda, desc.ldb, desc.ldc = options.lda, options.ldb, options.ldc
+    desc.a_len, desc.b_len, desc.c_len = a.len, b.len, c.len
+    desc.algorithm, desc.max_ctas = options.algorithm, options.max_ctas
+    desc.scale_a = options.scale_a.pointer if options.scale_a else 0
+    desc.scale_b = options.scale_b.pointer if options.scale_b else 0
+    _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
+
+
+class GpursErrorLocal(GpursError):
+    """A rejection raised by this layer before the C ABI is reached."""
+
+    def __init__(self, code: int, message: str):
+        RuntimeError.__init__(self, message)
+        self.code, self.operation, self.name, self.description = code, "matmul", "GPURS_ERROR", message

@@ -1,0 +1,199 @@
+/*
+ * gpurs_b200 — C ABI of the B200-native matrix-multiply path of gpurs.
+ *
+ * This is the boundary a gpurs host binds instead of (or beside) its own `crates/driver` FFI block
+ * (crates/driver/src/ffi.rs:47-214): plain pointers and sizes, opaque handles, `int` results.  Every
+ * function returns 0 on success, the raw CUresult of the failing CUDA driver call (1..99999), or one
+ * of the GPURS_E_* codes below, which mirror the variants of the reference's runtime error enum
+ * (crates/gpurs/src/error.rs:13-71).  Nothing throws, aborts or exits across this boundary.
+ *
+ * Threading follows the reference (crates/gpurs/src/lib.rs:7-9): a handle belongs to the host thread
+ * that created it; use one gpurs_gpu per device and thread.  Every call makes the handle's context
+ * current for its duration and restores the caller's on return
+ * (crates/driver/src/context.rs:117-129).
+ *
+ * Device memory handed to gpurs_matmul is borrowed until the stream has passed the launch
+ * (the contract of `Stream::submit_external`, crates/gpurs/src/raw/interop.rs:37-59).
+ */
+#ifndef GPURS_B200_H
+#define GPURS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef struct gpurs_gpu gpurs_gpu;
+typedef struct gpurs_stream gpurs_stream;
+typedef struct gpurs_event gpurs_event;
+typedef struct gpurs_module gpurs_module;
+typedef struct gpurs_kernel gpurs_kernel;
+typedef uint64_t gpurs_device_ptr; /* `DevicePointer = u64`, crates/driver/src/ffi.rs:10 */
+
+/* Library result codes (driver failures keep their CUresult value). */
+enum {
+    GPURS_OK = 0,
+    GPURS_E_CONTEXT_MISMATCH = 100001,   /* Error::ContextMismatch  */
+    GPURS_E_SIZE_OVERFLOW = 100002,      /* Error::SizeOverflow     */
+    GPURS_E_LENGTH_MISMATCH = 100003,    /* Error::LengthMismatch   */
+    GPURS_E_OVERLAP = 100004,            /* Error::Overlap          */
+    GPURS_E_INVALID_VIEW = 100005,       /* Error::InvalidView      */
+    GPURS_E_ALIASING = 100006,           /* Error::Aliasing         */
+    GPURS_E_UNKNOWN_KERNEL = 100007,     /* Error::UnknownKernel    */
+    GPURS_E_INCOMPATIBLE_DEVICE = 100008,/* Error::IncompatibleDevice */
+    GPURS_E_INVALID_ARGUMENT = 100009,   /* null handle / unknown enum value */
+    GPURS_E_DEVICE_TIMEOUT = 100010,     /* a bounded device-side wait gave up (no reference counterpart:
+                                            the reference's waits are unbounded) */
+    GPURS_E_DRIVER_UNAVAILABLE = 100011  /* libcuda could not be loaded */
+};
+
+/* Element types.  The values of the first three match the TMA data-type codes the reference uses
+ * (crates/gpurs/src/gpu/tensor/element.rs:48,78,113). */
+enum {
+    GPURS_F16 = 6,
+    GPURS_F32 = 7,
+    GPURS_BF16 = 9,
+    GPURS_I8 = 100,
+    GPURS_I32 = 101,
+    GPURS_E4M3 = 102
+};
+
+/* ---- context, streams, events ---------------------------------------------------------------- */
+
+/* `Gpu::new(ordinal)` (crates/gpurs/src/host/context.rs:69): retains the device's primary context.
+ * Fails with GPURS_E_INCOMPATIBLE_DEVICE unless the device is compute capability 10.0, the only
+ * target the embedded sm_100a image supports (crates/artifact/src/target.rs:68-72). */
+int gpurs_gpu_new(int ordinal, gpurs_gpu **out);
+void gpurs_gpu_free(gpurs_gpu *gpu);
+int gpurs_gpu_properties(gpurs_gpu *gpu, int *major, int *minor, int *multiprocessors, size_t *total_bytes);
+
+/* `gpu.stream()` (context.rs:125-130): a new non-blocking stream. */
+int gpurs_stream_new(gpurs_gpu *gpu, gpurs_stream **out);
+/* Borrow a CUstream created elsewhere (`AsRaw` / `Stream::submit_external`, crates/gpurs/src/raw/interop.rs:45-59).
+ * `raw` may be NULL for the legacy default stream. */
+int gpurs_stream_borrow(gpurs_gpu *gpu, void *raw, gpurs_stream **out);
+void gpurs_stream_free(gpurs_stream *stream);
+void *gpurs_stream_raw(gpurs_stream *stream);
+/* `Stream::synchronize` (crates/gpurs/src/host/stream.rs).  Also collects the device status word:
+ * returns GPURS_E_DEVICE_TIMEOUT if a kernel's bounded wait gave up since the last call. */
+int gpurs_stream_synchronize(gpurs_stream *stream);
+
+/* `Stream::record_timed` / `Event::elapsed` (crates/gpurs/src/host/stream.rs:109-115,184-186). */
+int gpurs_event_record_timed(gpurs_stream *stream, gpurs_event **out);
+int gpurs_event_synchronize(gpurs_event *event);
+int gpurs_event_elapsed_ms(gpurs_event *start, gpurs_event *end, float *milliseconds);
+void gpurs_event_free(gpurs_event *event);
+
+/* ---- memory ---------------------------------------------------------------------------------- */
+
+/* `Gpu::allocate` (crates/gpurs/src/raw/allocation.rs:54-74): uninitialised device memory. */
+int gpurs_alloc(gpurs_gpu *gpu, size_t bytes, gpurs_device_ptr *out);
+int gpurs_free(gpurs_gpu *gpu, gpurs_device_ptr pointer);
+/* `gpu.upload(&host)` (context.rs:132-149): allocate, copy, and wait for the copy. */
+int gpurs_upload(gpurs_gpu *gpu, const void *host, size_t bytes, gpurs_device_ptr *out);
+/* `gpu.zeros::<T>(n)` (context.rs:151-168): allocate and clear. */
+int gpurs_zeros(gpurs_gpu *gpu, size_t bytes, gpurs_device_ptr *out);
+/* `DeviceSlice::download` (crates/gpurs/src/host/memory/buffer.rs:251-271): copy back and wait. */
+int gpurs_download(gpurs_gpu *gpu, gpurs_device_ptr source, void *host, size_t bytes);
+/* Stream-ordered copies between existing buffers (`copy_from_host` / `copy_to_host`,
+ * crates/driver/src/memory.rs); the host side should be pinned for the copy to be asynchronous. */
+int gpurs_copy_to_device(gpurs_stream *stream, gpurs_device_ptr destination, const void *host, size_t bytes);
+int gpurs_copy_to_host(gpurs_stream *stream, void *host, gpurs_device_ptr source, size_t bytes);
+int gpurs_fill_u8(gpurs_stream *stream, gpurs_device_ptr destination, uint8_t value, size_t bytes);
+/* Page-locked host memory (`PinnedBuffer`, crates/gpurs/src/host/memory/pinned.rs). */
+int gpurs_host_alloc(gpurs_gpu *gpu, size_t bytes, void **out);
+int gpurs_host_free(gpurs_gpu *gpu, void *pointer);
+
+/* ---- TMA descriptors ------------------------------------------------------------------------- */
+
+/* Generalises `driver::try_tensor_map` (crates/driver/src/memory.rs:325-354), which is fixed to rank 2,
+ * SWIZZLE_128B, L2 promotion 256 B and zero fill.  `descriptor` receives the 128-byte CUtensorMap and
+ * must be 64-byte aligned.  dims / box are innermost first; strides_bytes has rank-1 entries (the
+ * innermost dimension is contiguous).  swizzle: 0 none, 1 32 B, 2 64 B, 3 128 B.  l2_promotion:
+ * 0 none, 1 64 B, 2 128 B, 3 256 B.  Element types: GPURS_F16/F32/BF16/I32, and GPURS_I8 / GPURS_E4M3
+ * (both encoded as bytes). */
+int gpurs_tensor_map_encode(gpurs_gpu *gpu, void *descriptor, int element_type, uint32_t rank,
+                            gpurs_device_ptr address, const uint64_t *dims, const uint64_t *strides_bytes,
+                            const uint32_t *box, int swizzle, int l2_promotion);
+
+/* ---- external modules: the reference's drop-in door ------------------------------------------- */
+
+/* `LaunchConfig` (crates/gpurs/src/host/stream.rs:28-52) plus the cluster dimension the driver crate
+ * already models (crates/driver/src/launch.rs:21,43-49) but the reference's raw launch never sets
+ * (crates/gpurs/src/raw/module.rs:195). */
+typedef struct gpurs_launch_config {
+    uint32_t grid[3];
+    uint32_t block[3];
+    uint32_t shared_bytes;
+    uint32_t cluster[3]; /* all zero or all one: no cluster attribute */
+} gpurs_launch_config;
+
+/* `Gpu::load_module` / `Module::kernel` / `Kernel::reserve_shared` / `Kernel::launch`
+ * (crates/gpurs/src/raw/module.rs:64-67,86-92,143-146,158-207).  `params` is the driver's
+ * array-of-pointers form (crates/driver/src/launch.rs:83-110). */
+int gpurs_module_load(gpurs_gpu *gpu, const void *image, size_t bytes, gpurs_module **out);
+void gpurs_module_free(gpurs_module *module);
+int gpurs_module_kernel(gpurs_module *module, const char *name, gpurs_kernel **out);
+int gpurs_kernel_reserve_shared(gpurs_kernel *kernel, uint32_t bytes);
+int gpurs_kernel_registers(gpurs_kernel *kernel, int *registers);
+int gpurs_kernel_launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params);
+/* The sm_100a kernel image built into this library, for hosts that prefer to load it through their
+ * own module path (the reference's `Gpu::load_module(&[u8])`). */
+const void *gpurs_kernel_image(size_t *bytes);
+
+/* ---- the matrix multiply --------------------------------------------------------------------- */
+
+/* Tile / algorithm choice.  AUTO is what a caller should use. */
+enum {
+    GPURS_ALGO_AUTO = 0,
+    GPURS_ALGO_SINGLE_CTA = 1,  /* 128 x 256 tiles, one CTA per tile (tcgen05 cta_group::1) */
+    GPURS_ALGO_CTA_PAIR = 2     /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
+};
+
+/* C[m, n] = sum_k A[m, k] * B[n, k]: A is m x k, B is n x k ("right_transposed",
+ * examples/blackwell/examples/blackwell_matrix.rs:35,64), C is m x n, all row-major.  A zeroed
+ * descriptor with the three types and m, n, k set describes the dense contiguous case. */
+typedef struct gpurs_matmul_desc {
+    int32_t a_type;   /* element type of A and of B: GPURS_F16, GPURS_BF16, GPURS_F32, GPURS_I8, GPURS_E4M3 */
+    int32_t c_type;   /* GPURS_F32, GPURS_BF16, GPURS_F16 (float inputs) or GPURS_I32 (GPURS_I8 inputs) */
+    uint64_t m, n, k;
+    uint64_t lda, ldb, ldc;          /* row pitches in elements; 0 = contiguous (k, k, n) */
+    uint64_t a_len, b_len, c_len;    /* slice lengths in elements for the bounds check; 0 = not checked */
+    int32_t algorithm;               /* GPURS_ALGO_* */
+    int32_t max_ctas;                /* upper bound on resident CTAs (0 = one per multiprocessor) */
+    gpurs_device_ptr scale_a;        /* GPURS_E4M3 block-scaled: fp32 [m][ceil(k/128)], else 0 */
+    gpurs_device_ptr scale_b;        /* GPURS_E4M3 block-scaled: fp32 [ceil(n/128)][ceil(k/128)], else 0 */
+} gpurs_matmul_desc;
+
+/* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
+ * generated launchers do before submitting (lengths, views, aliasing:
+ * crates/gpurs/src/host/launch/kernel.rs:178-255,322-355), encodes the TMA descriptors
+ * (crates/gpurs/src/host/argument/tensor_map.rs:24-60), and enqueues one kernel on `stream`.
+ * It does not wait. */
+int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
+                 gpurs_device_ptr c);
+
+/* Reads and clears the device status word: [0] code (0 = none), [1] block, [2] tile, [3] K-block of the
+ * first bounded wait that gave up.  Synchronises the device. */
+int gpurs_status_read(gpurs_gpu *gpu, uint32_t status[4]);
+
+/* Number of kernels this library has launched through `gpu` so far. */
+uint64_t gpurs_launch_count(gpurs_gpu *gpu);
+
+/* Detail of the calling thread's most recent failure: the operation, the CUDA error name and its
+ * description (`driver::Error`, crates/driver/src/error.rs:8-16).  Pointers stay valid until the
+ * thread's next failing call. */
+int gpurs_last_error(const char **operation, const char **name, const char **description);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPURS_B200_H */
