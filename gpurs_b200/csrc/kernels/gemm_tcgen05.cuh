@@ -275,6 +275,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     }
 
     // ---------------------------------------------------------------------- teardown
+    __syncwarp();
     ptx::tcgen05_fence_before();
     __syncthreads();
     if (*abort_flag != 0 && threadIdx.x == 0) {
@@ -283,6 +284,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
         const unsigned long long start = ptx::global_timer();
         while (ptx::global_timer() - start < 2000000ull) __nanosleep(1000);
     }
+    __syncwarp();
     if constexpr (CTA_GROUP == 2) {
         ptx::cluster_arrive();
         ptx::cluster_wait();
