@@ -1,0 +1,166 @@
+"""Parity of the CUDA GEMM path with the oracle, through the C ABI, on a B200."""
+import numpy as np
+import pytest
+
+import gpurs_b200 as G
+import oracle as O
+from helpers import KINDS, decode_output, make_operands, relative_error, run_matmul, spread_rows
+
+pytestmark = pytest.mark.gpu
+
+ALGORITHMS = [G.ALGO_SINGLE_CTA, G.ALGO_CTA_PAIR]
+
+# operand kind, output, tolerance on |d| / max(|ref|, 1) against the fp64 oracle (0 = bit-exact)
+FLOAT_CASES = [
+    ("f16", "f32", 1e-3),    # fp32 accumulation of exactly representable products: only summation-order error
+    ("f16", "f16", 2e-3),    # + one rounding to binary16 (2^-11)
+    ("bf16", "f32", 1e-3),
+    ("bf16", "bf16", 1e-2),  # the tolerance the bf16 configuration states
+    ("e4m3", "f32", 1e-3),
+    ("e4m3", "bf16", 1e-2),
+    ("f32", "f32", 2e-2),    # one TF32 pass, as the reference's f32 tensor element (element.rs:75-110)
+]
+SMALL_SHAPES = [(128, 256, 64), (1, 8, 16), (200, 300, 144), (384, 768, 1024), (129, 257, 4096), (640, 512, 80)]
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("shape", SMALL_SHAPES)
+@pytest.mark.parametrize("kind,out,tolerance", FLOAT_CASES)
+def test_float_product_matches_oracle(gpu, stream, kind, out, tolerance, shape, algorithm):
+    m, n, k = shape
+    a, b = make_operands(kind, m, n, k)
+    got = decode_output(run_matmul(gpu, stream, kind, out, a, b, m, n, k, algorithm), out).reshape(m, n)
+    expected = O.matmul_rows(KINDS[kind][1], a, b, n, k, np.arange(m))
+    assert relative_error(got, expected) <= tolerance
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("shape", SMALL_SHAPES + [(512, 512, 2048)])
+def test_int8_product_is_bit_exact(gpu, stream, shape, algorithm):
+    m, n, k = shape
+    a, b = make_operands("i8", m, n, k)
+    got = run_matmul(gpu, stream, "i8", "i32", a, b, m, n, k, algorithm).reshape(m, n)
+    assert np.array_equal(got.astype(np.int64), O.matmul_rows_i8(a, b, n, k, np.arange(m)))
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("size", [320, 1024])
+def test_reference_example_inputs_are_reproduced_bit_for_bit(gpu, stream, kind, size, algorithm):
+    """On the reference's own inputs every partial sum is exact in fp32, so the fp32 result is unique:
+    any correct kernel, the reference's included, must equal the fp64 check loop bit for bit."""
+    a, b = make_operands(kind, size, size, size, "example")
+    got = run_matmul(gpu, stream, kind, "f32", a, b, size, size, size, algorithm).reshape(size, size)
+    expected = O.matmul_rows(KINDS[kind][1], a, b, size, size, np.arange(size))
+    assert np.array_equal(got.astype(np.float64), expected)
+
+
+def test_golden_example_product(gpu, stream):
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "example_product_320.npz")
+    size = int(g["size"])
+    a, b = make_operands("f16", size, size, size, "example")
+    got = run_matmul(gpu, stream, "f16", "f32", a, b, size, size, size).reshape(size, size)
+    assert np.array_equal(got, g["product"])
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+def test_reference_configuration_4096(gpu, stream, algorithm):
+    """The reference example's own run: f16 4096^3, fp32 out, checked at the indices its report samples
+    (examples/matrix_benchmark.rs:36-51) and on whole rows; bit-exact, well inside its 1e-2 bound."""
+    size = 4096
+    a, b = make_operands("f16", size, size, size, "example")
+    got = run_matmul(gpu, stream, "f16", "f32", a, b, size, size, size, algorithm)
+    indices = O.reference_sample_indices(size, size)
+    assert np.array_equal(got[indices].astype(np.float64), O.matmul_samples(O.FMT_F16, a, b, size, size, indices))
+    rows = spread_rows(size, 24)
+    assert np.array_equal(got.reshape(size, size)[rows].astype(np.float64), O.matmul_rows(O.FMT_F16, a, b, size, size, rows))
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+def test_bf16_8192_configuration(gpu, stream, algorithm):
+    """bf16 8192^3, N(0,1) operands, fp32 accumulate, bf16 out; max rel err 1e-2 against fp64."""
+    size = 8192
+    a, b = make_operands("bf16", size, size, size)
+    bits = run_matmul(gpu, stream, "bf16", "bf16", a, b, size, size, size, algorithm)
+    got = decode_output(bits, "bf16")
+    indices = O.reference_sample_indices(size, size)
+    assert relative_error(got[indices], O.matmul_samples(O.FMT_BF16, a, b, size, size, indices)) <= 1e-2
+    rows = spread_rows(size, 32)
+    assert relative_error(got.reshape(size, size)[rows], O.matmul_rows(O.FMT_BF16, a, b, size, size, rows)) <= 1e-2
+    # size-independent property over the whole output: doubling A doubles every output exactly
+    doubled = (a + np.uint16(0x0080)).astype(np.uint16)  # exponent + 1; no operand is near overflow
+    bits2 = run_matmul(gpu, stream, "bf16", "bf16", doubled, b, size, size, size, algorithm)
+    assert np.array_equal(decode_output(bits2, "bf16"), 2.0 * got)
+
+
+def test_int8_8192_configuration_and_whole_matrix_checksum(gpu, stream):
+    """int8 8192^3 -> int32, bit-exact on sampled rows, and the sum of ALL outputs equals
+    sum_k (sum_m A[m,k]) * (sum_n B[n,k]) computed in int64 on the host."""
+    size = 8192
+    a, b = make_operands("i8", size, size, size)
+    got = run_matmul(gpu, stream, "i8", "i32", a, b, size, size, size).reshape(size, size)
+    rows = spread_rows(size, 32)
+    assert np.array_equal(got[rows].astype(np.int64), O.matmul_rows_i8(a, b, size, size, rows))
+    column_sums_a = a.reshape(size, size).astype(np.int64).sum(axis=0)
+    column_sums_b = b.reshape(size, size).astype(np.int64).sum(axis=0)
+    assert int(got.astype(np.int64).sum()) == int((column_sums_a * column_sums_b).sum())
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+def test_row_permutation_commutes(gpu, stream, algorithm):
+    """Permuting the rows of A permutes the rows of C bit for bit: no output depends on where its tile lies."""
+    m, n, k = 1024, 768, 512
+    a, b = make_operands("bf16", m, n, k)
+    base = run_matmul(gpu, stream, "bf16", "f32", a, b, m, n, k, algorithm).reshape(m, n)
+    order = np.random.default_rng(0).permutation(m)
+    permuted = run_matmul(gpu, stream, "bf16", "f32", a.reshape(m, k)[order].reshape(-1), b, m, n, k, algorithm).reshape(m, n)
+    assert np.array_equal(permuted, base[order])
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+def test_row_pitches_and_untouched_padding(gpu, stream, algorithm):
+    m, n, k, lda, ldb, ldc = 200, 264, 136, 144, 160, 272
+    a_dense, b_dense = make_operands("f16", m, n, k)
+    a = np.full(m * lda, 0x7E00, np.uint16)  # NaN in the padding: it must never be read into the product
+    b = np.full(n * ldb, 0x7E00, np.uint16)
+    a.reshape(m, lda)[:, :k] = a_dense.reshape(m, k)
+    b.reshape(n, ldb)[:, :k] = b_dense.reshape(n, k)
+    raw = run_matmul(gpu, stream, "f16", "f32", a, b, m, n, k, algorithm, lda=lda, ldb=ldb, ldc=ldc)
+    padded = np.full(m * ldc, np.nan, np.float32)
+    padded[: raw.size] = raw
+    padded = padded.reshape(m, ldc)
+    expected = O.matmul_rows(O.FMT_F16, a_dense, b_dense, n, k, np.arange(m))
+    assert relative_error(padded[:, :n].astype(np.float64), expected) <= 1e-3
+    poison = np.frombuffer(bytes([0x7F] * 4), np.float32)[0]
+    tail = padded[:-1, n:]
+    assert (tail.view(np.uint32) == np.float32(poison).view(np.uint32)).all(), "the kernel wrote outside its rows"
+
+
+def test_unaligned_output_falls_back_to_scalar_stores(gpu, stream):
+    m, n, k = 130, 77, 64   # n * 2 bytes is not a multiple of 16
+    a, b = make_operands("bf16", m, n, k)
+    got = decode_output(run_matmul(gpu, stream, "bf16", "bf16", a, b, m, n, k), "bf16").reshape(m, n)
+    assert relative_error(got, O.matmul_rows(O.FMT_BF16, a, b, n, k, np.arange(m))) <= 1e-2
+
+
+def test_empty_shapes(gpu, stream):
+    a = gpu.upload(np.zeros(64, np.uint16), G.F16)
+    b = gpu.upload(np.zeros(64, np.uint16), G.F16)
+    c = gpu.upload(np.full(64, 7.0, np.float32))
+    G.matmul(stream, a, b, c, [0, 8, 8])
+    G.matmul(stream, a, b, c, [8, 0, 8])
+    stream.synchronize()
+    assert (c.download() == 7.0).all()      # nothing to write
+    G.matmul(stream, a, b, c, [8, 8, 0])     # an empty sum is zero
+    stream.synchronize()
+    assert (c.download() == 0.0).all()
+
+
+def test_launches_are_counted_and_status_is_clean(gpu, stream):
+    before = gpu.launches
+    a, b = make_operands("bf16", 256, 256, 256)
+    run_matmul(gpu, stream, "bf16", "bf16", a, b, 256, 256, 256)
+    assert gpu.launches == before + 1
+    assert gpu.status() == [0, 0, 0, 0]
