@@ -35,7 +35,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC = "GEMM TFLOP/s and % of B200 tensor peak (bf16/FP8/int8) at 1/2/4/8 GPUs"
-NOMINAL_PEAK = {"bf16": 2250.0, "f16": 2250.0, "i8": 4500.0, "e4m3": 4500.0}
+NOMINAL_PEAK = {"bf16": 2250.0, "f16": 2250.0, "i8": 4500.0, "e4m3": 4500.0, "f32": 1125.0}
 
 # name -> (operand kind, output, M per GPU, N, K)
 WORKLOADS = {
@@ -43,6 +43,8 @@ WORKLOADS = {
     "f16_4096_example": ("f16", "f32", 4096, 4096, 4096),
     "int8_8192": ("i8", "i32", 8192, 8192, 8192),
     "e4m3_unscaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),
+    "e4m3_scaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),   # fp32 scales per 1x128 / 128x128 block
+    "f32_1024": ("f32", "f32", 1024, 1024, 1024),
 }
 DEFAULT_WORKLOAD = "bf16_8192"
 
@@ -67,6 +69,8 @@ def synthetic_operand(kind: str, rows: int, depth: int, seed: int) -> np.ndarray
         return ((index * factor % modulus) / 16.0 - 1.0).astype(np.float16).view(np.uint16)
     if kind == "i8":
         return rng.integers(-128, 128, rows * depth, dtype=np.int8)
+    if kind == "f32":
+        return rng.uniform(-1.0, 1.0, rows * depth).astype(np.float32)
     if kind == "e4m3":
         import torch
 
@@ -134,7 +138,7 @@ def cpu_band(kind: str, n: int, k: int, rows: int, seed: int = 1):
     """Times the oracle's check loop on `rows` complete output rows; returns (seconds, flops, threads)."""
     import oracle as O
 
-    fmt = {"bf16": O.FMT_BF16, "f16": O.FMT_F16, "i8": O.FMT_I8, "e4m3": O.FMT_E4M3}[kind]
+    fmt = {"bf16": O.FMT_BF16, "f16": O.FMT_F16, "i8": O.FMT_I8, "e4m3": O.FMT_E4M3, "f32": O.FMT_F32}[kind]
     a = synthetic_operand(kind, rows, k, seed)
     b = synthetic_operand(kind, n, k, seed + 1)
     row_list = np.arange(rows)
@@ -181,7 +185,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     import gpurs_b200 as G
 
     kind, out, m, n, k = WORKLOADS[args.workload]
-    element = {"bf16": G.BF16, "f16": G.F16, "i8": G.I8, "e4m3": G.E4M3}[kind]
+    element = {"bf16": G.BF16, "f16": G.F16, "i8": G.I8, "e4m3": G.E4M3, "f32": G.F32}[kind]
     out_element = {"bf16": G.BF16, "f32": G.F32, "i32": G.I32}[out]
     element_bytes, out_bytes = G.host.ELEMENT_BYTES[element], G.host.ELEMENT_BYTES[out_element]
 
@@ -201,7 +205,13 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     a, b = gpu.upload(a_host, element), gpu.upload(b_host, element)
     c = gpu.allocate(out_element, m * n)
     shape = [m, n, k]
-    options = G.MatmulOptions(algorithm=args.algorithm)
+    options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows)
+    if "scaled" in args.workload and "unscaled" not in args.workload:
+        # synthetic scales with the magnitude absmax/448 has for N(0,1) blocks
+        rng = np.random.default_rng(99)
+        k_blocks = (k + 127) // 128
+        options.scale_a = gpu.upload(rng.uniform(3.0, 4.5, m * k_blocks).astype(np.float32) / np.float32(448.0))
+        options.scale_b = gpu.upload(rng.uniform(4.0, 5.0, ((n + 127) // 128) * k_blocks).astype(np.float32) / np.float32(448.0))
 
     def barrier():
         stream.synchronize()
@@ -275,6 +285,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
         peak, peak_source = measured_peak_tflops()
         if kind in ("i8", "e4m3"):
             peak, peak_source = peak * 2.0, peak_source + " x2 for 8-bit operands"
+        if kind == "f32":
+            peak, peak_source = peak / 2.0, peak_source + " /2 for TF32 operands"
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind, "data": "synthetic",
@@ -314,6 +326,7 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--algorithm", type=int, default=0, help="0 auto, 1 single-CTA tiles, 2 CTA-pair tiles")
+    parser.add_argument("--raster-rows", type=int, default=0, help="tile rows walked together (0 = library default)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))

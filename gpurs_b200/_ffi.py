@@ -26,6 +26,7 @@ E_DRIVER_UNAVAILABLE = 100011
 
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
 ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR = 0, 1, 2
+PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
 
 
 class LaunchConfigStruct(C.Structure):
@@ -38,7 +39,7 @@ class MatmulDesc(C.Structure):
         ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
         ("lda", C.c_uint64), ("ldb", C.c_uint64), ("ldc", C.c_uint64),
         ("a_len", C.c_uint64), ("b_len", C.c_uint64), ("c_len", C.c_uint64),
-        ("algorithm", C.c_int32), ("max_ctas", C.c_int32),
+        ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64),
     ]
 

@@ -21,6 +21,7 @@ namespace driver {
     X(cuStreamCreate)             \
     X(cuStreamDestroy)            \
     X(cuStreamSynchronize)        \
+    X(cuStreamWaitEvent)          \
     X(cuEventCreate)              \
     X(cuEventRecord)              \
     X(cuEventSynchronize)         \

@@ -38,6 +38,98 @@ bool choose(int a_type, int c_type, Choice &choice) {
 // Half-open byte ranges [begin, end) overlap?
 bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { return a < b + b_bytes && b < a + a_bytes; }
 
+// One launch of a tcgen05 GEMM entry: everything the kernel needs, already validated.
+struct Gemm {
+    const char *stem;
+    int element_type, element_bytes, output_bytes;
+    gpurs_device_ptr a, b, c;
+    uint64_t lda, ldb, ldc, m, n, k;
+    int cta_group, raster_rows, max_ctas;
+    gpurs_device_ptr scale_a = 0, scale_b = 0;   // block-scaled E4M3 only
+    int threads = gemm::NUM_THREADS;
+};
+
+int launch_gemm(gpurs_stream *stream, const Gemm &g) {
+    gpurs_gpu *gpu = stream->gpu;
+    const int cta_group = g.cta_group;
+    const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
+    char name[96];
+    std::snprintf(name, sizeof name, "%s_cg%d", g.stem, cta_group);
+    const uint32_t shared_bytes = cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
+                                                 : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
+    if (result != GPURS_OK) return result;
+
+    // The two operand descriptors: rows of 128 bytes of K, 128-byte swizzle, out-of-range reads as
+    // zero, the same form the reference encodes (crates/driver/src/memory.rs:325-354) with boxes of
+    // 128 rows of A and 256 (or, per CTA of a pair, 128) rows of B.
+    const uint32_t block_k = uint32_t(gemm::ROW_BYTES / g.element_bytes);
+    alignas(64) CUtensorMap map_a, map_b;
+    const uint64_t dims_a[2] = {g.k, g.m}, dims_b[2] = {g.k, g.n};
+    const uint64_t stride_a[1] = {g.lda * eb}, stride_b[1] = {g.ldb * eb};
+    const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)}, box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
+    result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 2, g.a, dims_a, stride_a, box_a, 3, 3);
+    if (result != GPURS_OK) return result;
+    result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 2, g.b, dims_b, stride_b, box_b, 3, 3);
+    if (result != GPURS_OK) return result;
+
+    gemm::Params params;
+    std::memset(&params, 0, sizeof params);
+    params.c = reinterpret_cast<void *>(g.c);
+    params.ldc = (long long)g.ldc;
+    params.m = int(g.m);
+    params.n = int(g.n);
+    params.k = int(g.k);
+    const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
+    params.tiles_m = int((g.m + tile_rows - 1) / tile_rows);
+    params.tiles_n = int((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
+    // Bands of 2048 rows by default: with one tile per SM in flight, the tiles running together then
+    // cover about 2048 x 2304 outputs, a near-square patch whose A and B panels are shared through L2.
+    params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16 / cta_group;
+    params.vector_stores = (g.c % 16 == 0 && (g.ldc * ob) % 16 == 0) ? 1 : 0;
+    params.status = reinterpret_cast<unsigned int *>(gpu->status);
+    params.scale_a = reinterpret_cast<const float *>(g.scale_a);
+    params.scale_b = reinterpret_cast<const float *>(g.scale_b);
+
+    const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
+    uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    uint64_t clusters = std::max<uint64_t>(1, ctas / cta_group);
+    clusters = std::min(clusters, tiles);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(clusters * cta_group);
+    config.grid[1] = config.grid[2] = 1;
+    config.block[0] = uint32_t(g.threads);
+    config.block[1] = config.block[2] = 1;
+    config.shared_bytes = shared_bytes;
+    config.cluster[0] = uint32_t(cta_group);
+    config.cluster[1] = config.cluster[2] = 1;
+    void *arguments[3] = {&map_a, &map_b, &params};
+    return runtime::launch(kernel, stream, &config, arguments);
+}
+
+// Enqueues the hi/lo split of a rows x k fp32 matrix into a rows x 3k one (kernels/transform.cu).
+int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t rows, uint64_t k, int order) {
+    gpurs_gpu *gpu = stream->gpu;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_split_tf32", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t quads = rows * (k / 4);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    // a whole number of waves: up to 8 blocks of 256 threads per multiprocessor
+    const uint64_t blocks = std::min<uint64_t>((quads + 255) / 256, uint64_t(gpu->multiprocessors) * 8);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, blocks));
+    config.block[0] = 256;
+    const void *source_pointer = reinterpret_cast<const void *>(source);
+    void *destination_pointer = reinterpret_cast<void *>(destination);
+    long long source_pitch = (long long)pitch;
+    int row_count = int(rows), depth = int(k);
+    void *arguments[6] = {&source_pointer, &source_pitch, &destination_pointer, &row_count, &depth, &order};
+    return runtime::launch(kernel, stream, &config, arguments);
+}
+
 }  // namespace
 
 extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
@@ -61,6 +153,7 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     if (!c) return fail(op, GPURS_E_INVALID_ARGUMENT, "null output");
     const uint64_t eb = uint64_t(choice.element_bytes), ob = uint64_t(choice.output_bytes);
     runtime::Enter enter(gpu);
+    int result = GPURS_OK;
     if (k == 0) {
         // An empty sum: the product is all zeros.
         for (uint64_t row = 0; row < (ldc == n ? 1 : m); row++)
@@ -79,63 +172,56 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     if (c % ob) return fail(op, GPURS_E_INVALID_VIEW, "the output is not aligned to its element size");
     if ((desc->scale_a != 0) != (desc->scale_b != 0))
         return fail(op, GPURS_E_INVALID_ARGUMENT, "both scale arrays or neither must be given");
-    if (desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "block-scaled operands are not supported by this build");
+    if (desc->scale_a && desc->a_type != GPURS_E4M3) return fail(op, GPURS_E_INVALID_ARGUMENT, "scales are for E4M3 operands only");
+    if (desc->scale_a && (desc->scale_a % 4 || desc->scale_b % 4)) return fail(op, GPURS_E_INVALID_VIEW, "scale arrays must be 4-byte aligned");
 
     int group = desc->algorithm;
-    if (group == GPURS_ALGO_AUTO) group = m > 128 ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
+    // Kernels that promote every K-block to registers hand an accumulator back and forth once per block;
+    // across a CTA pair that hand-off costs more than the pair saves, so they default to one-CTA tiles.
+    const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
+    if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
-    const int cta_group = group == GPURS_ALGO_CTA_PAIR ? 2 : 1;
+    if (desc->precision != GPURS_PRECISION_DEFAULT && desc->precision != GPURS_PRECISION_TF32)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown precision");
+    Gemm gemm;
+    gemm.stem = choice.stem;
+    gemm.element_type = desc->a_type;
+    gemm.element_bytes = choice.element_bytes;
+    gemm.output_bytes = choice.output_bytes;
+    gemm.a = a, gemm.b = b, gemm.c = c;
+    gemm.lda = lda, gemm.ldb = ldb, gemm.ldc = ldc;
+    gemm.m = m, gemm.n = n, gemm.k = k;
+    gemm.cta_group = group == GPURS_ALGO_CTA_PAIR ? 2 : 1;
+    gemm.raster_rows = desc->raster_rows;
+    gemm.max_ctas = desc->max_ctas;
+    if (desc->scale_a) {
+        // per-K-block promotion kernel: fp32 scales [m][ceil(k/128)] and [ceil(n/128)][ceil(k/128)]
+        gemm.stem = desc->c_type == GPURS_BF16 ? "gpurs_gemm_e4m3_scaled_bf16" : "gpurs_gemm_e4m3_scaled_f32";
+        gemm.scale_a = desc->scale_a;
+        gemm.scale_b = desc->scale_b;
+        gemm.threads = gemm::SCALED_THREADS;
+    }
 
-    char name[96];
-    std::snprintf(name, sizeof name, "%s_cg%d", choice.stem, cta_group);
-    const uint32_t shared_bytes = cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
-                                                 : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
-    gpurs_kernel *kernel = nullptr;
-    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
-    if (result != GPURS_OK) return result;
-
-    // The two operand descriptors: rows of 128 bytes of K, 128-byte swizzle, out-of-range reads as
-    // zero, the same form the reference encodes (crates/driver/src/memory.rs:325-354) with boxes of
-    // 128 rows of A and 256 (or, per CTA of a pair, 128) rows of B.
-    const uint32_t block_k = uint32_t(gemm::ROW_BYTES / choice.element_bytes);
-    alignas(64) CUtensorMap map_a, map_b;
-    const uint64_t dims_a[2] = {k, m}, dims_b[2] = {k, n};
-    const uint64_t stride_a[1] = {lda * eb}, stride_b[1] = {ldb * eb};
-    const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)}, box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
-    result = gpurs_tensor_map_encode(gpu, &map_a, desc->a_type, 2, a, dims_a, stride_a, box_a, 3, 3);
-    if (result != GPURS_OK) return result;
-    result = gpurs_tensor_map_encode(gpu, &map_b, desc->a_type, 2, b, dims_b, stride_b, box_b, 3, 3);
-    if (result != GPURS_OK) return result;
-
-    gemm::Params params;
-    std::memset(&params, 0, sizeof params);
-    params.c = reinterpret_cast<void *>(c);
-    params.ldc = (long long)ldc;
-    params.m = int(m);
-    params.n = int(n);
-    params.k = int(k);
-    const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
-    params.tiles_m = int((m + tile_rows - 1) / tile_rows);
-    params.tiles_n = int((n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
-    // Bands of 2048 rows: with one tile per SM in flight, the tiles running together then cover about
-    // 2048 x 2304 outputs, whose A and B panels stay within the L2.
-    params.raster_rows = 16 / cta_group;
-    params.vector_stores = (c % 16 == 0 && (ldc * ob) % 16 == 0) ? 1 : 0;
-    params.status = reinterpret_cast<unsigned int *>(gpu->status);
-
-    const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
-    uint64_t ctas = desc->max_ctas > 0 ? uint64_t(desc->max_ctas) : uint64_t(gpu->multiprocessors);
-    uint64_t clusters = std::max<uint64_t>(1, ctas / cta_group);
-    clusters = std::min(clusters, tiles);
-    gpurs_launch_config config;
-    std::memset(&config, 0, sizeof config);
-    config.grid[0] = uint32_t(clusters * cta_group);
-    config.grid[1] = config.grid[2] = 1;
-    config.block[0] = gemm::NUM_THREADS;
-    config.block[1] = config.block[2] = 1;
-    config.shared_bytes = shared_bytes;
-    config.cluster[0] = uint32_t(cta_group);
-    config.cluster[1] = config.cluster[2] = 1;
-    void *arguments[3] = {&map_a, &map_b, &params};
-    return runtime::launch(kernel, stream, &config, arguments);
+    if (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT) {
+        // fp32 operands at fp32-like accuracy: split both operands into TF32 hi and lo parts in scratch
+        // memory, laid out so that ONE K-major product over 3K sums hi*hi + hi*lo + lo*hi.
+        if (k % 4) return fail(op, GPURS_E_INVALID_VIEW, "operand bases and row pitches must be multiples of 16 bytes");
+        const uint64_t a_split = m * 3 * k * sizeof(float), b_split = n * 3 * k * sizeof(float);
+        CUdeviceptr scratch = 0;
+        result = runtime::workspace_acquire(stream, a_split + b_split, &scratch);
+        if (result != GPURS_OK) return result;
+        result = split_tf32(stream, a, lda, scratch, m, k, 0);
+        if (result == GPURS_OK) result = split_tf32(stream, b, ldb, scratch + a_split, n, k, 1);
+        gemm.a = scratch, gemm.b = scratch + a_split;
+        gemm.lda = gemm.ldb = 3 * k;
+        gemm.k = 3 * k;
+        // The tensor core's fp32 accumulator truncates after every instruction; promoting each K-block to
+        // registers keeps the sum round-to-nearest, which the 1e-4 bound needs once K reaches thousands.
+        gemm.stem = "gpurs_gemm_tf32_promoted_f32";
+        gemm.threads = gemm::SCALED_THREADS;
+        if (result == GPURS_OK) result = launch_gemm(stream, gemm);
+        int released = runtime::workspace_release(stream);
+        return result != GPURS_OK ? result : released;
+    }
+    return launch_gemm(stream, gemm);
 }

@@ -94,6 +94,33 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
     return GPURS_OK;
 }
 
+int workspace_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out) {
+    gpurs_gpu *gpu = stream->gpu;
+    const driver::Api *api = gpu->api;
+    if (gpu->workspace_bytes < bytes) {
+        // Nobody may still be using the old block when it is replaced.
+        GPURS_TRY(api, cuCtxSynchronize());
+        if (gpu->workspace) GPURS_TRY(api, cuMemFree(gpu->workspace));
+        gpu->workspace = 0;
+        gpu->workspace_bytes = 0;
+        const size_t rounded = (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);
+        GPURS_TRY(api, cuMemAlloc(&gpu->workspace, rounded));
+        gpu->workspace_bytes = rounded;
+        gpu->workspace_used = false;
+    }
+    if (!gpu->workspace_event) GPURS_TRY(api, cuEventCreate(&gpu->workspace_event, CU_EVENT_DISABLE_TIMING));
+    if (gpu->workspace_used) GPURS_TRY(api, cuStreamWaitEvent(stream->handle, gpu->workspace_event, 0));
+    *out = gpu->workspace;
+    return GPURS_OK;
+}
+
+int workspace_release(gpurs_stream *stream) {
+    gpurs_gpu *gpu = stream->gpu;
+    GPURS_TRY(gpu->api, cuEventRecord(gpu->workspace_event, stream->handle));
+    gpu->workspace_used = true;
+    return GPURS_OK;
+}
+
 }  // namespace runtime
 
 using runtime::Enter;
@@ -170,6 +197,8 @@ void gpurs_gpu_free(gpurs_gpu *gpu) {
             delete gpu->builtin;
         }
         gpu->api->cuMemFree(gpu->status);
+        if (gpu->workspace) gpu->api->cuMemFree(gpu->workspace);
+        if (gpu->workspace_event) gpu->api->cuEventDestroy(gpu->workspace_event);
         gpu->api->cuStreamDestroy(gpu->transfer);
     }
     gpu->api->cuDevicePrimaryCtxRelease(gpu->device);

@@ -29,6 +29,12 @@ struct gpurs_gpu {
     gpurs_module *builtin = nullptr;   // the embedded sm_100a image, loaded on first use
     std::map<std::string, gpurs_kernel *> kernels;
     uint64_t launches = 0;
+    // Grow-only scratch for operand transforms (the hi/lo split of fp32 operands).  One user at a time:
+    // `workspace_event` marks the end of the previous user's work, and the next user's stream waits on it.
+    CUdeviceptr workspace = 0;
+    size_t workspace_bytes = 0;
+    CUevent workspace_event = nullptr;
+    bool workspace_used = false;
 };
 
 struct gpurs_stream {
@@ -69,6 +75,11 @@ int fail(const char *operation, int code, const char *description);
 int builtin_kernel(gpurs_gpu *gpu, const char *name, uint32_t shared_bytes, gpurs_kernel **out);
 
 int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params);
+
+// Borrows at least `bytes` of the gpu's scratch for work about to be enqueued on `stream`; the work of
+// the previous borrower is ordered before it.  Call workspace_release once that work is enqueued.
+int workspace_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out);
+int workspace_release(gpurs_stream *stream);
 
 }  // namespace runtime
 

@@ -33,6 +33,7 @@ constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swi
 constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
 constexpr int NUM_THREADS = 192;
 constexpr int EPILOGUE_WARPS = 4;
+constexpr int SCALED_THREADS = 320;  // block-scaled FP8 kernel: producer warp, MMA warp, 8 promotion warps
 constexpr int BLOCK_N = 256;       // columns per tile
 constexpr int STAGES_SINGLE = 4;   // pipeline depth of the one-CTA kernels (48 KiB per stage)
 constexpr int STAGES_PAIR = 6;     // pipeline depth of the CTA-pair kernels (32 KiB per stage and CTA)

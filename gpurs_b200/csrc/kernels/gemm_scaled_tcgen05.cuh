@@ -1,0 +1,240 @@
+// Block-scaled FP8 (E4M3) GEMM for sm_100a:
+//
+//     C[m, n] = sum_kb  sA[m, kb] * sB[n / 128, kb] * ( sum_{k in block kb} A[m, k] * B[n, k] )
+//
+// A is M x K with one fp32 scale per row and 128-deep K-block, B is N x K with one fp32 scale per
+// 128 x 128 block.  The reference only ships the raw FP8 instruction for this
+// (crates/gpurs/src/gpu/tensor/blackwell/instruction.rs:13-21, tensor_memory.rs:136-165) and no kernel.
+//
+// The scales change with every K-block, so the tensor core cannot accumulate across blocks.  Instead each
+// 128-deep block is multiplied into a fresh TMEM accumulator (one pipeline stage = one block = 4
+// tcgen05.mma of K = 32), and the epilogue warps promote it: TMEM -> registers, times the block's scale,
+// added into fp32 register accumulators, while the tensor core already works on the next block in the
+// other TMEM accumulator.  Eight epilogue warps share the work: warps 2..5 own columns 0..127 of the
+// tile, warps 6..9 columns 128..255 (one 128-wide scale block of B each), each warp its 32 TMEM lanes.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace gemm {
+
+constexpr int SCALED_EPILOGUE_WARPS = 8;
+constexpr int SCALE_BLOCK = 128;             // K-depth and B-row extent of one scale
+
+// KIND / ELEMENT_FORMAT as in gemm_body.  SCALED = true multiplies every 128-byte K-block by
+// scale_a[row][block] * scale_b[column / 128][block]; SCALED = false only promotes (scale 1): the fp32
+// accumulator of the tensor core truncates after every instruction, so a long K loop drifts towards
+// zero, while sums promoted to registers every K-block are added with round-to-nearest.  The fp32
+// (three-pass TF32) product uses the unscaled form.
+template <int KIND, int ELEMENT_FORMAT, int OUT, bool SCALED, int CTA_GROUP, int STAGES>
+__device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const Params &p) {
+    constexpr int BN = BLOCK_N;
+    using L = SharedLayout<BN, CTA_GROUP, STAGES>;
+    constexpr uint32_t TMEM_COLUMNS = 2 * BN;
+    constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, BN);   // f32 accumulate
+    constexpr int ELEMENT_BYTES = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
+    constexpr int BLOCK_K = ROW_BYTES / ELEMENT_BYTES;   // elements of K per stage (128 for FP8: one scale block)
+
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (ptx::smem_u32(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - ptx::smem_u32(raw_shared));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(aligned + L::TMEM_SLOT_OFFSET);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(aligned + L::ABORT_OFFSET);
+
+    auto stage_a = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES; };
+    auto stage_b = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES; };
+    auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
+    auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
+    auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 2 + a) * 8; };
+
+    const int warp = threadIdx.x / 32;
+    const uint32_t lane = ptx::lane_id();
+    const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int cluster_count = gridDim.x / CTA_GROUP;
+    const int tile_count = p.tiles_m * p.tiles_n;
+    const int k_blocks = (p.k + BLOCK_K - 1) / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            ptx::mbarrier_init(full_bar(s), 1);
+            ptx::mbarrier_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            ptx::mbarrier_init(acc_full_bar(a), 1);
+            ptx::mbarrier_init(acc_empty_bar(a), SCALED_EPILOGUE_WARPS * CTA_GROUP);
+        }
+        ptx::fence_mbarrier_init();
+        ptx::prefetch_tensor_map(map_a);
+        ptx::prefetch_tensor_map(map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+        ptx::tmem_relinquish<CTA_GROUP>();
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer (as in the dense kernel)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                int tile_m, tile_n;
+                tile_position(tile, p, tile_m, tile_n);
+                const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
+                const int row_b = tile_n * BN + int(cta_rank) * L::B_ROWS;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+                        ptx::tma_load_2d(stage_a(stage), map_a, kb * BLOCK_K, row_a, full_bar(stage));
+                        ptx::tma_load_2d(stage_b(stage), map_b, kb * BLOCK_K, row_b, full_bar(stage));
+                    } else {
+                        if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+                        const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
+                        ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * BLOCK_K, row_a, leader_bar);
+                        ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * BLOCK_K, row_b, leader_bar);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            for (int s = 0; s < STAGES && ok; s++) {
+                ok = ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer: one accumulator per K-block
+        if (lane == 0 && leader) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag) ||
+                        !ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
+                        report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after();
+                    const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
+                    const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
+                    const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
+#pragma unroll
+                    for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
+                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
+                                                                     b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(j != 0));
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::tcgen05_commit(empty_bar(stage));
+                        ptx::tcgen05_commit(acc_full_bar(acc));
+                    } else {
+                        ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
+                        ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ promotion + epilogue
+        const int epilogue_warp = warp - 2;
+        const int quadrant = warp % 4;             // TMEM lanes this warp may read
+        const int half = epilogue_warp / 4;        // which 128 columns of the tile
+        const int scale_pitch = k_blocks;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            int tile_m, tile_n;
+            tile_position(tile, p, tile_m, tile_n);
+            const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
+            const int column = tile_n * BN + half * SCALE_BLOCK;
+            const float *row_scales = SCALED ? p.scale_a + size_t(min(row, p.m - 1)) * scale_pitch : nullptr;
+            const float *block_scales = SCALED ? p.scale_b + size_t(min(column, p.n - 1) / SCALE_BLOCK) * scale_pitch : nullptr;
+            float sums[SCALE_BLOCK];
+#pragma unroll
+            for (int i = 0; i < SCALE_BLOCK; i++) sums[i] = 0.0f;
+            float scale = SCALED ? __ldg(row_scales) * __ldg(block_scales) : 1.0f;
+            for (int kb = 0; kb < k_blocks; kb++) {
+                // fetch the next block's scale while waiting for this block's products
+                const int next = min(kb + 1, k_blocks - 1);
+                const float next_scale = SCALED ? __ldg(row_scales + next) * __ldg(block_scales + next) : 1.0f;
+                const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
+                if (!__all_sync(0xffffffffu, ready)) {
+                    if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, kb);
+                    ok = false;
+                    break;
+                }
+                ptx::tcgen05_fence_after();
+                const uint32_t address = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN + uint32_t(half * SCALE_BLOCK);
+#pragma unroll
+                for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
+                    uint32_t values[32];
+                    ptx::tmem_load_32x32(address + uint32_t(chunk * 32), values);
+                    ptx::tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        sums[chunk * 32 + i] = SCALED ? fmaf(__uint_as_float(values[i]), scale, sums[chunk * 32 + i])
+                                                      : sums[chunk * 32 + i] + __uint_as_float(values[i]);
+                }
+                ptx::tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                    else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                scale = next_scale;
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
+                uint32_t values[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) values[i] = __float_as_uint(sums[chunk * 32 + i]);
+                store_chunk<OUT>(p, values, row, column + chunk * 32);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncwarp();
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0 && threadIdx.x == 0) {
+        const unsigned long long start = ptx::global_timer();
+        while (ptx::global_timer() - start < 2000000ull) __nanosleep(1000);
+    }
+    __syncwarp();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc<CTA_GROUP>(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+}  // namespace gemm

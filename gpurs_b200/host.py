@@ -277,6 +277,8 @@ class MatmulOptions:
     ldc: int = 0
     algorithm: int = _ffi.ALGO_AUTO
     max_ctas: int = 0
+    precision: int = _ffi.PRECISION_DEFAULT
+    raster_rows: int = 0
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
     extra: dict = field(default_factory=dict)
@@ -301,6 +303,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.lda, desc.ldb, desc.ldc = options.lda, options.ldb, options.ldc
     desc.a_len, desc.b_len, desc.c_len = a.len, b.len, c.len
     desc.algorithm, desc.max_ctas = options.algorithm, options.max_ctas
+    desc.precision, desc.raster_rows = options.precision, options.raster_rows
     desc.scale_a = options.scale_a.pointer if options.scale_a else 0
     desc.scale_b = options.scale_b.pointer if options.scale_b else 0
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))

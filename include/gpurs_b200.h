@@ -155,6 +155,13 @@ enum {
     GPURS_ALGO_CTA_PAIR = 2     /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
 };
 
+/* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */
+enum {
+    GPURS_PRECISION_DEFAULT = 0, /* fp32 operands: three TF32 passes over a hi/lo split, about 2^-21 relative */
+    GPURS_PRECISION_TF32 = 1     /* fp32 operands: one TF32 pass, what the reference's `f32` tensor element
+                                    does (crates/gpurs/src/gpu/tensor/element.rs:75-110); about 2^-11 relative */
+};
+
 /* C[m, n] = sum_k A[m, k] * B[n, k]: A is m x k, B is n x k ("right_transposed",
  * examples/blackwell/examples/blackwell_matrix.rs:35,64), C is m x n, all row-major.  A zeroed
  * descriptor with the three types and m, n, k set describes the dense contiguous case. */
@@ -166,6 +173,8 @@ typedef struct gpurs_matmul_desc {
     uint64_t a_len, b_len, c_len;    /* slice lengths in elements for the bounds check; 0 = not checked */
     int32_t algorithm;               /* GPURS_ALGO_* */
     int32_t max_ctas;                /* upper bound on resident CTAs (0 = one per multiprocessor) */
+    int32_t precision;               /* GPURS_PRECISION_* (fp32 operands only) */
+    int32_t raster_rows;             /* tile rows walked together for L2 reuse (0 = library default) */
     gpurs_device_ptr scale_a;        /* GPURS_E4M3 block-scaled: fp32 [m][ceil(k/128)], else 0 */
     gpurs_device_ptr scale_b;        /* GPURS_E4M3 block-scaled: fp32 [ceil(n/128)][ceil(k/128)], else 0 */
 } gpurs_matmul_desc;

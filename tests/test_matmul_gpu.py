@@ -18,7 +18,6 @@ FLOAT_CASES = [
     ("bf16", "bf16", 1e-2),  # the tolerance the bf16 configuration states
     ("e4m3", "f32", 1e-3),
     ("e4m3", "bf16", 1e-2),
-    ("f32", "f32", 2e-2),    # one TF32 pass, as the reference's f32 tensor element (element.rs:75-110)
 ]
 SMALL_SHAPES = [(128, 256, 64), (1, 8, 16), (200, 300, 144), (384, 768, 1024), (129, 257, 4096), (640, 512, 80)]
 
@@ -32,6 +31,67 @@ def test_float_product_matches_oracle(gpu, stream, kind, out, tolerance, shape, 
     got = decode_output(run_matmul(gpu, stream, kind, out, a, b, m, n, k, algorithm), out).reshape(m, n)
     expected = O.matmul_rows(KINDS[kind][1], a, b, n, k, np.arange(m))
     assert relative_error(got, expected) <= tolerance
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("shape", SMALL_SHAPES + [(1024, 1024, 1024)])
+def test_f32_product_meets_1e_4(gpu, stream, shape, algorithm):
+    """fp32 operands, uniform[-1, 1): the default precision (three TF32 passes over a hi/lo split) stays
+    within 1e-4 of the fp64 loop; (1024, 1024, 1024) is the f32 configuration."""
+    m, n, k = shape
+    a, b = make_operands("f32", m, n, k)
+    got = run_matmul(gpu, stream, "f32", "f32", a, b, m, n, k, algorithm).reshape(m, n).astype(np.float64)
+    assert relative_error(got, O.matmul_rows(O.FMT_F32, a, b, n, k, np.arange(m))) <= 1e-4
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+def test_f32_single_tf32_pass(gpu, stream, algorithm):
+    """One TF32 pass is what the reference's `f32` tensor element computes (element.rs:75-110): inputs keep
+    10 mantissa bits, so the bound is loose and grows with K."""
+    m, n, k = 384, 768, 1024
+    a, b = make_operands("f32", m, n, k)
+    got = run_matmul(gpu, stream, "f32", "f32", a, b, m, n, k, algorithm, precision=G.PRECISION_TF32).reshape(m, n).astype(np.float64)
+    expected = O.matmul_rows(O.FMT_F32, a, b, n, k, np.arange(m))
+    error = relative_error(got, expected)
+    assert 1e-5 < error <= 2e-2   # visibly TF32, not fp32
+
+
+def scaled_operands(m, n, k, seed=1):
+    a_source, b_source = O.fill_normal_f32(m * k, seed), O.fill_normal_f32(n * k, seed + 1)
+    a_codes, a_scales = O.quantize_e4m3(a_source, m, k, 1)
+    b_codes, b_scales = O.quantize_e4m3(b_source, n, k, 128)
+    return a_codes, a_scales, b_codes, b_scales
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("out,tolerance", [("f32", 1e-4), ("bf16", 2e-2)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (200, 300, 400), (384, 768, 1024), (129, 257, 2048), (640, 512, 144)])
+def test_block_scaled_fp8_matches_dequantised_product(gpu, stream, shape, out, tolerance, algorithm):
+    """E4M3 operands with fp32 scales per 1 x 128 (A) and 128 x 128 (B) block against the fp64 product of
+    the dequantised operands; 2e-2 is the tolerance the FP8 configuration states for bf16 output."""
+    m, n, k = shape
+    a, sa, b, sb = scaled_operands(m, n, k)
+    scale_a, scale_b = gpu.upload(sa), gpu.upload(sb)
+    bits = run_matmul(gpu, stream, "e4m3", out, a, b, m, n, k, algorithm, scale_a=scale_a, scale_b=scale_b)
+    got = decode_output(bits, out).reshape(m, n)
+    expected = O.matmul_rows(O.FMT_E4M3, a, b, n, k, np.arange(m), sa, sb)
+    assert relative_error(got, expected) <= tolerance
+
+
+def test_block_scaled_fp8_configuration(gpu, stream):
+    """M=4096, N=7168, K=7168, bf16 out, tolerance 2e-2 against the dequantised fp64 product."""
+    m, n, k = 4096, 7168, 7168
+    a, sa, b, sb = scaled_operands(m, n, k)
+    scale_a, scale_b = gpu.upload(sa), gpu.upload(sb)
+    got = decode_output(run_matmul(gpu, stream, "e4m3", "bf16", a, b, m, n, k, scale_a=scale_a, scale_b=scale_b), "bf16")
+    indices = O.reference_sample_indices(m, n)
+    assert relative_error(got[indices], O.matmul_samples(O.FMT_E4M3, a, b, n, k, indices, sa, sb)) <= 2e-2
+    rows = spread_rows(m, 16)
+    assert relative_error(got.reshape(m, n)[rows], O.matmul_rows(O.FMT_E4M3, a, b, n, k, rows, sa, sb)) <= 2e-2
+    # scaling every A scale by 2 doubles the product exactly
+    doubled = gpu.upload(sa * np.float32(2.0))
+    again = decode_output(run_matmul(gpu, stream, "e4m3", "bf16", a, b, m, n, k, scale_a=doubled, scale_b=scale_b), "bf16")
+    assert np.array_equal(again, 2.0 * got)
 
 
 @pytest.mark.parametrize("algorithm", ALGORITHMS)
