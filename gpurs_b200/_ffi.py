@@ -27,6 +27,7 @@ E_DRIVER_UNAVAILABLE = 100011
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
 ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR = 0, 1, 2
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
+STATIC_SCRATCH_BYTES = 32 << 20
 
 
 class LaunchConfigStruct(C.Structure):
@@ -81,6 +82,7 @@ SIGNATURES = {
     "gpurs_kernel_launch": (C.c_int, [_P, _P, C.POINTER(LaunchConfigStruct), _PP]),
     "gpurs_kernel_image": (_P, [C.POINTER(C.c_size_t)]),
     "gpurs_matmul": (C.c_int, [_P, C.POINTER(MatmulDesc), C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),
     "gpurs_last_error": (C.c_int, [C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), C.POINTER(C.c_char_p)]),

@@ -44,7 +44,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     kernels = sorted((CSRC / "kernels").glob("*.cu"))
     kernel_deps = kernels + sorted((CSRC / "kernels").glob("*.cuh")) + sorted((CSRC / "kernels").glob("*.hpp"))
     host = sorted((CSRC / "host").glob("*.cpp"))
-    host_deps = host + sorted((CSRC / "host").glob("*.hpp")) + [CSRC / "host" / "image.S", PACKAGE.parent / "include" / "gpurs_b200.h"]
+    host_cuda = sorted((CSRC / "host").glob("*.cu"))   # host code that needs the CUDA runtime (static device data)
+    host_deps = host + host_cuda + sorted((CSRC / "kernels").glob("*.hpp")) + sorted((CSRC / "host").glob("*.hpp")) + [CSRC / "host" / "image.S", PACKAGE.parent / "include" / "gpurs_b200.h"]
     log: list[str] = []
     nvcc = str(CUDA_HOME / "bin" / "nvcc")
     if force or not IMAGE.exists() or IMAGE.stat().st_mtime < _newest(kernel_deps):
@@ -59,10 +60,20 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         (scratch / "ptxas.log").write_text(log[-1])
         del objects
     if force or not LIBRARY.exists() or LIBRARY.stat().st_mtime < max(_newest(host_deps), IMAGE.stat().st_mtime):
+        scratch = PACKAGE / "build"
+        scratch.mkdir(exist_ok=True)
+        objects = []
+        for source in host_cuda:
+            target = scratch / (source.stem + ".o")
+            _run([nvcc, *NVCC_FLAGS, "-Xcompiler", "-fPIC,-fvisibility=hidden", "-c", str(source), "-o", str(target)], log)
+            objects.append(str(target))
         _run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-Wextra",
               "-I", str(CUDA_HOME / "include"), f'-DGPURS_IMAGE_PATH="{IMAGE}"',
-              *[str(h) for h in host], str(CSRC / "host" / "image.S"),
-              "-o", str(LIBRARY), "-ldl", "-lpthread"], log)
+              *[str(h) for h in host], str(CSRC / "host" / "image.S"), *objects,
+              "-o", str(LIBRARY), "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread",
+              # keep the statically linked CUDA runtime private to this library: another copy (torch's) may
+              # live in the same process
+              "-Wl,--exclude-libs,ALL", "-Wl,-Bsymbolic"], log)
     if verbose:
         print("\n".join(log))
     return LIBRARY

@@ -1,0 +1,23 @@
+// The validated description of one tcgen05 GEMM launch and the function that enqueues it (matmul.cpp).
+#pragma once
+#include "../kernels/gemm_params.hpp"
+#include "runtime.hpp"
+
+namespace launcher {
+
+// One launch of a tcgen05 GEMM entry: everything the kernel needs, already validated.
+struct Gemm {
+    const char *stem;
+    int element_type, element_bytes, output_bytes;
+    gpurs_device_ptr a, b, c;
+    uint64_t lda, ldb, ldc, m, n, k;
+    int cta_group, raster_rows, max_ctas;
+    gpurs_device_ptr scale_a = 0, scale_b = 0;   // block-scaled E4M3 only
+    int threads = gemm::NUM_THREADS;
+};
+
+// Encodes the operand descriptors, picks the geometry and enqueues the kernel on `stream`.  The
+// caller has made the gpu's context current.
+int launch_gemm(gpurs_stream *stream, const Gemm &g);
+
+}  // namespace launcher

@@ -2,8 +2,7 @@
 // the reference's `#[gpu]` macro generates for a kernel (crates/macros/src/launcher.rs:110-223) plus the
 // example's own set-up (examples/blackwell/examples/blackwell_matrix.rs:58-83): check the arguments,
 // describe A and B to the TMA unit, pick the launch geometry and enqueue one kernel.
-#include "../kernels/gemm_params.hpp"
-#include "runtime.hpp"
+#include "gemm_launch.hpp"
 
 #include <algorithm>
 #include <cstdio>
@@ -38,18 +37,11 @@ bool choose(int a_type, int c_type, Choice &choice) {
 // Half-open byte ranges [begin, end) overlap?
 bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { return a < b + b_bytes && b < a + a_bytes; }
 
-// One launch of a tcgen05 GEMM entry: everything the kernel needs, already validated.
-struct Gemm {
-    const char *stem;
-    int element_type, element_bytes, output_bytes;
-    gpurs_device_ptr a, b, c;
-    uint64_t lda, ldb, ldc, m, n, k;
-    int cta_group, raster_rows, max_ctas;
-    gpurs_device_ptr scale_a = 0, scale_b = 0;   // block-scaled E4M3 only
-    int threads = gemm::NUM_THREADS;
-};
+}  // namespace
 
-int launch_gemm(gpurs_stream *stream, const Gemm &g) {
+using launcher::Gemm;
+
+int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     gpurs_gpu *gpu = stream->gpu;
     const int cta_group = g.cta_group;
     const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
@@ -108,6 +100,10 @@ int launch_gemm(gpurs_stream *stream, const Gemm &g) {
     void *arguments[3] = {&map_a, &map_b, &params};
     return runtime::launch(kernel, stream, &config, arguments);
 }
+
+namespace {
+
+using launcher::launch_gemm;
 
 // Enqueues the hi/lo split of a rows x k fp32 matrix into a rows x 3k one (kernels/transform.cu).
 int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t rows, uint64_t k, int order) {

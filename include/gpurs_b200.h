@@ -187,6 +187,22 @@ typedef struct gpurs_matmul_desc {
 int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
                  gpurs_device_ptr c);
 
+/* Size of the fixed device array behind gpurs_matmul_f32_static.  Every GPU that loads this library
+ * holds this much memory for it until the process exits. */
+#define GPURS_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* No counterpart in the reference.  The fp32 product C[m, n] = sum_k A[m, k] * B[n, k] (contiguous
+ * row-major fp32 A m x k, B n x k, C m x n; same arithmetic as gpurs_matmul with GPURS_F32 operands and
+ * GPURS_PRECISION_DEFAULT) for hosts that must not allocate device memory when they call: ones whose
+ * whole device is owned by their own pool, and ones that cannot take the device-wide synchronisation an
+ * allocation or a free implies.  The scratch for the split operands is a fixed array inside the library
+ * image instead of an allocation, so (m + n) * 3 * k * 4 bytes (the A part rounded up to 256) must fit
+ * GPURS_STATIC_SCRATCH_BYTES, else GPURS_E_SIZE_OVERFLOW.  All calls on a device share that array: calls
+ * ordered by one stream are safe, calls that may overlap on the GPU race.  The first call on a device
+ * resolves the array's address and loads the kernels; make it before starting any stream capture. */
+int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_t n, uint64_t k, gpurs_device_ptr a,
+                            gpurs_device_ptr b, gpurs_device_ptr c);
+
 /* Reads and clears the device status word: [0] code (0 = none), [1] block, [2] tile, [3] K-block of the
  * first bounded wait that gave up.  Synchronises the device. */
 int gpurs_status_read(gpurs_gpu *gpu, uint32_t status[4]);
