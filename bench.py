@@ -50,7 +50,7 @@ DEFAULT_WORKLOAD = "bf16_8192"
 
 # DRAM bytes moved by one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
 # an ncu capture, see profiles/); None until a capture of that workload has been taken.
-MEASURED_TRAFFIC = {}
+MEASURED_TRAFFIC = {"bf16_8192": 1_213_700_000}   # profiles/gemm_bf16_bf16_cg2_8192.md: 1.0859 GB read + 127.9 MB written
 
 
 def bf16_bits(values: np.ndarray) -> np.ndarray:
@@ -185,6 +185,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     import gpurs_b200 as G
 
     kind, out, m, n, k = WORKLOADS[args.workload]
+    if args.scaling == "strong":
+        from gpurs_b200.sharding import row_shard
+
+        m = row_shard(m, world, rank)[1]     # the workload's M split over the ranks, B still replicated
     element = {"bf16": G.BF16, "f16": G.F16, "i8": G.I8, "e4m3": G.E4M3, "f32": G.F32}[kind]
     out_element = {"bf16": G.BF16, "f32": G.F32, "i32": G.I32}[out]
     element_bytes, out_bytes = G.host.ELEMENT_BYTES[element], G.host.ELEMENT_BYTES[out_element]
@@ -279,6 +283,39 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     checksum = int(np.frombuffer(C.string_at(pinned[2], 64), np.uint8).sum())  # the result really arrived on the host
     for pointer in pinned:
         lib.gpurs_host_free(gpu._handle, pointer)
+
+    # ---- optional: GEMM followed by the all-gather of the C blocks (NCCL), reported beside `value` ----
+    gather = None
+    if dist is not None and args.allgather:
+        import torch
+
+        shard_bytes = m * n * out_bytes
+        full = torch.empty(world * shard_bytes, dtype=torch.uint8, device="cuda")
+        mine = full[rank * shard_bytes:(rank + 1) * shard_bytes]
+        c_block = gpu.import_allocation(full.data_ptr() + rank * shard_bytes, m * n, out_element)
+        torch_stream = torch.cuda.current_stream()
+        borrowed = gpu.borrow_stream(torch_stream.cuda_stream)
+
+        def gather_step():
+            G.matmul(borrowed, a, b, c_block, shape, options)
+            dist.all_gather_into_tensor(full, mine)      # in place: block r of `full` is rank r's C
+
+        for _ in range(3):
+            gather_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(torch_stream)
+        for _ in range(args.steps):
+            gather_step()
+        finish.record(torch_stream)
+        torch.cuda.synchronize()
+        worst = torch.tensor([begin.elapsed_time(finish)], device="cuda")
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        gather_ms = float(worst.item()) / args.steps
+        gather = {"ms_per_step": gather_ms, "value": world * flops_per_step / (gather_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                  "bytes_received_per_gpu": int((world - 1) * shard_bytes), "collective": "ncclAllGather, in place, after the GEMM on the same stream"}
+        del c_block, borrowed
     status = gpu.status()
 
     if rank == 0:
@@ -289,7 +326,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
             peak, peak_source = peak / 2.0, peak_source + " /2 for TF32 operands"
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": kind, "data": "synthetic",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": kind, "data": "synthetic",
             "config": {"workload": args.workload, "m_per_gpu": m, "global_m": m * world, "n": n, "k": k, "output": out,
                        "operands": "A m x k and B n x k, both K-major (the reference's convention)", "parallelism": f"M-sharded x{world}, B replicated, no collective",
                        "l2": "inputs (A+B+C = %d MB per GPU) larger than the 126 MB L2; no flush" % ((a_host.nbytes + b_host.nbytes + m * n * out_bytes) >> 20),
@@ -305,6 +342,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
                          "algorithmic_bytes_per_launch": int(a_host.nbytes + b_host.nbytes + m * n * out_bytes)},
             "device_status": status,
         }
+        if gather is not None:
+            line["allgather"] = gather
         if world == 1 and not args.no_cpu_baseline:
             rows = 4096
             seconds, flops, threads = cpu_band(kind, n, k, rows)
@@ -327,6 +366,9 @@ def main() -> None:
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--algorithm", type=int, default=0, help="0 auto, 1 single-CTA tiles, 2 CTA-pair tiles")
     parser.add_argument("--raster-rows", type=int, default=0, help="tile rows walked together (0 = library default)")
+    parser.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                        help="weak: every GPU multiplies a full-size shard (global M grows); strong: the workload's M is split")
+    parser.add_argument("--allgather", action="store_true", help="also time GEMM + NCCL all-gather of C (N > 1)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
