@@ -45,6 +45,7 @@ WORKLOADS = {
     "e4m3_unscaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),
     "e4m3_scaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),   # fp32 scales per 1x128 / 128x128 block
     "f32_1024": ("f32", "f32", 1024, 1024, 1024),
+    "sparse24_bf16_2048x8192x8192": ("bf16", "bf16", 2048, 8192, 8192),   # one GPU's shard of 16384 x 8192 (2:4) x 8192
 }
 DEFAULT_WORKLOAD = "bf16_8192"
 
@@ -210,6 +211,20 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     c = gpu.allocate(out_element, m * n)
     shape = [m, n, k]
     options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows)
+    if args.workload.startswith("sparse24"):
+        # A becomes 2:4: zero two elements of every group of four (seeded choice), then compress on the device
+        rng = np.random.default_rng(5 + rank)
+        pairs = np.array([[0, 1], [0, 2], [0, 3], [1, 2], [1, 3], [2, 3]])[rng.integers(0, 6, m * k // 4)]
+        groups = a_host.reshape(-1, 4).copy()
+        keep = np.zeros(groups.shape, bool)
+        keep[np.arange(len(groups))[:, None], pairs] = True
+        groups[~keep] = 0
+        dense = gpu.upload(groups.reshape(-1), element)
+        a, options.metadata, violations = G.compress_24(stream, dense, m, k)
+        stream.synchronize()
+        assert violations.download()[0] == 0
+        del dense
+        a_host = a.download()     # the end-to-end leg copies the compressed operand (its metadata stays resident)
     if "scaled" in args.workload and "unscaled" not in args.workload:
         # synthetic scales with the magnitude absmax/448 has for N(0,1) blocks
         rng = np.random.default_rng(99)

@@ -41,7 +41,7 @@ class MatmulDesc(C.Structure):
         ("lda", C.c_uint64), ("ldb", C.c_uint64), ("ldc", C.c_uint64),
         ("a_len", C.c_uint64), ("b_len", C.c_uint64), ("c_len", C.c_uint64),
         ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
-        ("scale_a", C.c_uint64), ("scale_b", C.c_uint64),
+        ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
     ]
 
 
@@ -82,6 +82,8 @@ SIGNATURES = {
     "gpurs_kernel_launch": (C.c_int, [_P, _P, C.POINTER(LaunchConfigStruct), _PP]),
     "gpurs_kernel_image": (_P, [C.POINTER(C.c_size_t)]),
     "gpurs_matmul": (C.c_int, [_P, C.POINTER(MatmulDesc), C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_metadata_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64]),
+    "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),

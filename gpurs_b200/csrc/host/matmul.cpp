@@ -47,8 +47,10 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
     char name[96];
     std::snprintf(name, sizeof name, "%s_cg%d", g.stem, cta_group);
-    const uint32_t shared_bytes = cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
-                                                 : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
+    const bool sparse = g.metadata != 0;
+    const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
+                                  : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
+                                                   : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
     gpurs_kernel *kernel = nullptr;
     int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
@@ -57,14 +59,25 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     // zero, the same form the reference encodes (crates/driver/src/memory.rs:325-354) with boxes of
     // 128 rows of A and 256 (or, per CTA of a pair, 128) rows of B.
     const uint32_t block_k = uint32_t(gemm::ROW_BYTES / g.element_bytes);
-    alignas(64) CUtensorMap map_a, map_b;
-    const uint64_t dims_a[2] = {g.k, g.m}, dims_b[2] = {g.k, g.n};
+    alignas(64) CUtensorMap map_a, map_b, map_e;
+    // A sparse A is stored as its kept half: k/2 values per row.
+    const uint64_t dims_a[2] = {sparse ? g.k / 2 : g.k, g.m}, dims_b[2] = {g.k, g.n};
     const uint64_t stride_a[1] = {g.lda * eb}, stride_b[1] = {g.ldb * eb};
     const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)}, box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
     result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 2, g.a, dims_a, stride_a, box_a, 3, 3);
     if (result != GPURS_OK) return result;
     result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 2, g.b, dims_b, stride_b, box_b, 3, 3);
     if (result != GPURS_OK) return result;
+
+    if (sparse) {
+        // The metadata as rows of 16 bytes, 128 rows per block, no swizzle: block (row block, K block) starts at
+        // row (row_block * k_blocks + k_block) * 128.
+        const uint64_t blocks = ((g.m + 127) / 128) * ((g.k + gemm::SPARSE_BLOCK_K - 1) / gemm::SPARSE_BLOCK_K);
+        const uint64_t dims_e[2] = {16, blocks * 128}, stride_e[1] = {16};
+        const uint32_t box_e[2] = {16, 128};
+        result = gpurs_tensor_map_encode(gpu, &map_e, GPURS_I8, 2, g.metadata, dims_e, stride_e, box_e, 0, 3);
+        if (result != GPURS_OK) return result;
+    }
 
     gemm::Params params;
     std::memset(&params, 0, sizeof params);
@@ -98,7 +111,8 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     config.cluster[0] = uint32_t(cta_group);
     config.cluster[1] = config.cluster[2] = 1;
     void *arguments[3] = {&map_a, &map_b, &params};
-    return runtime::launch(kernel, stream, &config, arguments);
+    void *sparse_arguments[4] = {&map_a, &map_b, &map_e, &params};
+    return runtime::launch(kernel, stream, &config, sparse ? sparse_arguments : arguments);
 }
 
 namespace {
@@ -139,10 +153,18 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     const uint64_t m = desc->m, n = desc->n, k = desc->k;
     if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
         return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
-    const uint64_t lda = desc->lda ? desc->lda : k, ldb = desc->ldb ? desc->ldb : k, ldc = desc->ldc ? desc->ldc : n;
-    if (lda < k || ldb < k || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    const bool sparse = desc->metadata != 0;
+    if (sparse && desc->a_type != GPURS_F16 && desc->a_type != GPURS_BF16)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "2:4-sparse A is supported for 16-bit operands");
+    if (sparse && (desc->a_type == GPURS_F16) && desc->c_type != GPURS_F32)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
+    if (sparse && k % 128) return fail(op, GPURS_E_INVALID_VIEW, "the depth of a 2:4-sparse product must be a multiple of 128");
+    if (sparse && desc->metadata % 16) return fail(op, GPURS_E_INVALID_VIEW, "the metadata must be 16-byte aligned");
+    const uint64_t a_columns = sparse ? k / 2 : k;   // stored elements per row of A
+    const uint64_t lda = desc->lda ? desc->lda : a_columns, ldb = desc->ldb ? desc->ldb : k, ldc = desc->ldc ? desc->ldc : n;
+    if (lda < a_columns || ldb < k || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
     // Extent of each operand in elements: the last row ends at (rows - 1) * pitch + columns.
-    const uint64_t a_extent = m ? (m - 1) * lda + k : 0, b_extent = n ? (n - 1) * ldb + k : 0, c_extent = m ? (m - 1) * ldc + n : 0;
+    const uint64_t a_extent = m ? (m - 1) * lda + a_columns : 0, b_extent = n ? (n - 1) * ldb + k : 0, c_extent = m ? (m - 1) * ldc + n : 0;
     if ((desc->a_len && desc->a_len < a_extent) || (desc->b_len && desc->b_len < b_extent) || (desc->c_len && desc->c_len < c_extent))
         return fail(op, GPURS_E_LENGTH_MISMATCH, "a slice is shorter than the matrix it is said to hold");
     if (m == 0 || n == 0) return GPURS_OK;
@@ -190,6 +212,12 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.cta_group = group == GPURS_ALGO_CTA_PAIR ? 2 : 1;
     gemm.raster_rows = desc->raster_rows;
     gemm.max_ctas = desc->max_ctas;
+    if (sparse) {
+        if (desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "a sparse product takes no scales");
+        gemm.stem = desc->a_type == GPURS_F16 ? "gpurs_gemm_sparse_f16_f32"
+                    : desc->c_type == GPURS_BF16 ? "gpurs_gemm_sparse_bf16_bf16" : "gpurs_gemm_sparse_bf16_f32";
+        gemm.metadata = desc->metadata;
+    }
     if (desc->scale_a) {
         // per-K-block promotion kernel: fp32 scales [m][ceil(k/128)] and [ceil(n/128)][ceil(k/128)]
         gemm.stem = desc->c_type == GPURS_BF16 ? "gpurs_gemm_e4m3_scaled_bf16" : "gpurs_gemm_e4m3_scaled_f32";
@@ -220,4 +248,42 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
         return result != GPURS_OK ? result : released;
     }
     return launch_gemm(stream, gemm);
+}
+
+extern "C" size_t gpurs_metadata_bytes(uint64_t m, uint64_t k) {
+    return size_t(((m + 127) / 128) * ((k + gemm::SPARSE_BLOCK_K - 1) / gemm::SPARSE_BLOCK_K) * gemm::SPARSE_METADATA_BLOCK_BYTES);
+}
+
+extern "C" int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_t m, uint64_t k, gpurs_device_ptr dense, uint64_t ld,
+                                 gpurs_device_ptr values, gpurs_device_ptr metadata, gpurs_device_ptr violations) {
+    const char *const op = "gpurs_compress_24";
+    if (!stream) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream");
+    if (element_type != GPURS_F16 && element_type != GPURS_BF16) return fail(op, GPURS_E_INVALID_ARGUMENT, "16-bit element types only");
+    if (m > 0x7fffffffull || k > 0x7fffffffull) return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
+    if (m == 0 || k == 0) return GPURS_OK;
+    if (k % 128) return fail(op, GPURS_E_INVALID_VIEW, "the depth must be a multiple of 128");
+    const uint64_t pitch = ld ? ld : k;
+    if (pitch < k) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (!dense || !values || !metadata) return fail(op, GPURS_E_INVALID_ARGUMENT, "null argument");
+    if (dense % 16 || (pitch * 2) % 16 || values % 16 || metadata % 16 || violations % 4)
+        return fail(op, GPURS_E_INVALID_VIEW, "buffers and the row pitch must be multiples of 16 bytes");
+    if (overlap(values, m * k, dense, ((m - 1) * pitch + k) * 2) || overlap(metadata, gpurs_metadata_bytes(m, k), dense, ((m - 1) * pitch + k) * 2))
+        return fail(op, GPURS_E_ALIASING, "an output overlaps the input");
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_compress_24", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t spans = m * (k / 16);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>((spans + 255) / 256, uint64_t(gpu->multiprocessors) * 8)));
+    config.block[0] = 256;
+    const void *source = reinterpret_cast<const void *>(dense);
+    void *value_pointer = reinterpret_cast<void *>(values), *metadata_pointer = reinterpret_cast<void *>(metadata);
+    void *violation_pointer = reinterpret_cast<void *>(violations);
+    long long source_pitch = (long long)pitch;
+    int rows = int(m), depth = int(k);
+    void *arguments[7] = {&source, &source_pitch, &value_pointer, &metadata_pointer, &violation_pointer, &rows, &depth};
+    return runtime::launch(kernel, stream, &config, arguments);
 }

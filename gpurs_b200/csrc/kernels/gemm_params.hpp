@@ -53,4 +53,11 @@ struct SharedLayout {
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;   // slack to align the stages to 1024 bytes
 };
 
+// 2:4 sparse kernels (gemm_sparse_tcgen05.cuh): dynamic shared memory of the one-CTA (2 stages of 82 KiB) and
+// CTA-pair (4 stages of 50 KiB) entries, and the size of one metadata block (128 rows x 128 logical K).
+constexpr int SPARSE_SHARED_SINGLE = 2 * (BLOCK_M * ROW_BYTES + 2 * BLOCK_N * ROW_BYTES + 2048) + (2 * 2 + 2) * 8 + 8 + 1024;
+constexpr int SPARSE_SHARED_PAIR = 4 * (BLOCK_M * ROW_BYTES + BLOCK_N * ROW_BYTES + 2048) + (2 * 4 + 2) * 8 + 8 + 1024;
+constexpr int SPARSE_METADATA_BLOCK_BYTES = 2048;
+constexpr int SPARSE_BLOCK_K = 128;
+
 }  // namespace gemm

@@ -1,0 +1,16 @@
+// Entry points of the 2:4 structured-sparse GEMM (see gemm_sparse_tcgen05.cuh).
+#include "gemm_sparse_tcgen05.cuh"
+
+#define GPURS_SPARSE_KERNEL(NAME, FORMAT, OUT, GROUP, STAGES)                                                         \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                               \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                       \
+         const __grid_constant__ CUtensorMap map_e, const __grid_constant__ gemm::Params params) {                   \
+        gemm::gemm_sparse_body<FORMAT, OUT, GROUP, STAGES>(&map_a, &map_b, &map_e, params);                          \
+    }
+
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_bf16_bf16_cg1, 1, gemm::OUT_BF16, 1, gemm::SPARSE_STAGES_SINGLE)
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_bf16_bf16_cg2, 1, gemm::OUT_BF16, 2, gemm::SPARSE_STAGES_PAIR)
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_bf16_f32_cg1, 1, gemm::OUT_F32, 1, gemm::SPARSE_STAGES_SINGLE)
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_bf16_f32_cg2, 1, gemm::OUT_F32, 2, gemm::SPARSE_STAGES_PAIR)
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_f16_f32_cg1, 0, gemm::OUT_F32, 1, gemm::SPARSE_STAGES_SINGLE)
+GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_f16_f32_cg2, 0, gemm::OUT_F32, 2, gemm::SPARSE_STAGES_PAIR)

@@ -1,0 +1,250 @@
+// 2:4 structured-sparse GEMM for sm_100a (16-bit operands):
+//
+//     C[m, n] = sum_k A[m, k] * B[n, k],     A has at most 2 non-zeros in every aligned group of 4 along K.
+//
+// The reference has nothing for this (no sparse instruction, kernel or test); the definition is the dense
+// product of the densified A.  A arrives compressed: `values` is M x K/2 (the kept pair of every group, in
+// order) and `metadata` holds, per group, the two 2-bit positions of the kept elements (low bits first),
+// arranged in 2048-byte blocks, one per 128 rows x 128 logical K, in the order the tensor core reads them
+// from tensor memory (see metadata_offset below; gpurs_compress_24 in transform.cu produces both).
+//
+// One pipeline stage is 128 logical K: 128 bytes of compressed A per row, two 128-byte-swizzled tiles of B
+// (logical K 0..63 and 64..127) and one metadata block.  The MMA thread copies the block into tensor memory
+// (tcgen05.cp, 4 columns) and issues 4 tcgen05.mma.sp of 32 logical K each, one metadata column apiece.
+// Tensor memory: one 256-column accumulator plus 4 metadata columns per stage.  With a single accumulator
+// the epilogue of a tile is not overlapped with the next tile's main loop (about 2000 of 34000 cycles per
+// tile at K = 8192).
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace gemm {
+
+constexpr int SPARSE_STAGE_K = 128;            // logical K per stage
+constexpr int METADATA_BLOCK_BYTES = 2048;     // 128 rows x 128 logical K x 4 bits per group of 4
+
+// Byte offset, inside its 2048-byte block, of the metadata of logical element (row, k) of a 128 x 128 block,
+// and the nibble within that byte.  Row r = r0 + 8*r1 + 16*r2 (r0 < 8, r1 < 2), k = k0 + 16*k1 + 32*k2
+// (k0 < 16, k1 < 2, k2 < 4):  offset = 16*r0 + 2*r1 + 256*r2 + 128*k1 + 4*k2 + k0/8, nibble = (k0 % 8) / 4.
+// Read as 128 units of 16 bytes, unit u = r0 + 8*k1 + 16*r2 lands in TMEM lane u, and its four 32-bit words are
+// the metadata columns of the stage's four instructions (k2): low half-word row r1 = 0, high half-word r1 = 1.
+__host__ __device__ inline int metadata_offset(int row, int k) {
+    return 16 * (row % 8) + 2 * ((row / 8) % 2) + 256 * (row / 16) + 128 * ((k / 16) % 2) + 4 * (k / 32) + (k % 16) / 8;
+}
+
+template <int CTA_GROUP, int STAGES>
+struct SparseLayout {
+    static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;                   // 128 rows x 64 kept elements
+    static constexpr int B_ROWS = BLOCK_N / CTA_GROUP;
+    static constexpr int B_HALF_BYTES = B_ROWS * ROW_BYTES;               // one 64-deep half of the B tile
+    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_HALF_BYTES + METADATA_BLOCK_BYTES;
+    static constexpr int BARRIER_OFFSET = ((STAGES * STAGE_BYTES + 1023) / 1024) * 1024;
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 2;                   // full, empty, accumulator full / empty
+    static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
+    static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
+    static constexpr int DYNAMIC_BYTES = ABORT_OFFSET + 4 + 1024;
+};
+
+constexpr int SPARSE_STAGES_SINGLE = 2;   // 82 KiB per stage
+constexpr int SPARSE_STAGES_PAIR = 4;     // 50 KiB per stage and CTA
+static_assert(SparseLayout<1, SPARSE_STAGES_SINGLE>::DYNAMIC_BYTES == SPARSE_SHARED_SINGLE, "host and kernel disagree on shared memory");
+static_assert(SparseLayout<2, SPARSE_STAGES_PAIR>::DYNAMIC_BYTES == SPARSE_SHARED_PAIR, "host and kernel disagree on shared memory");
+static_assert(METADATA_BLOCK_BYTES == SPARSE_METADATA_BLOCK_BYTES && SPARSE_STAGE_K == SPARSE_BLOCK_K, "host and kernel disagree on the metadata block");
+
+// ELEMENT_FORMAT: 0 = f16, 1 = bf16.  map_e describes the metadata as rows of 16 bytes (box 16 x 128).
+template <int ELEMENT_FORMAT, int OUT, int CTA_GROUP, int STAGES>
+__device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_e, const Params &p) {
+    using L = SparseLayout<CTA_GROUP, STAGES>;
+    constexpr int BN = BLOCK_N;
+    constexpr uint32_t TMEM_COLUMNS = 512;
+    constexpr uint32_t METADATA_COLUMN = BN;      // metadata of stage s: columns BN + 4*s .. +3
+    // sparse flag (bit 2) on top of the dense descriptor
+    constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, BN) | (1u << 2);
+    static_assert(L::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
+
+    extern __shared__ uint8_t raw_shared[];
+    const uint32_t base = (ptx::smem_u32(raw_shared) + 1023u) & ~1023u;
+    uint8_t *aligned = raw_shared + (base - ptx::smem_u32(raw_shared));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(aligned + L::TMEM_SLOT_OFFSET);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(aligned + L::ABORT_OFFSET);
+
+    auto stage_a = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES; };
+    auto stage_b = [&](int s, int half) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES + uint32_t(half) * L::B_HALF_BYTES; };
+    auto stage_e = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES + 2 * L::B_HALF_BYTES; };
+    auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
+    auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
+    const uint32_t acc_full_bar = base + L::BARRIER_OFFSET + uint32_t(2 * STAGES) * 8;
+    const uint32_t acc_empty_bar = base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 1) * 8;
+
+    const int warp = threadIdx.x / 32;
+    const uint32_t lane = ptx::lane_id();
+    const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int cluster_count = gridDim.x / CTA_GROUP;
+    const int tile_count = p.tiles_m * p.tiles_n;
+    const int k_blocks = (p.k + SPARSE_STAGE_K - 1) / SPARSE_STAGE_K;     // p.k is the logical depth
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; s++) {
+            ptx::mbarrier_init(full_bar(s), 1);
+            ptx::mbarrier_init(empty_bar(s), 1);
+        }
+        ptx::mbarrier_init(acc_full_bar, 1);
+        ptx::mbarrier_init(acc_empty_bar, EPILOGUE_WARPS * CTA_GROUP);
+        ptx::fence_mbarrier_init();
+        ptx::prefetch_tensor_map(map_a);
+        ptx::prefetch_tensor_map(map_b);
+        ptx::prefetch_tensor_map(map_e);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+        ptx::tmem_relinquish<CTA_GROUP>();
+    }
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer: A, two halves of B, metadata
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                int tile_m, tile_n;
+                tile_position(tile, p, tile_m, tile_n);
+                const int row_block = tile_m * CTA_GROUP + int(cta_rank);          // 128-row block of A this CTA owns
+                const int row_a = row_block * BLOCK_M;
+                const int row_b = tile_n * BN + int(cta_rank) * L::B_ROWS;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    const int k_logical = kb * SPARSE_STAGE_K;
+                    const int metadata_row = (row_block * k_blocks + kb) * 128;     // 128 rows of 16 bytes per block
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+                        ptx::tma_load_2d(stage_a(stage), map_a, k_logical / 2, row_a, full_bar(stage));
+                        ptx::tma_load_2d(stage_b(stage, 0), map_b, k_logical, row_b, full_bar(stage));
+                        ptx::tma_load_2d(stage_b(stage, 1), map_b, k_logical + 64, row_b, full_bar(stage));
+                        ptx::tma_load_2d(stage_e(stage), map_e, 0, metadata_row, full_bar(stage));
+                    } else {
+                        if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+                        const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
+                        ptx::tma_load_2d_pair(stage_a(stage), map_a, k_logical / 2, row_a, leader_bar);
+                        ptx::tma_load_2d_pair(stage_b(stage, 0), map_b, k_logical, row_b, leader_bar);
+                        ptx::tma_load_2d_pair(stage_b(stage, 1), map_b, k_logical + 64, row_b, leader_bar);
+                        ptx::tma_load_2d_pair(stage_e(stage), map_e, 0, metadata_row, leader_bar);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            for (int s = 0; s < STAGES && ok; s++) {
+                ok = ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && leader) {
+            int stage = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar, acc_phase ^ 1, abort_flag)) {
+                    report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
+                    break;
+                }
+                ptx::tcgen05_fence_after();
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
+                        report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after();
+                    const uint32_t metadata_tmem = tmem_base + METADATA_COLUMN + uint32_t(stage) * 4;
+                    ptx::tcgen05_copy_128x128b<CTA_GROUP>(metadata_tmem, ptx::smem_descriptor_rows16(stage_e(stage)));
+                    const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // instruction j: 32 logical K = 32 bytes of compressed A, 64 bytes of B (half j / 2, offset j % 2)
+                        const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage, j / 2)) + uint64_t((j % 2) * (64 >> 4));
+                        // The instruction takes the metadata column pair (an even column address) and, in bits 0..1 of
+                        // its descriptor, which column of the pair to use.
+                        const uint32_t column = metadata_tmem + uint32_t(j);
+                        ptx::tcgen05_mma_sparse_f16<CTA_GROUP>(tmem_base, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc,
+                                                               column & ~1u, IDESC | (column & 1u), uint32_t((kb | j) != 0));
+                    }
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar);
+                else ptx::tcgen05_commit_pair(acc_full_bar, 0x3);
+                acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (single accumulator)
+        const int quadrant = warp % 4;
+        uint32_t acc_phase = 0;
+        for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
+            int tile_m, tile_n;
+            tile_position(tile, p, tile_m, tile_n);
+            const bool ready = ptx::mbarrier_wait(acc_full_bar, acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, -1);
+                break;
+            }
+            ptx::tcgen05_fence_after();
+            const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
+            const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; chunk++) {
+                uint32_t values[32];
+                ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
+                ptx::tmem_load_wait();
+                store_chunk<OUT>(p, values, row, tile_n * BN + chunk * 32);
+            }
+            ptx::tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar);
+                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar, 0));
+            }
+            acc_phase ^= 1;
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncwarp();
+    ptx::tcgen05_fence_before();
+    __syncthreads();
+    if (*abort_flag != 0 && threadIdx.x == 0) {
+        const unsigned long long start = ptx::global_timer();
+        while (ptx::global_timer() - start < 2000000ull) __nanosleep(1000);
+    }
+    __syncwarp();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    if (warp == 1) {
+        ptx::tcgen05_fence_after();
+        ptx::tmem_dealloc<CTA_GROUP>(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+}  // namespace gemm

@@ -219,3 +219,37 @@ __device__ __forceinline__ uint64_t smem_descriptor_k_major_sw128(uint32_t addre
 }
 
 }  // namespace ptx
+
+namespace ptx {
+
+// ---- 2:4 structured sparsity ----------------------------------------------------------------------
+
+// Copies 128 rows x 128 bits from shared memory into 4 columns of tensor memory (one row per TMEM lane):
+// the sparsity metadata of four tcgen05.mma.sp instructions.  Ordered with the tcgen05.mma that the same
+// thread issues afterwards.
+template <int CTA_GROUP>
+__device__ __forceinline__ void tcgen05_copy_128x128b(uint32_t tmem_address, uint64_t smem_descriptor) {
+    if constexpr (CTA_GROUP == 1) asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(tmem_address), "l"(smem_descriptor) : "memory");
+    else asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(tmem_address), "l"(smem_descriptor) : "memory");
+}
+
+// Descriptor of 128 rows of 16 bytes stored back to back (no swizzle): groups of eight rows are 128 bytes apart.
+__device__ __forceinline__ uint64_t smem_descriptor_rows16(uint32_t address) {
+    return static_cast<uint64_t>((address & 0x3ffffu) >> 4) | (1ull << 16) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+}
+
+// D[tmem] (+)= A[smem, 2:4 compressed] * B[smem], metadata in tensor memory at `metadata_tmem`.  16-bit kinds.
+template <int CTA_GROUP>
+__device__ __forceinline__ void tcgen05_mma_sparse_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t metadata_tmem,
+                                                       uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CTA_GROUP == 1)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                     "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(metadata_tmem), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                     "tcgen05.mma.sp.cta_group::2.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(metadata_tmem), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+}  // namespace ptx

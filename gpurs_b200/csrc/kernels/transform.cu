@@ -35,3 +35,57 @@ gpurs_split_tf32(const float *__restrict__ source, long long source_pitch, float
         *reinterpret_cast<float4 *>(out + 2ll * k) = order == 0 ? lo : hi;
     }
 }
+
+#include "gemm_sparse_tcgen05.cuh"
+
+// 2:4 compression of a 16-bit matrix (no counterpart in the reference, which has no sparse path).  One
+// thread handles 16 consecutive logical K of one row: 32 bytes in, the 8 kept values (16 bytes) and 16 bits of
+// metadata out.  In every group of four the first two non-zeros are kept; a group with fewer than two
+// non-zeros keeps zeros from its lowest free positions, so the kept positions are distinct and ascending.
+// A group with more than two non-zeros is not 2:4: it is counted in *violations (if given) and loses its
+// later non-zeros.  Metadata goes to the block layout of gemm::metadata_offset.
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_compress_24(const uint16_t *__restrict__ dense, long long pitch, uint16_t *__restrict__ values, uint8_t *__restrict__ metadata,
+                  unsigned int *violations, int rows, int k) {
+    const long long spans_per_row = k / 16;
+    const long long total = (long long)rows * spans_per_row;
+    const int k_blocks = (k + gemm::SPARSE_STAGE_K - 1) / gemm::SPARSE_STAGE_K;
+    unsigned int bad = 0;
+    for (long long index = blockIdx.x * (long long)blockDim.x + threadIdx.x; index < total; index += (long long)gridDim.x * blockDim.x) {
+        const long long row = index / spans_per_row;
+        const int span = int(index - row * spans_per_row);
+        const uint4 *source = reinterpret_cast<const uint4 *>(dense + row * pitch + span * 16);
+        const uint4 lo = source[0], hi = source[1];
+        const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t kept_words[4];
+        uint32_t nibbles = 0;
+#pragma unroll
+        for (int group = 0; group < 4; group++) {
+            const uint16_t v[4] = {uint16_t(words[2 * group]), uint16_t(words[2 * group] >> 16), uint16_t(words[2 * group + 1]),
+                                   uint16_t(words[2 * group + 1] >> 16)};
+            int first = -1, second = -1, nonzero = 0;
+#pragma unroll
+            for (int position = 0; position < 4; position++)
+                if ((v[position] & 0x7fffu) != 0) {
+                    if (nonzero == 0) first = position;
+                    else if (nonzero == 1) second = position;
+                    nonzero++;
+                }
+            bad += nonzero > 2;
+#pragma unroll
+            for (int position = 0; position < 4; position++)
+                if ((v[position] & 0x7fffu) == 0) {
+                    if (first < 0) first = position;
+                    else if (second < 0 && position != first) second = position;
+                }
+            if (first > second) { const int t = first; first = second; second = t; }
+            kept_words[group] = uint32_t(v[first]) | (uint32_t(v[second]) << 16);
+            nibbles |= uint32_t(first | (second << 2)) << (4 * group);
+        }
+        *reinterpret_cast<uint4 *>(values + row * (long long)(k / 2) + span * 8) = make_uint4(kept_words[0], kept_words[1], kept_words[2], kept_words[3]);
+        const long long block = (row / 128) * k_blocks + (span * 16) / gemm::SPARSE_STAGE_K;
+        const int offset = gemm::metadata_offset(int(row % 128), (span * 16) % gemm::SPARSE_STAGE_K);
+        *reinterpret_cast<uint16_t *>(metadata + block * gemm::METADATA_BLOCK_BYTES + offset) = uint16_t(nibbles);
+    }
+    if (violations != nullptr && bad != 0) atomicAdd(violations, bad);
+}

@@ -281,6 +281,7 @@ class MatmulOptions:
     raster_rows: int = 0
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
+    metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
 
@@ -306,7 +307,20 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.precision, desc.raster_rows = options.precision, options.raster_rows
     desc.scale_a = options.scale_a.pointer if options.scale_a else 0
     desc.scale_b = options.scale_b.pointer if options.scale_b else 0
+    desc.metadata = options.metadata.pointer if options.metadata else 0
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
+
+
+def compress_24(stream: Stream, dense: DeviceBuffer, m: int, k: int, ld: int = 0):
+    """2:4 compression of an m x k 16-bit matrix on the device: returns (values, metadata, violations) where
+    `values` is the m x k/2 buffer of kept elements, `metadata` the byte buffer of their positions in the layout
+    the sparse kernels read, and `violations` a one-element I32 buffer counting groups that were not 2:4."""
+    gpu = stream.gpu
+    values = gpu.allocate(dense.element, m * k // 2)
+    metadata = gpu.zeros(I8, gpu._lib.gpurs_metadata_bytes(m, k))
+    violations = gpu.zeros(I32, 1)
+    _check(gpu._lib.gpurs_compress_24(stream._handle, dense.element, m, k, dense.pointer, ld, values.pointer, metadata.pointer, violations.pointer))
+    return values, metadata, violations
 
 
 class GpursErrorLocal(GpursError):

@@ -177,6 +177,9 @@ typedef struct gpurs_matmul_desc {
     int32_t raster_rows;             /* tile rows walked together for L2 reuse (0 = library default) */
     gpurs_device_ptr scale_a;        /* GPURS_E4M3 block-scaled: fp32 [m][ceil(k/128)], else 0 */
     gpurs_device_ptr scale_b;        /* GPURS_E4M3 block-scaled: fp32 [ceil(n/128)][ceil(k/128)], else 0 */
+    gpurs_device_ptr metadata;       /* 2:4-sparse A (GPURS_F16 / GPURS_BF16): the metadata from gpurs_compress_24; then `a`
+                                        is the m x k/2 array of kept values, k stays the logical depth (a multiple of
+                                        128), lda counts kept values (0 = k/2).  0 = dense A */
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
@@ -186,6 +189,18 @@ typedef struct gpurs_matmul_desc {
  * It does not wait. */
 int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
                  gpurs_device_ptr c);
+
+/* ---- 2:4 structured sparsity (no counterpart in the reference, which has no sparse path) ---------- */
+
+/* Bytes of metadata gpurs_compress_24 writes for an m x k matrix: one 2048-byte block per 128 rows x 128 K. */
+size_t gpurs_metadata_bytes(uint64_t m, uint64_t k);
+
+/* Compresses a row-major m x k matrix of GPURS_F16 / GPURS_BF16 with at most two non-zeros in every aligned
+ * group of four along k (pitch `ld` elements, 0 = k; k a multiple of 128): `values` receives the m x k/2 kept
+ * elements, `metadata` their positions in the layout the sparse kernels read.  `violations`, if not 0, points
+ * to a u32 on the device that is incremented by the number of groups holding more than two non-zeros. */
+int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_t m, uint64_t k, gpurs_device_ptr dense, uint64_t ld,
+                      gpurs_device_ptr values, gpurs_device_ptr metadata, gpurs_device_ptr violations);
 
 /* Size of the fixed device array behind gpurs_matmul_f32_static.  Every GPU that loads this library
  * holds this much memory for it until the process exits. */
