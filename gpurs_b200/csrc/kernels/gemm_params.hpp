@@ -33,7 +33,7 @@ constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swi
 constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
 constexpr int NUM_THREADS = 192;
 constexpr int EPILOGUE_WARPS = 4;
-constexpr int SCALED_THREADS = 320;  // block-scaled FP8 kernel: producer warp, MMA warp, 8 promotion warps
+constexpr int SCALED_THREADS = 384;  // promotion kernels: warpgroup 0 (producer warp, MMA warp, two idle), 8 promotion warps
 constexpr int BLOCK_N = 256;       // columns per tile
 constexpr int STAGES_SINGLE = 4;   // pipeline depth of the one-CTA kernels (48 KiB per stage)
 constexpr int STAGES_PAIR = 6;     // pipeline depth of the CTA-pair kernels (32 KiB per stage and CTA)
@@ -45,8 +45,9 @@ struct SharedLayout {
     static constexpr int B_BYTES = B_ROWS * ROW_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
-    // full[STAGES], empty[STAGES], accumulator_full[2], accumulator_empty[2], then the TMEM base word
-    static constexpr int NUM_BARRIERS = 2 * STAGES + 4;
+    // full[STAGES], empty[STAGES], accumulator_full[4], accumulator_empty[4] (the dense kernels use two of each),
+    // then the TMEM base word
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 8;
     static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
     static constexpr int TOTAL = ABORT_OFFSET + 4;

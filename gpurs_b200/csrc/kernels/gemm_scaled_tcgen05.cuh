@@ -18,6 +18,9 @@
 namespace gemm {
 
 constexpr int SCALED_EPILOGUE_WARPS = 8;
+constexpr int PRODUCER_REGISTERS = 40;      // warpgroup 0 after setmaxnreg.dec
+constexpr int PROMOTION_REGISTERS = 232;    // warpgroups 1 and 2 after setmaxnreg.inc: 128 sums + 64 staged values + addressing
+static_assert(128 * PRODUCER_REGISTERS + 256 * PROMOTION_REGISTERS <= 65536, "register budgets exceed the register file");
 constexpr int SCALE_BLOCK = 128;             // K-depth and B-row extent of one scale
 
 // KIND / ELEMENT_FORMAT as in gemm_body.  SCALED = true multiplies every 128-byte K-block by
@@ -30,7 +33,12 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     constexpr int BN = BLOCK_N;
     using L = SharedLayout<BN, CTA_GROUP, STAGES>;
     constexpr uint32_t TMEM_COLUMNS = 2 * BN;
-    constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, BN);   // f32 accumulate
+    // SPLIT issues every K-block as two products of 128 columns, each into its own accumulator with its own pair of
+    // barriers (four accumulators in flight instead of two).
+    constexpr bool SPLIT = false;   // measured: two 128-column products per block ran slower (1359 vs 1665 TFLOP/s) than one of 256
+    constexpr int HALVES = SPLIT ? 2 : 1;
+    constexpr int MMA_N = BN / HALVES;
+    constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, MMA_N);   // f32 accumulate
     constexpr int ELEMENT_BYTES = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
     constexpr int BLOCK_K = ROW_BYTES / ELEMENT_BYTES;   // elements of K per stage (128 for FP8: one scale block)
 
@@ -45,7 +53,7 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
     auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
     auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
-    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 2 + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 4 + a) * 8; };
 
     const int warp = threadIdx.x / 32;
     const uint32_t lane = ptx::lane_id();
@@ -62,9 +70,9 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             ptx::mbarrier_init(full_bar(s), 1);
             ptx::mbarrier_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; a++) {
+        for (int a = 0; a < 4; a++) {
             ptx::mbarrier_init(acc_full_bar(a), 1);
-            ptx::mbarrier_init(acc_empty_bar(a), SCALED_EPILOGUE_WARPS * CTA_GROUP);
+            ptx::mbarrier_init(acc_empty_bar(a), SCALED_EPILOGUE_WARPS / HALVES * CTA_GROUP);
         }
         ptx::fence_mbarrier_init();
         ptx::prefetch_tensor_map(map_a);
@@ -83,6 +91,7 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (warp < 4) ptx::registers_decrease<PRODUCER_REGISTERS>();
     if (warp == 0) {
         // ------------------------------------------------------------------ producer (as in the dense kernel)
         if (lane == 0) {
@@ -127,36 +136,43 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
-                for (int kb = 0; kb < k_blocks; kb++) {
-                    if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag) ||
-                        !ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
+                for (int kb = 0; kb < k_blocks && ok; kb++) {
+                    if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                         report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
                         ok = false;
                         break;
                     }
-                    ptx::tcgen05_fence_after();
-                    const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
                     const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
-                    const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
 #pragma unroll
-                    for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
-                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
-                                                                     b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(j != 0));
-                    if constexpr (CTA_GROUP == 1) {
-                        ptx::tcgen05_commit(empty_bar(stage));
-                        ptx::tcgen05_commit(acc_full_bar(acc));
-                    } else {
-                        ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
-                        ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
+                    for (int half = 0; half < HALVES; half++) {
+                        const int slot = acc * 2 + half;
+                        if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(slot), acc_phase ^ 1, abort_flag)) {
+                            report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
+                            ok = false;
+                            break;
+                        }
+                        ptx::tcgen05_fence_after();
+                        const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN + uint32_t(half) * MMA_N;
+                        const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage) + uint32_t(half) * MMA_N * ROW_BYTES);
+#pragma unroll
+                        for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
+                            ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
+                                                              b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(j != 0));
+                        if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(slot));
+                        else ptx::tcgen05_commit_pair(acc_full_bar(slot), 0x3);
                     }
+                    if (!ok) break;
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
             }
         }
-    } else {
+    } else if (warp >= 4) {
         // ------------------------------------------------------------------ promotion + epilogue
-        const int epilogue_warp = warp - 2;
+        ptx::registers_increase<PROMOTION_REGISTERS>();
+        const int epilogue_warp = warp - 4;
         const int quadrant = warp % 4;             // TMEM lanes this warp may read
         const int half = epilogue_warp / 4;        // which 128 columns of the tile
         const int scale_pitch = k_blocks;
@@ -178,7 +194,8 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                 // fetch the next block's scale while waiting for this block's products
                 const int next = min(kb + 1, k_blocks - 1);
                 const float next_scale = SCALED ? __ldg(row_scales + next) * __ldg(block_scales + next) : 1.0f;
-                const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
+                const int slot = acc * 2 + (SPLIT ? half : 0);
+                const bool ready = ptx::mbarrier_wait(acc_full_bar(slot), acc_phase, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) {
                     if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, kb);
                     ok = false;
@@ -187,20 +204,24 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                 ptx::tcgen05_fence_after();
                 const uint32_t address = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN + uint32_t(half * SCALE_BLOCK);
 #pragma unroll
-                for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
-                    uint32_t values[32];
-                    ptx::tmem_load_32x32(address + uint32_t(chunk * 32), values);
+                for (int pair = 0; pair < SCALE_BLOCK / 64; pair++) {
+                    // two 32-column loads in flight per wait: the TMEM round trip is paid twice per block, not four times
+                    uint32_t first[32], second[32];
+                    ptx::tmem_load_32x32(address + uint32_t(pair * 64), first);
+                    ptx::tmem_load_32x32(address + uint32_t(pair * 64 + 32), second);
                     ptx::tmem_load_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        sums[chunk * 32 + i] = SCALED ? fmaf(__uint_as_float(values[i]), scale, sums[chunk * 32 + i])
-                                                      : sums[chunk * 32 + i] + __uint_as_float(values[i]);
+                    for (int i = 0; i < 32; i += 2) {
+                        // two columns per instruction (fma.rn.f32x2): half the issue slots of scalar FMAs
+                        ptx::fma2(sums[pair * 64 + i], sums[pair * 64 + i + 1], first[i], first[i + 1], scale);
+                        ptx::fma2(sums[pair * 64 + 32 + i], sums[pair * 64 + 32 + i + 1], second[i], second[i + 1], scale);
+                    }
                 }
                 ptx::tcgen05_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
-                    else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                    if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(slot));
+                    else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(slot), 0));
                 }
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 scale = next_scale;

@@ -117,7 +117,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
     auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
     auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
-    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 2 + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 4 + a) * 8; };
 
     const int warp = threadIdx.x / 32;
     const uint32_t lane = ptx::lane_id();

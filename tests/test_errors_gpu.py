@@ -107,7 +107,7 @@ def test_external_module_door(gpu, stream):
     assert code_of(lambda: module.kernel("no_such_kernel")) == _ffi.E_UNKNOWN_KERNEL
     kernel = module.kernel("gpurs_gemm_bf16_f32_cg1")
     assert 0 < kernel.registers <= 255
-    shared = 4 * (128 * 128 + 256 * 128) + (2 * 4 + 4) * 8 + 8 + 1024
+    shared = 4 * (128 * 128 + 256 * 128) + (2 * 4 + 8) * 8 + 8 + 1024
     kernel.reserve_shared(shared)
     map_a, map_b = _aligned_tensor_map(), _aligned_tensor_map()
     for tensor_map, buffer, rows, box_rows in ((map_a, a, m, 128), (map_b, b, n, 256)):
