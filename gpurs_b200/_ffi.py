@@ -82,6 +82,7 @@ SIGNATURES = {
     "gpurs_kernel_launch": (C.c_int, [_P, _P, C.POINTER(LaunchConfigStruct), _PP]),
     "gpurs_kernel_image": (_P, [C.POINTER(C.c_size_t)]),
     "gpurs_matmul": (C.c_int, [_P, C.POINTER(MatmulDesc), C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_quantize_e4m3": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64]),
     "gpurs_metadata_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64]),
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),

@@ -287,3 +287,39 @@ extern "C" int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_
     void *arguments[7] = {&source, &source_pitch, &value_pointer, &metadata_pointer, &violation_pointer, &rows, &depth};
     return runtime::launch(kernel, stream, &config, arguments);
 }
+
+extern "C" int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, uint32_t block_rows,
+                                   gpurs_device_ptr codes, gpurs_device_ptr scales) {
+    const char *const op = "gpurs_quantize_e4m3";
+    if (!stream) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream");
+    if (block_rows != 1 && block_rows != 128) return fail(op, GPURS_E_INVALID_ARGUMENT, "block_rows must be 1 or 128");
+    if (rows > 0x7fffffffull || k > 0x7fffffffull) return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
+    if (rows == 0 || k == 0) return GPURS_OK;
+    const uint64_t pitch = ld ? ld : k;
+    if (pitch < k) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (!source || !codes || !scales) return fail(op, GPURS_E_INVALID_ARGUMENT, "null argument");
+    if (k % 4 || source % 16 || (pitch * 4) % 16 || codes % 4 || scales % 4)
+        return fail(op, GPURS_E_INVALID_VIEW, "k must be a multiple of 4, the source 16-byte aligned, the outputs 4-byte aligned");
+    const uint64_t k_blocks = (k + 127) / 128, row_blocks = (rows + block_rows - 1) / block_rows;
+    const uint64_t source_bytes = ((rows - 1) * pitch + k) * 4;
+    if (overlap(codes, rows * k, source, source_bytes) || overlap(scales, row_blocks * k_blocks * 4, source, source_bytes))
+        return fail(op, GPURS_E_ALIASING, "an output overlaps the input");
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, block_rows == 1 ? "gpurs_quantize_e4m3_rows" : "gpurs_quantize_e4m3_tiles", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t blocks = row_blocks * k_blocks;
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    // rows form: 8 warps = 8 blocks per CTA of 256 threads; tiles form: one 128 x 128 block per CTA of 1024 threads
+    const uint64_t ctas = block_rows == 1 ? (blocks + 7) / 8 : blocks;
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(ctas, uint64_t(gpu->multiprocessors) * (block_rows == 1 ? 8 : 2))));
+    config.block[0] = block_rows == 1 ? 256 : 1024;
+    const void *source_pointer = reinterpret_cast<const void *>(source);
+    void *code_pointer = reinterpret_cast<void *>(codes), *scale_pointer = reinterpret_cast<void *>(scales);
+    long long source_pitch = (long long)pitch;
+    int row_count = int(rows), depth = int(k);
+    void *arguments[6] = {&source_pointer, &source_pitch, &code_pointer, &scale_pointer, &row_count, &depth};
+    return runtime::launch(kernel, stream, &config, arguments);
+}

@@ -89,3 +89,73 @@ gpurs_compress_24(const uint16_t *__restrict__ dense, long long pitch, uint16_t 
     }
     if (violations != nullptr && bad != 0) atomicAdd(violations, bad);
 }
+
+#include <cuda_fp8.h>
+
+// Block quantisation of an fp32 matrix to E4M3 with one fp32 scale per block of BLOCK_ROWS x 128 elements
+// (BLOCK_ROWS = 1 for a left operand, 128 for a right one): scale = absmax / 448, or 1 for an all-zero block,
+// code = E4M3(x / scale) with round-to-nearest-even and saturation, the conversion the reference's host code
+// performs in crates/gpurs/src/gpu/float8.rs:20-52 (`cvt.rn.satfinite.e4m3x2.f32` on the device, float8.rs:96-101).
+// One warp owns 128 consecutive elements of a row (a float4 per lane); for 128-row blocks a CTA of 32 warps owns
+// the block, each warp four of its rows, and the block maximum goes through shared memory.
+template <int BLOCK_ROWS>
+__device__ __forceinline__ void quantize_e4m3_body(const float *__restrict__ source, long long pitch, uint8_t *__restrict__ codes,
+                                                    float *__restrict__ scales, int rows, int k) {
+    constexpr int ROWS_PER_WARP = BLOCK_ROWS == 1 ? 1 : 4;
+    __shared__ float warp_max[32];
+    const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const int k_blocks = (k + 127) / 128;
+    const long long row_blocks = (rows + BLOCK_ROWS - 1) / BLOCK_ROWS;
+    // BLOCK_ROWS == 1: a "block" per warp, blockDim.x / 32 of them per CTA; otherwise one block per CTA.
+    const long long blocks_total = row_blocks * k_blocks;
+    const int per_cta = BLOCK_ROWS == 1 ? blockDim.x / 32 : 1;
+    for (long long first = (long long)blockIdx.x * per_cta; first < blocks_total; first += (long long)gridDim.x * per_cta) {
+        const long long block = BLOCK_ROWS == 1 ? first + warp : first;
+        const bool active = block < blocks_total;
+        const long long row_block = active ? block / k_blocks : 0;
+        const int k_block = active ? int(block - row_block * k_blocks) : 0;
+        const int column = k_block * 128 + lane * 4;
+        float4 values[ROWS_PER_WARP];
+        float absmax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; i++) {
+            const long long row = row_block * BLOCK_ROWS + (BLOCK_ROWS == 1 ? 0 : warp * ROWS_PER_WARP + i);
+            values[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (active && row < rows && column < k) {   // k is a multiple of 4, so a float4 is all in or all out
+                values[i] = *reinterpret_cast<const float4 *>(source + row * pitch + column);
+                absmax = fmaxf(absmax, fmaxf(fmaxf(fabsf(values[i].x), fabsf(values[i].y)), fmaxf(fabsf(values[i].z), fabsf(values[i].w))));
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, offset));
+        if constexpr (BLOCK_ROWS != 1) {
+            if (lane == 0) warp_max[warp] = absmax;
+            __syncthreads();
+            absmax = warp_max[lane];
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, offset));
+            __syncthreads();
+        }
+        const float scale = absmax > 0.0f ? __fdiv_rn(absmax, 448.0f) : 1.0f;
+        if (active && lane == 0 && (BLOCK_ROWS == 1 || warp == 0)) scales[block] = scale;
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; i++) {
+            const long long row = row_block * BLOCK_ROWS + (BLOCK_ROWS == 1 ? 0 : warp * ROWS_PER_WARP + i);
+            if (active && row < rows && column < k) {
+                const __nv_fp8x2_storage_t low = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(values[i].x, scale), __fdiv_rn(values[i].y, scale)), __NV_SATFINITE, __NV_E4M3);
+                const __nv_fp8x2_storage_t high = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(values[i].z, scale), __fdiv_rn(values[i].w, scale)), __NV_SATFINITE, __NV_E4M3);
+                *reinterpret_cast<uint32_t *>(codes + row * (long long)k + column) = uint32_t(low) | (uint32_t(high) << 16);
+            }
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_quantize_e4m3_rows(const float *source, long long pitch, uint8_t *codes, float *scales, int rows, int k) {
+    quantize_e4m3_body<1>(source, pitch, codes, scales, rows, k);
+}
+
+extern "C" __global__ void __launch_bounds__(1024)
+gpurs_quantize_e4m3_tiles(const float *source, long long pitch, uint8_t *codes, float *scales, int rows, int k) {
+    quantize_e4m3_body<128>(source, pitch, codes, scales, rows, k);
+}

@@ -311,6 +311,16 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 
+def quantize_e4m3(stream: Stream, source: DeviceBuffer, rows: int, k: int, block_rows: int, ld: int = 0):
+    """Block quantisation of a rows x k fp32 matrix on the device: returns (codes, scales) with one fp32 scale per
+    block_rows x 128 block (block_rows = 1 for the left operand of a block-scaled product, 128 for the right one)."""
+    gpu = stream.gpu
+    codes = gpu.allocate(E4M3, rows * k)
+    scales = gpu.allocate(F32, -(-rows // block_rows) * -(-k // 128))
+    _check(gpu._lib.gpurs_quantize_e4m3(stream._handle, rows, k, source.pointer, ld, block_rows, codes.pointer, scales.pointer))
+    return codes, scales
+
+
 def compress_24(stream: Stream, dense: DeviceBuffer, m: int, k: int, ld: int = 0):
     """2:4 compression of an m x k 16-bit matrix on the device: returns (values, metadata, violations) where
     `values` is the m x k/2 buffer of kept elements, `metadata` the byte buffer of their positions in the layout

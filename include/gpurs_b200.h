@@ -190,6 +190,17 @@ typedef struct gpurs_matmul_desc {
 int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
                  gpurs_device_ptr c);
 
+/* ---- FP8 block quantisation ------------------------------------------------------------------------ */
+
+/* Quantises a row-major rows x k fp32 matrix (pitch `ld` elements, 0 = k; k a multiple of 4) to E4M3 with one fp32
+ * scale per block of block_rows x 128 elements, block_rows = 1 (left operand) or 128 (right operand): scale =
+ * absmax / 448 (1 for an all-zero block), code = E4M3(x / scale), round to nearest even with saturation — the host
+ * conversion of the reference (crates/gpurs/src/gpu/float8.rs:20-52); the reference has no block quantiser.
+ * `codes` receives rows x k bytes, `scales` [ceil(rows / block_rows)][ceil(k / 128)] floats: the operand and scale
+ * layout gpurs_matmul takes for GPURS_E4M3 with scales. */
+int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, uint32_t block_rows,
+                        gpurs_device_ptr codes, gpurs_device_ptr scales);
+
 /* ---- 2:4 structured sparsity (no counterpart in the reference, which has no sparse path) ---------- */
 
 /* Bytes of metadata gpurs_compress_24 writes for an m x k matrix: one 2048-byte block per 128 rows x 128 K. */
