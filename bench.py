@@ -210,7 +210,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     a, b = gpu.upload(a_host, element), gpu.upload(b_host, element)
     c = gpu.allocate(out_element, m * n)
     shape = [m, n, k]
-    options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows)
+    options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows, l2_policy=args.l2_policy)
     if args.workload.startswith("sparse24"):
         # A becomes 2:4: zero two elements of every group of four (seeded choice), then compress on the device
         rng = np.random.default_rng(5 + rank)
@@ -381,6 +381,7 @@ def main() -> None:
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--algorithm", type=int, default=0, help="0 auto, 1 single-CTA tiles, 2 CTA-pair tiles")
     parser.add_argument("--raster-rows", type=int, default=0, help="tile rows walked together (0 = library default)")
+    parser.add_argument("--l2-policy", type=int, default=0, help="0 default, 1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 none")
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                         help="weak: every GPU multiplies a full-size shard (global M grows); strong: the workload's M is split")
     parser.add_argument("--allgather", action="store_true", help="also time GEMM + NCCL all-gather of C (N > 1)")

@@ -96,6 +96,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.status = reinterpret_cast<unsigned int *>(gpu->status);
     params.scale_a = reinterpret_cast<const float *>(g.scale_a);
     params.scale_b = reinterpret_cast<const float *>(g.scale_b);
+    params.l2_policy = g.l2_policy;
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
     uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
@@ -212,6 +213,8 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.cta_group = group == GPURS_ALGO_CTA_PAIR ? 2 : 1;
     gemm.raster_rows = desc->raster_rows;
     gemm.max_ctas = desc->max_ctas;
+    if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
+    gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints
     if (sparse) {
         if (desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "a sparse product takes no scales");
         gemm.stem = desc->a_type == GPURS_F16 ? "gpurs_gemm_sparse_f16_f32"

@@ -26,6 +26,7 @@ struct Params {
     unsigned int *status;    // [0] first failure code, [1] block, [2] tile, [3] K-block
     const float *scale_a;    // block-scaled FP8 only: [M][ceil(K/128)]
     const float *scale_b;    // block-scaled FP8 only: [ceil(N/128)][ceil(K/128)]
+    int l2_policy;           // dense kernels: 0 no hint; 1 keep A (evict last), stream B (evict first); 2 the reverse; 3 keep both
 };
 
 constexpr int BLOCK_M = 128;       // rows per CTA (= TMEM lanes)

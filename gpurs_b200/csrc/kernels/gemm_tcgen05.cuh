@@ -165,6 +165,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // L2 residency: the operand whose panel is shared by the tiles of successive waves can be asked to
+            // stay (evict last) while the other streams through (evict first).
+            const bool hinted = p.l2_policy != 0;
+            const uint64_t policy_a = (p.l2_policy == 1 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
+            const uint64_t policy_b = (p.l2_policy == 2 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
                 int tile_m, tile_n;
                 tile_position(tile, p, tile_m, tile_n);
@@ -178,15 +183,25 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     }
                     if constexpr (CTA_GROUP == 1) {
                         ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
-                        ptx::tma_load_2d(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage));
-                        ptx::tma_load_2d(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage));
+                        if (hinted) {
+                            ptx::tma_load_2d_hint(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage), policy_a);
+                            ptx::tma_load_2d_hint(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage), policy_b);
+                        } else {
+                            ptx::tma_load_2d(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage));
+                            ptx::tma_load_2d(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage));
+                        }
                     } else {
                         // Both CTAs' loads are counted on the leader's barrier, which the leader arms
                         // for the bytes of the pair.
                         if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
                         const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
-                        ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
-                        ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * block_k, row_b, leader_bar);
+                        if (hinted) {
+                            ptx::tma_load_2d_pair_hint(stage_a(stage), map_a, kb * block_k, row_a, leader_bar, policy_a);
+                            ptx::tma_load_2d_pair_hint(stage_b(stage), map_b, kb * block_k, row_b, leader_bar, policy_b);
+                        } else {
+                            ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
+                            ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * block_k, row_b, leader_bar);
+                        }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }

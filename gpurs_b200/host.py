@@ -279,6 +279,7 @@ class MatmulOptions:
     max_ctas: int = 0
     precision: int = _ffi.PRECISION_DEFAULT
     raster_rows: int = 0
+    l2_policy: int = 0
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
@@ -308,6 +309,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.scale_a = options.scale_a.pointer if options.scale_a else 0
     desc.scale_b = options.scale_b.pointer if options.scale_b else 0
     desc.metadata = options.metadata.pointer if options.metadata else 0
+    desc.l2_policy = options.l2_policy
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 

@@ -180,6 +180,9 @@ typedef struct gpurs_matmul_desc {
     gpurs_device_ptr metadata;       /* 2:4-sparse A (GPURS_F16 / GPURS_BF16): the metadata from gpurs_compress_24; then `a`
                                         is the m x k/2 array of kept values, k stays the logical depth (a multiple of
                                         128), lda counts kept values (0 = k/2).  0 = dense A */
+    int32_t l2_policy;               /* L2 residency hint of the operand loads (dense kernels): 0 library default,
+                                        1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 no hints */
+    int32_t reserved;                /* 0 */
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
