@@ -45,6 +45,8 @@ WORKLOADS = {
     "e4m3_unscaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),
     "e4m3_scaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),   # fp32 scales per 1x128 / 128x128 block
     "f32_1024": ("f32", "f32", 1024, 1024, 1024),
+    "f16_skinny_16x4096x4096": ("f16", "f32", 16, 4096, 4096),   # the reference's decode-shaped example, bias included
+    "f16_skinny_16x16384x16384": ("f16", "f32", 16, 16384, 16384),   # same shape class with a weight (512 MiB) larger than L2
     "sparse24_bf16_2048x8192x8192": ("bf16", "bf16", 2048, 8192, 8192),   # one GPU's shard of 16384 x 8192 (2:4) x 8192
 }
 DEFAULT_WORKLOAD = "bf16_8192"
@@ -211,6 +213,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     c = gpu.allocate(out_element, m * n)
     shape = [m, n, k]
     options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows, l2_policy=args.l2_policy)
+    if "skinny" in args.workload:
+        options.bias = gpu.upload((np.arange(n) / 64.0).astype(np.float32))
     if args.workload.startswith("sparse24"):
         # A becomes 2:4: zero two elements of every group of four (seeded choice), then compress on the device
         rng = np.random.default_rng(5 + rank)
@@ -359,6 +363,15 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
         }
         if gather is not None:
             line["allgather"] = gather
+        if "skinny" in args.workload:
+            # bound by streaming B once from HBM: report the roofline against the measured copy bandwidth
+            path = ROOT / "MEASURED_PEAKS.json"
+            hbm = float(json.loads(path.read_text())["hbm_gbs"]) if path.exists() else 6650.0
+            streamed = float(b_host.nbytes + a_host.nbytes + m * n * out_bytes)
+            achieved = streamed / (ms_per_step * 1e-3) / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "traffic": None,
+                                "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if path.exists() else "fallback",
+                                "algorithmic_bytes_per_launch": int(streamed)}
         if world == 1 and not args.no_cpu_baseline:
             rows = 4096
             seconds, flops, threads = cpu_band(kind, n, k, rows)

@@ -25,7 +25,7 @@ E_DEVICE_TIMEOUT = 100010
 E_DRIVER_UNAVAILABLE = 100011
 
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
-ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR = 0, 1, 2
+ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -42,7 +42,7 @@ class MatmulDesc(C.Structure):
         ("a_len", C.c_uint64), ("b_len", C.c_uint64), ("c_len", C.c_uint64),
         ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
-        ("l2_policy", C.c_int32), ("reserved", C.c_int32),
+        ("l2_policy", C.c_int32), ("reserved", C.c_int32), ("bias", C.c_uint64),
     ]
 
 

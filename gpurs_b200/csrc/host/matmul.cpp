@@ -97,6 +97,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.scale_a = reinterpret_cast<const float *>(g.scale_a);
     params.scale_b = reinterpret_cast<const float *>(g.scale_b);
     params.l2_policy = g.l2_policy;
+    params.bias = reinterpret_cast<const float *>(g.bias);
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
     uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
@@ -119,6 +120,74 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
 namespace {
 
 using launcher::launch_gemm;
+
+// Host mirror of gemm::SkinnyParams (kernels/gemm_skinny_tcgen05.cuh).
+struct SkinnyParams {
+    float *c;
+    long long ldc;
+    const float *bias;
+    unsigned int *turns;
+    float *partials;
+    unsigned int *status;
+    int m, n, k, tiles, splits, k_blocks_per_split;
+};
+
+// The decode-shaped product: m <= 64 rows of A against all of B, K split among CTAs, ordered reduction.
+int launch_skinny(gpurs_stream *stream, const launcher::Gemm &g) {
+    gpurs_gpu *gpu = stream->gpu;
+    const int tokens = g.m <= 16 ? 16 : (g.m <= 32 ? 32 : 64);
+    char name[96];
+    std::snprintf(name, sizeof name, "gpurs_gemm_skinny_%s_f32_t%d", g.element_type == GPURS_F16 ? "f16" : "bf16", tokens);
+    const uint32_t shared_bytes = uint32_t(gemm::skinny_shared_bytes(tokens));
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
+    if (result != GPURS_OK) return result;
+    alignas(64) CUtensorMap map_big, map_small;
+    const uint64_t dims_big[2] = {g.k, g.n}, dims_small[2] = {g.k, g.m};
+    const uint64_t stride_big[1] = {g.ldb * 2}, stride_small[1] = {g.lda * 2};
+    const uint32_t box_big[2] = {64, uint32_t(gemm::BLOCK_M)}, box_small[2] = {64, uint32_t(tokens)};
+    result = gpurs_tensor_map_encode(gpu, &map_big, g.element_type, 2, g.b, dims_big, stride_big, box_big, 3, 3);
+    if (result != GPURS_OK) return result;
+    result = gpurs_tensor_map_encode(gpu, &map_small, g.element_type, 2, g.a, dims_small, stride_small, box_small, 3, 3);
+    if (result != GPURS_OK) return result;
+
+    SkinnyParams params;
+    std::memset(&params, 0, sizeof params);
+    params.c = reinterpret_cast<float *>(g.c);
+    params.ldc = (long long)g.ldc;
+    params.bias = reinterpret_cast<const float *>(g.bias);
+    params.status = reinterpret_cast<unsigned int *>(gpu->status);
+    params.m = int(g.m), params.n = int(g.n), params.k = int(g.k);
+    params.tiles = int((g.n + gemm::BLOCK_M - 1) / gemm::BLOCK_M);
+    // One CTA per multiprocessor at most (each keeps 8 stages in flight), each with a whole number of 64-deep K-blocks.
+    const int k_blocks = int((g.k + 63) / 64);
+    const int ctas = g.max_ctas > 0 ? g.max_ctas : gpu->multiprocessors;
+    int splits = std::max(1, std::min(k_blocks, ctas / params.tiles));
+    params.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + params.k_blocks_per_split - 1) / params.k_blocks_per_split;   // no empty trailing split
+    params.splits = splits;
+    CUdeviceptr turns = 0, partials = 0;
+    if (splits > 1) {
+        result = runtime::turns_acquire(stream, size_t(gemm::SKINNY_MAX_TILES) * 4 * sizeof(unsigned int), &turns);
+        if (result != GPURS_OK) return result;
+        result = runtime::workspace_acquire(stream, size_t(params.tiles) * splits * tokens * gemm::BLOCK_M * sizeof(float), &partials);
+        if (result != GPURS_OK) return result;
+    }
+    params.turns = reinterpret_cast<unsigned int *>(turns);
+    params.partials = reinterpret_cast<float *>(partials);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(params.tiles) * uint32_t(splits);
+    config.block[0] = gemm::NUM_THREADS;
+    config.shared_bytes = shared_bytes;
+    void *arguments[3] = {&map_big, &map_small, &params};
+    result = runtime::launch(kernel, stream, &config, arguments);
+    if (splits > 1) {
+        const int released = runtime::turns_release(stream), freed = runtime::workspace_release(stream);
+        if (result == GPURS_OK) result = released != GPURS_OK ? released : freed;
+    }
+    return result;
+}
 
 // Enqueues the hi/lo split of a rows x k fp32 matrix into a rows x 3k one (kernels/transform.cu).
 int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t rows, uint64_t k, int order) {
@@ -198,8 +267,18 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     // Kernels that promote every K-block to registers hand an accumulator back and forth once per block;
     // across a CTA pair that hand-off costs more than the pair saves, so they default to one-CTA tiles.
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
+    // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
+    const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
+                                 desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
+                                 c % 4 == 0;
+    if (group == GPURS_ALGO_SKINNY && !skinny_possible)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm needs m <= 64, 16-bit dense operands and fp32 output");
+    if (group == GPURS_ALGO_AUTO && skinny_possible) group = GPURS_ALGO_SKINNY;
     if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
-    if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
+    if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR && group != GPURS_ALGO_SKINNY)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
+    if (desc->bias && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "a bias is for floating-point outputs");
+    if (desc->bias % 4) return fail(op, GPURS_E_INVALID_VIEW, "the bias must be 4-byte aligned");
     if (desc->precision != GPURS_PRECISION_DEFAULT && desc->precision != GPURS_PRECISION_TF32)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown precision");
     Gemm gemm;
@@ -213,6 +292,8 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.cta_group = group == GPURS_ALGO_CTA_PAIR ? 2 : 1;
     gemm.raster_rows = desc->raster_rows;
     gemm.max_ctas = desc->max_ctas;
+    gemm.bias = desc->bias;
+    if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
     if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
     gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints
     if (sparse) {

@@ -94,32 +94,40 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
     return GPURS_OK;
 }
 
-int workspace_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out) {
+static int scratch_acquire(gpurs_stream *stream, gpurs_gpu::Scratch &scratch, size_t bytes, bool zeroed, CUdeviceptr *out) {
     gpurs_gpu *gpu = stream->gpu;
     const driver::Api *api = gpu->api;
-    if (gpu->workspace_bytes < bytes) {
+    if (scratch.bytes < bytes) {
         // Nobody may still be using the old block when it is replaced.
         GPURS_TRY(api, cuCtxSynchronize());
-        if (gpu->workspace) GPURS_TRY(api, cuMemFree(gpu->workspace));
-        gpu->workspace = 0;
-        gpu->workspace_bytes = 0;
+        if (scratch.pointer) GPURS_TRY(api, cuMemFree(scratch.pointer));
+        scratch.pointer = 0;
+        scratch.bytes = 0;
         const size_t rounded = (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);
-        GPURS_TRY(api, cuMemAlloc(&gpu->workspace, rounded));
-        gpu->workspace_bytes = rounded;
-        gpu->workspace_used = false;
+        GPURS_TRY(api, cuMemAlloc(&scratch.pointer, rounded));
+        scratch.bytes = rounded;
+        scratch.used = false;
+        if (zeroed) {
+            GPURS_TRY(api, cuMemsetD8Async(scratch.pointer, 0, rounded, gpu->transfer));
+            GPURS_TRY(api, cuStreamSynchronize(gpu->transfer));
+        }
     }
-    if (!gpu->workspace_event) GPURS_TRY(api, cuEventCreate(&gpu->workspace_event, CU_EVENT_DISABLE_TIMING));
-    if (gpu->workspace_used) GPURS_TRY(api, cuStreamWaitEvent(stream->handle, gpu->workspace_event, 0));
-    *out = gpu->workspace;
+    if (!scratch.event) GPURS_TRY(api, cuEventCreate(&scratch.event, CU_EVENT_DISABLE_TIMING));
+    if (scratch.used) GPURS_TRY(api, cuStreamWaitEvent(stream->handle, scratch.event, 0));
+    *out = scratch.pointer;
     return GPURS_OK;
 }
 
-int workspace_release(gpurs_stream *stream) {
-    gpurs_gpu *gpu = stream->gpu;
-    GPURS_TRY(gpu->api, cuEventRecord(gpu->workspace_event, stream->handle));
-    gpu->workspace_used = true;
+static int scratch_release(gpurs_stream *stream, gpurs_gpu::Scratch &scratch) {
+    GPURS_TRY(stream->gpu->api, cuEventRecord(scratch.event, stream->handle));
+    scratch.used = true;
     return GPURS_OK;
 }
+
+int workspace_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out) { return scratch_acquire(stream, stream->gpu->workspace, bytes, false, out); }
+int workspace_release(gpurs_stream *stream) { return scratch_release(stream, stream->gpu->workspace); }
+int turns_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out) { return scratch_acquire(stream, stream->gpu->turns, bytes, true, out); }
+int turns_release(gpurs_stream *stream) { return scratch_release(stream, stream->gpu->turns); }
 
 }  // namespace runtime
 
@@ -197,8 +205,10 @@ void gpurs_gpu_free(gpurs_gpu *gpu) {
             delete gpu->builtin;
         }
         gpu->api->cuMemFree(gpu->status);
-        if (gpu->workspace) gpu->api->cuMemFree(gpu->workspace);
-        if (gpu->workspace_event) gpu->api->cuEventDestroy(gpu->workspace_event);
+        for (gpurs_gpu::Scratch *scratch : {&gpu->workspace, &gpu->turns}) {
+            if (scratch->pointer) gpu->api->cuMemFree(scratch->pointer);
+            if (scratch->event) gpu->api->cuEventDestroy(scratch->event);
+        }
         gpu->api->cuStreamDestroy(gpu->transfer);
     }
     gpu->api->cuDevicePrimaryCtxRelease(gpu->device);

@@ -29,12 +29,16 @@ struct gpurs_gpu {
     gpurs_module *builtin = nullptr;   // the embedded sm_100a image, loaded on first use
     std::map<std::string, gpurs_kernel *> kernels;
     uint64_t launches = 0;
-    // Grow-only scratch for operand transforms (the hi/lo split of fp32 operands).  One user at a time:
-    // `workspace_event` marks the end of the previous user's work, and the next user's stream waits on it.
-    CUdeviceptr workspace = 0;
-    size_t workspace_bytes = 0;
-    CUevent workspace_event = nullptr;
-    bool workspace_used = false;
+    // Scratch owned by the handle.  Each block has one user at a time: `event` marks the end of the previous
+    // user's work and the next user's stream waits on it.
+    struct Scratch {
+        CUdeviceptr pointer = 0;
+        size_t bytes = 0;
+        CUevent event = nullptr;
+        bool used = false;
+    };
+    Scratch workspace;   // grow-only: the hi/lo split copies of fp32 operands
+    Scratch turns;       // fixed: the turn counters of split-K products, zero between launches
 };
 
 struct gpurs_stream {
@@ -80,6 +84,9 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
 // the previous borrower is ordered before it.  Call workspace_release once that work is enqueued.
 int workspace_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out);
 int workspace_release(gpurs_stream *stream);
+// The same for the block of zero-initialised turn counters (`bytes` is fixed after the first call).
+int turns_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out);
+int turns_release(gpurs_stream *stream);
 
 }  // namespace runtime
 

@@ -26,6 +26,7 @@ struct Params {
     unsigned int *status;    // [0] first failure code, [1] block, [2] tile, [3] K-block
     const float *scale_a;    // block-scaled FP8 only: [M][ceil(K/128)]
     const float *scale_b;    // block-scaled FP8 only: [ceil(N/128)][ceil(K/128)]
+    const float *bias;       // optional fp32 [N], added to every row before the output rounding (float outputs), or null
     int l2_policy;           // dense kernels: 0 no hint; 1 keep A (evict last), stream B (evict first); 2 the reverse; 3 keep both
 };
 
@@ -54,6 +55,11 @@ struct SharedLayout {
     static constexpr int TOTAL = ABORT_OFFSET + 4;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;   // slack to align the stages to 1024 bytes
 };
+
+// Skinny kernels (gemm_skinny_tcgen05.cuh): 8 stages of 128 rows of the big operand + the padded small one.
+constexpr int skinny_shared_bytes(int tokens) { return 8 * (BLOCK_M * ROW_BYTES + ((tokens * ROW_BYTES + 1023) / 1024) * 1024) + (2 * 8 + 1) * 8 + 8 + 1024; }
+constexpr int SKINNY_MAX_ROWS = 64;      // m up to which the skinny kernels are used
+constexpr int SKINNY_MAX_TILES = 4096;   // turn counters kept per gpu handle
 
 // 2:4 sparse kernels (gemm_sparse_tcgen05.cuh): dynamic shared memory of the one-CTA (2 stages of 82 KiB) and
 // CTA-pair (4 stages of 50 KiB) entries, and the size of one metadata block (128 rows x 128 logical K).

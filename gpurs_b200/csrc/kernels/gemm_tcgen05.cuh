@@ -47,19 +47,42 @@ __device__ __forceinline__ void tile_position(int tile, const Params &p, int &ti
     tile_n = local / rows;
 }
 
-__device__ __forceinline__ void report(const Params &p, volatile uint32_t *abort_flag, uint32_t code, int tile, int k_block) {
+__device__ __forceinline__ void report_status(unsigned int *status, volatile uint32_t *abort_flag, uint32_t code, int tile, int k_block) {
     *abort_flag = code;
-    if (atomicCAS(p.status, 0u, code) == 0u) {
-        p.status[1] = blockIdx.x;
-        p.status[2] = uint32_t(tile);
-        p.status[3] = uint32_t(k_block);
+    if (atomicCAS(status, 0u, code) == 0u) {
+        status[1] = blockIdx.x;
+        status[2] = uint32_t(tile);
+        status[3] = uint32_t(k_block);
     }
 }
 
+__device__ __forceinline__ void report(const Params &p, volatile uint32_t *abort_flag, uint32_t code, int tile, int k_block) {
+    report_status(p.status, abort_flag, code, tile, k_block);
+}
+
+// COLUMNS (16, 32 or 64) consecutive accumulator columns of this warp's 32 TMEM lanes.
+template <int COLUMNS>
+__device__ __forceinline__ void tmem_load_columns(uint32_t address, uint32_t (&values)[COLUMNS]) {
+    if constexpr (COLUMNS == 16) ptx::tmem_load_32x16(address, values);
+    else if constexpr (COLUMNS == 32) ptx::tmem_load_32x32(address, values);
+    else ptx::tmem_load_32x64(address, values);
+}
+
 template <int OUT>
-__device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&acc)[32], int row, int column) {
+__device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column) {
     if (row >= p.m || column >= p.n) return;
     const bool whole = column + 32 <= p.n && p.vector_stores;
+    uint32_t acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) acc[i] = source[i];
+    if constexpr (OUT != OUT_I32) {
+        // optional bias, one fp32 per output column, added before the output rounding
+        if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __ldg(p.bias + column + i));
+        }
+    }
     if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
         uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + size_t(row) * p.ldc + column;
         if (whole) {

@@ -320,3 +320,21 @@ __device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const CUtens
 }
 
 }  // namespace ptx
+
+namespace ptx {
+
+// 32 lanes x 16 consecutive 32-bit columns (see tmem_load_32x32).
+__device__ __forceinline__ void tmem_load_32x16(uint32_t address, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(address)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_acquire(const unsigned int *address) {
+    uint32_t value;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+    return value;
+}
+
+}  // namespace ptx

@@ -282,6 +282,7 @@ class MatmulOptions:
     l2_policy: int = 0
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
+    bias: DeviceBuffer | None = None       # fp32 [n], added to every row of C
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
@@ -310,6 +311,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.scale_b = options.scale_b.pointer if options.scale_b else 0
     desc.metadata = options.metadata.pointer if options.metadata else 0
     desc.l2_policy = options.l2_policy
+    desc.bias = options.bias.pointer if options.bias else 0
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 

@@ -152,7 +152,9 @@ const void *gpurs_kernel_image(size_t *bytes);
 enum {
     GPURS_ALGO_AUTO = 0,
     GPURS_ALGO_SINGLE_CTA = 1,  /* 128 x 256 tiles, one CTA per tile (tcgen05 cta_group::1) */
-    GPURS_ALGO_CTA_PAIR = 2     /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
+    GPURS_ALGO_CTA_PAIR = 2,    /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
+    GPURS_ALGO_SKINNY = 3       /* m <= 64, 16-bit operands, fp32 output: B fills the tensor core's rows, K is split among CTAs
+                                   and the splits add in order (the reference's SplitDepth + TileLock); AUTO picks it */
 };
 
 /* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */
@@ -183,6 +185,8 @@ typedef struct gpurs_matmul_desc {
     int32_t l2_policy;               /* L2 residency hint of the operand loads (dense kernels): 0 library default,
                                         1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 no hints */
     int32_t reserved;                /* 0 */
+    gpurs_device_ptr bias;           /* optional fp32 [n] added to every row of C before the output rounding (float outputs;
+                                        the epilogue of the reference's skinny example, examples/ada/examples/skinny_matrix.rs:60-64) */
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
