@@ -42,7 +42,7 @@ class MatmulDesc(C.Structure):
         ("a_len", C.c_uint64), ("b_len", C.c_uint64), ("c_len", C.c_uint64),
         ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
-        ("l2_policy", C.c_int32), ("reserved", C.c_int32), ("bias", C.c_uint64),
+        ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
     ]
 
 

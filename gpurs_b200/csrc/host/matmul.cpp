@@ -61,9 +61,16 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint32_t block_k = uint32_t(gemm::ROW_BYTES / g.element_bytes);
     alignas(64) CUtensorMap map_a, map_b, map_e;
     // A sparse A is stored as its kept half: k/2 values per row.
-    const uint64_t dims_a[2] = {sparse ? g.k / 2 : g.k, g.m}, dims_b[2] = {g.k, g.n};
+    const uint64_t dims_a[2] = {sparse ? g.k / 2 : g.k, g.m};
     const uint64_t stride_a[1] = {g.lda * eb}, stride_b[1] = {g.ldb * eb};
-    const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)}, box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
+    const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)};
+    // B as n x k: one box of (128 bytes of k) x (the tile's rows of n).  B as k x n: boxes of (128 bytes of n) x (block_k rows of k).
+    uint64_t dims_b[2] = {g.k, g.n};
+    uint32_t box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
+    if (g.b_row_major) {
+        dims_b[0] = g.n, dims_b[1] = g.k;
+        box_b[0] = uint32_t(gemm::ROW_BYTES / g.element_bytes), box_b[1] = block_k;
+    }
     result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 2, g.a, dims_a, stride_a, box_a, 3, 3);
     if (result != GPURS_OK) return result;
     result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 2, g.b, dims_b, stride_b, box_b, 3, 3);
@@ -97,6 +104,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.scale_a = reinterpret_cast<const float *>(g.scale_a);
     params.scale_b = reinterpret_cast<const float *>(g.scale_b);
     params.l2_policy = g.l2_policy;
+    params.b_row_major = g.b_row_major ? 1 : 0;
     params.bias = reinterpret_cast<const float *>(g.bias);
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
@@ -231,10 +239,15 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     if (sparse && k % 128) return fail(op, GPURS_E_INVALID_VIEW, "the depth of a 2:4-sparse product must be a multiple of 128");
     if (sparse && desc->metadata % 16) return fail(op, GPURS_E_INVALID_VIEW, "the metadata must be 16-byte aligned");
     const uint64_t a_columns = sparse ? k / 2 : k;   // stored elements per row of A
-    const uint64_t lda = desc->lda ? desc->lda : a_columns, ldb = desc->ldb ? desc->ldb : k, ldc = desc->ldc ? desc->ldc : n;
-    if (lda < a_columns || ldb < k || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (desc->b_row_major != 0 && desc->b_row_major != 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "b_row_major must be 0 or 1");
+    const bool b_row_major = desc->b_row_major == 1;
+    // B is n rows of k (the reference's layout) or, row-major as in C = A * B, k rows of n.
+    const uint64_t b_rows = b_row_major ? k : n, b_columns = b_row_major ? n : k;
+    const uint64_t lda = desc->lda ? desc->lda : a_columns, ldb = desc->ldb ? desc->ldb : b_columns, ldc = desc->ldc ? desc->ldc : n;
+    if (lda < a_columns || ldb < b_columns || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
     // Extent of each operand in elements: the last row ends at (rows - 1) * pitch + columns.
-    const uint64_t a_extent = m ? (m - 1) * lda + a_columns : 0, b_extent = n ? (n - 1) * ldb + k : 0, c_extent = m ? (m - 1) * ldc + n : 0;
+    const uint64_t a_extent = m ? (m - 1) * lda + a_columns : 0, b_extent = b_rows ? (b_rows - 1) * ldb + b_columns : 0,
+                   c_extent = m ? (m - 1) * ldc + n : 0;
     if ((desc->a_len && desc->a_len < a_extent) || (desc->b_len && desc->b_len < b_extent) || (desc->c_len && desc->c_len < c_extent))
         return fail(op, GPURS_E_LENGTH_MISMATCH, "a slice is shorter than the matrix it is said to hold");
     if (m == 0 || n == 0) return GPURS_OK;
@@ -269,8 +282,12 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
-                                 desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
+                                 desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && !b_row_major && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
                                  c % 4 == 0;
+    // N-major reading of 32-bit elements needs a different shared-memory swizzle (32-byte atoms) that these kernels
+    // do not set up; measured: the plain 128-byte swizzle yields zeros for TF32.
+    if (b_row_major && (sparse || promoted || desc->a_type == GPURS_F32))
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "a k x n right operand is supported by the dense 16-bit and 8-bit tile kernels only");
     if (group == GPURS_ALGO_SKINNY && !skinny_possible)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm needs m <= 64, 16-bit dense operands and fp32 output");
     if (group == GPURS_ALGO_AUTO && skinny_possible) group = GPURS_ALGO_SKINNY;
@@ -293,6 +310,7 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.raster_rows = desc->raster_rows;
     gemm.max_ctas = desc->max_ctas;
     gemm.bias = desc->bias;
+    gemm.b_row_major = b_row_major;
     if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
     if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
     gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints

@@ -16,6 +16,8 @@ enum : uint32_t {
     STATUS_EPILOGUE_TIMEOUT = 3,
 };
 
+// Kernel parameter block of the tile kernels (after the TMA descriptors).  Hosts that launch an entry themselves
+// through the module door fill it field by field; its layout is part of the kernel image's interface.
 struct Params {
     void *c;                 // output, row-major M x N with row pitch ldc (elements)
     long long ldc;
@@ -23,12 +25,15 @@ struct Params {
     int tiles_m, tiles_n;    // in units of (128 * CTA_GROUP) x BLOCK_N tiles
     int raster_rows;         // tile rows walked together so concurrent tiles share operands in L2
     int vector_stores;       // 1 when every output row start is 16-byte aligned
+    int b_row_major;         // dense kernels: 0 = B is N x K (K contiguous, the reference's layout), 1 = B is K x N (N contiguous)
     unsigned int *status;    // [0] first failure code, [1] block, [2] tile, [3] K-block
     const float *scale_a;    // block-scaled FP8 only: [M][ceil(K/128)]
     const float *scale_b;    // block-scaled FP8 only: [ceil(N/128)][ceil(K/128)]
     const float *bias;       // optional fp32 [N], added to every row before the output rounding (float outputs), or null
     int l2_policy;           // dense kernels: 0 no hint; 1 keep A (evict last), stream B (evict first); 2 the reverse; 3 keep both
+    int reserved;            // 0
 };
+static_assert(sizeof(Params) == 88, "the parameter block is part of the kernel image's interface");
 
 constexpr int BLOCK_M = 128;       // rows per CTA (= TMEM lanes)
 constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swizzle span

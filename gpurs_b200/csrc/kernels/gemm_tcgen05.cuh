@@ -152,6 +152,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     const int element_bytes = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
     const int block_k = ROW_BYTES / element_bytes;
     const int k_blocks = (p.k + block_k - 1) / block_k;
+    // K x N storage of B: one TMA box is 128 bytes of N (n_per_box elements) by block_k rows of K.
+    const int n_per_box = ROW_BYTES / element_bytes;
+    const uint32_t box_bytes = uint32_t(block_k) * ROW_BYTES;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -209,6 +212,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         if (hinted) {
                             ptx::tma_load_2d_hint(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage), policy_a);
                             ptx::tma_load_2d_hint(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage), policy_b);
+                        } else if (p.b_row_major) {
+                            ptx::tma_load_2d(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage));
+                            // K x N storage: boxes of 128 bytes of N by block_k rows of K, side by side
+                            for (int i = 0; i < L::B_ROWS / n_per_box; i++)
+                                ptx::tma_load_2d(stage_b(stage) + uint32_t(i) * box_bytes, map_b, row_b + i * n_per_box, kb * block_k, full_bar(stage));
                         } else {
                             ptx::tma_load_2d(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage));
                             ptx::tma_load_2d(stage_b(stage), map_b, kb * block_k, row_b, full_bar(stage));
@@ -221,6 +229,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         if (hinted) {
                             ptx::tma_load_2d_pair_hint(stage_a(stage), map_a, kb * block_k, row_a, leader_bar, policy_a);
                             ptx::tma_load_2d_pair_hint(stage_b(stage), map_b, kb * block_k, row_b, leader_bar, policy_b);
+                        } else if (p.b_row_major) {
+                            ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
+                            for (int i = 0; i < L::B_ROWS / n_per_box; i++)
+                                ptx::tma_load_2d_pair(stage_b(stage) + uint32_t(i) * box_bytes, map_b, row_b + i * n_per_box, kb * block_k, leader_bar);
                         } else {
                             ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
                             ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * block_k, row_b, leader_bar);
@@ -259,12 +271,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     }
                     ptx::tcgen05_fence_after();
                     const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
-                    const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
+                    // B as N x K: K-major like A, 32 bytes of K per instruction inside the swizzle span.  B as K x N: N-major
+                    // (bit 16 of the instruction descriptor), an instruction's K is MMA_K rows of 128 bytes.
+                    const uint64_t b_desc = p.b_row_major ? ptx::smem_descriptor_mn_major_sw128(stage_b(stage), box_bytes)
+                                                          : ptx::smem_descriptor_k_major_sw128(stage_b(stage));
+                    const uint64_t b_step = p.b_row_major ? uint64_t(((MMA_K_BYTES / element_bytes) * ROW_BYTES) >> 4) : uint64_t(MMA_K_BYTES >> 4);
+                    const uint32_t idesc = p.b_row_major ? (IDESC | (1u << 16)) : IDESC;
 #pragma unroll
                     for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++) {
-                        // advancing the start address by 32 bytes steps through K inside the swizzle span
-                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
-                                                          b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC,
+                        // advancing A's start address by 32 bytes steps through K inside the swizzle span
+                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j) * b_step, idesc,
                                                           uint32_t((kb | j) != 0));
                     }
                     if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));

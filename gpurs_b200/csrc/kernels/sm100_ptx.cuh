@@ -338,3 +338,16 @@ __device__ __forceinline__ uint32_t load_acquire(const unsigned int *address) {
 }
 
 }  // namespace ptx
+
+namespace ptx {
+
+// Shared-memory matrix descriptor of an MN-major operand stored as blocks of `rows` K-rows x 128 bytes (128 bytes of
+// consecutive M/N elements per K index, 128-byte swizzle in groups of eight rows): the leading offset is the distance
+// between consecutive 128-byte-wide blocks along M/N (one TMA box), the stride offset the 1024 bytes between groups
+// of eight K-rows.
+__device__ __forceinline__ uint64_t smem_descriptor_mn_major_sw128(uint32_t address, uint32_t block_bytes) {
+    return static_cast<uint64_t>((address & 0x3ffffu) >> 4) | (static_cast<uint64_t>(block_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+}  // namespace ptx

@@ -280,6 +280,7 @@ class MatmulOptions:
     precision: int = _ffi.PRECISION_DEFAULT
     raster_rows: int = 0
     l2_policy: int = 0
+    b_row_major: bool = False              # B given as k x n (n contiguous) instead of n x k
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
     bias: DeviceBuffer | None = None       # fp32 [n], added to every row of C
@@ -311,6 +312,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.scale_b = options.scale_b.pointer if options.scale_b else 0
     desc.metadata = options.metadata.pointer if options.metadata else 0
     desc.l2_policy = options.l2_policy
+    desc.b_row_major = 1 if options.b_row_major else 0
     desc.bias = options.bias.pointer if options.bias else 0
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 

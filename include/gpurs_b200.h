@@ -184,7 +184,9 @@ typedef struct gpurs_matmul_desc {
                                         128), lda counts kept values (0 = k/2).  0 = dense A */
     int32_t l2_policy;               /* L2 residency hint of the operand loads (dense kernels): 0 library default,
                                         1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 no hints */
-    int32_t reserved;                /* 0 */
+    int32_t b_row_major;             /* 0: B is n x k, k contiguous (the reference's "right_transposed" operand); 1: B is k x n,
+                                        n contiguous (C = A * B with all three row-major), ldb >= n; dense 16-bit and 8-bit tile
+                                        kernels only */
     gpurs_device_ptr bias;           /* optional fp32 [n] added to every row of C before the output rounding (float outputs;
                                         the epilogue of the reference's skinny example, examples/ada/examples/skinny_matrix.rs:60-64) */
 } gpurs_matmul_desc;

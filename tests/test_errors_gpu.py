@@ -75,10 +75,10 @@ def test_tensor_map_encode_checks(gpu):
 
 
 class _Params(C.Structure):
-    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp
+    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp (88 bytes)
     _fields_ = [("c", C.c_uint64), ("ldc", C.c_longlong), ("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("tiles_m", C.c_int),
-                ("tiles_n", C.c_int), ("raster_rows", C.c_int), ("vector_stores", C.c_int), ("status", C.c_uint64),
-                ("scale_a", C.c_uint64), ("scale_b", C.c_uint64)]
+                ("tiles_n", C.c_int), ("raster_rows", C.c_int), ("vector_stores", C.c_int), ("b_row_major", C.c_int), ("status", C.c_uint64),
+                ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("bias", C.c_uint64), ("l2_policy", C.c_int), ("reserved", C.c_int)]
 
 
 class _TensorMap(C.Structure):
@@ -113,7 +113,8 @@ def test_external_module_door(gpu, stream):
     for tensor_map, buffer, rows, box_rows in ((map_a, a, m, 128), (map_b, b, n, 256)):
         dims, strides, box = (C.c_uint64 * 2)(k, rows), (C.c_uint64 * 1)(k * 2), (C.c_uint32 * 2)(64, box_rows)
         assert gpu._lib.gpurs_tensor_map_encode(gpu._handle, C.addressof(tensor_map), G.BF16, 2, buffer.pointer, dims, strides, box, 3, 3) == 0
-    params = _Params(c.pointer, n, m, n, k, m // 128, n // 256, 16, 1, status.pointer, 0, 0)
+    assert C.sizeof(_Params) == 88
+    params = _Params(c=c.pointer, ldc=n, m=m, n=n, k=k, tiles_m=m // 128, tiles_n=n // 256, raster_rows=16, vector_stores=1, status=status.pointer)
     kernel.launch(stream, G.LaunchConfig(grid=(4, 1, 1), block=(192, 1, 1), shared_bytes=shared), [map_a, map_b, params])
     stream.synchronize()
     got = c.download().reshape(m, n).astype(np.float64)

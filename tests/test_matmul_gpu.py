@@ -224,3 +224,32 @@ def test_launches_are_counted_and_status_is_clean(gpu, stream):
     run_matmul(gpu, stream, "bf16", "bf16", a, b, 256, 256, 256)
     assert gpu.launches == before + 1
     assert gpu.status() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("algorithm", ALGORITHMS)
+@pytest.mark.parametrize("kind,out,tolerance", [("f16", "f32", 1e-3), ("bf16", "bf16", 1e-2), ("e4m3", "f32", 1e-3), ("i8", "i32", 0.0)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (200, 304, 144), (384, 768, 1024), (129, 272, 2048)])
+def test_row_major_right_operand(gpu, stream, kind, out, tolerance, shape, algorithm):
+    """C = A * B with B stored k x n (n contiguous), the ordinary row-major product, instead of the reference's
+    n x k "right_transposed" operand: same numbers, the tensor core reads B N-major."""
+    m, n, k = shape
+    a, b = make_operands(kind, m, n, k)
+    b_row_major = np.ascontiguousarray(b.reshape(n, k).T).reshape(-1)
+    got = decode_output(run_matmul(gpu, stream, kind, out, a, b_row_major, m, n, k, algorithm, b_row_major=True), out).reshape(m, n)
+    if kind == "i8":
+        assert np.array_equal(got.astype(np.int64), O.matmul_rows_i8(a, b, n, k, np.arange(m)))
+    else:
+        assert relative_error(got, O.matmul_rows(KINDS[kind][1], a, b, n, k, np.arange(m))) <= tolerance
+
+
+def test_row_major_right_operand_with_pitch(gpu, stream):
+    m, n, k, ldb = 256, 264, 192, 272
+    a, b = make_operands("bf16", m, n, k)
+    padded = np.full(k * ldb, 0x7FC0, np.uint16)        # NaN in the padding columns: never read
+    padded.reshape(k, ldb)[:, :n] = b.reshape(n, k).T
+    got = decode_output(run_matmul(gpu, stream, "bf16", "f32", a, padded, m, n, k, G.ALGO_AUTO, b_row_major=True, ldb=ldb), "f32")
+    assert relative_error(got.reshape(m, n), O.matmul_rows(O.FMT_BF16, a, b, n, k, np.arange(m))) <= 1e-3
+    fa, fb = make_operands("f32", m, n, k)
+    with pytest.raises(G.GpursError) as raised:           # 32-bit operands are read n x k only
+        run_matmul(gpu, stream, "f32", "f32", fa, np.ascontiguousarray(fb.reshape(n, k).T).reshape(-1), m, n, k, G.ALGO_AUTO, b_row_major=True)
+    assert raised.value.code == 100009
