@@ -9,6 +9,7 @@ namespace launcher {
 struct Gemm {
     const char *stem;
     int element_type, element_bytes, output_bytes;
+    int output_type = GPURS_F32;                 // element type of C
     gpurs_device_ptr a, b, c;
     uint64_t lda, ldb, ldc, m, n, k;
     int cta_group, raster_rows, max_ctas;

@@ -120,9 +120,21 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     config.shared_bytes = shared_bytes;
     config.cluster[0] = uint32_t(cta_group);
     config.cluster[1] = config.cluster[2] = 1;
+    // The dense tile kernels also take a descriptor of C: boxes of 32 rows x 128 bytes for their TMA-store epilogue
+    // (used when every row of C starts on a 16-byte boundary; otherwise the descriptor is ignored).
+    const bool takes_output_map = !sparse && g.threads == gemm::NUM_THREADS;
+    alignas(64) CUtensorMap map_c;
+    std::memset(&map_c, 0, sizeof map_c);
+    if (takes_output_map && params.vector_stores == 1) {
+        const uint64_t dims_c[2] = {g.n, g.m}, stride_c[1] = {g.ldc * ob};
+        const uint32_t box_c[2] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32};
+        result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, 2, g.c, dims_c, stride_c, box_c, 3, 3);
+        if (result != GPURS_OK) return result;
+    }
     void *arguments[3] = {&map_a, &map_b, &params};
+    void *dense_arguments[4] = {&map_a, &map_b, &map_c, &params};
     void *sparse_arguments[4] = {&map_a, &map_b, &map_e, &params};
-    return runtime::launch(kernel, stream, &config, sparse ? sparse_arguments : arguments);
+    return runtime::launch(kernel, stream, &config, sparse ? sparse_arguments : takes_output_map ? dense_arguments : arguments);
 }
 
 namespace {
@@ -303,6 +315,7 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.element_type = desc->a_type;
     gemm.element_bytes = choice.element_bytes;
     gemm.output_bytes = choice.output_bytes;
+    gemm.output_type = desc->c_type;
     gemm.a = a, gemm.b = b, gemm.c = c;
     gemm.lda = lda, gemm.ldb = ldb, gemm.ldc = ldc;
     gemm.m = m, gemm.n = n, gemm.k = k;

@@ -24,7 +24,8 @@ struct Params {
     int m, n, k;
     int tiles_m, tiles_n;    // in units of (128 * CTA_GROUP) x BLOCK_N tiles
     int raster_rows;         // tile rows walked together so concurrent tiles share operands in L2
-    int vector_stores;       // 1 when every output row start is 16-byte aligned
+    int vector_stores;       // 1 when every output row start is 16-byte aligned (16-byte stores, and TMA stores where a
+                             // kernel takes a descriptor of C)
     int b_row_major;         // dense kernels: 0 = B is N x K (K contiguous, the reference's layout), 1 = B is K x N (N contiguous)
     unsigned int *status;    // [0] first failure code, [1] block, [2] tile, [3] K-block
     const float *scale_a;    // block-scaled FP8 only: [M][ceil(K/128)]
@@ -57,8 +58,12 @@ struct SharedLayout {
     static constexpr int NUM_BARRIERS = 2 * STAGES + 8;
     static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
-    static constexpr int TOTAL = ABORT_OFFSET + 4;
+    // Epilogue staging for TMA stores: per epilogue warp two buffers of 32 rows x 128 bytes (128-byte swizzle).
+    static constexpr int STAGING_OFFSET = ((ABORT_OFFSET + 4 + 1023) / 1024) * 1024;
+    static constexpr int STAGING_BYTES = EPILOGUE_WARPS * 2 * 32 * ROW_BYTES;
+    static constexpr int TOTAL = STAGING_OFFSET + STAGING_BYTES;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;   // slack to align the stages to 1024 bytes
+    static_assert(DYNAMIC_BYTES <= 232448, "more than the 227 KiB a CTA may have");
 };
 
 // Skinny kernels (gemm_skinny_tcgen05.cuh): 8 stages of 128 rows of the big operand + the padded small one.

@@ -6,8 +6,8 @@
 #define GPURS_GEMM_KERNEL(NAME, KIND, FORMAT, ACC, OUT, BLOCK_N, GROUP, STAGES)                                   \
     extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                           \
     NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                   \
-         const __grid_constant__ gemm::Params params) {                                                          \
-        gemm::gemm_body<KIND, FORMAT, ACC, OUT, BLOCK_N, GROUP, STAGES>(&map_a, &map_b, params);                 \
+         const __grid_constant__ CUtensorMap map_c, const __grid_constant__ gemm::Params params) {               \
+        gemm::gemm_body<KIND, FORMAT, ACC, OUT, BLOCK_N, GROUP, STAGES>(&map_a, &map_b, &map_c, params);         \
     }
 
 // Operand format codes inside each kind: f16 = 0, bf16 = 1, tf32 = 2 (kind f16 / tf32); signed int8 = 1

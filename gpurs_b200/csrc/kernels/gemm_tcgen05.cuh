@@ -68,6 +68,30 @@ __device__ __forceinline__ void tmem_load_columns(uint32_t address, uint32_t (&v
     else ptx::tmem_load_32x64(address, values);
 }
 
+// Adds the optional bias (fp32 per output column) to 32 accumulator columns starting at `column`.
+template <int OUT>
+__device__ __forceinline__ void add_bias(const Params &p, uint32_t (&acc)[32], int column) {
+    if constexpr (OUT != OUT_I32) {
+        if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __ldg(p.bias + column + i));
+        }
+    }
+}
+
+// Two fp32 accumulators rounded to nearest even and packed into one word of bf16 or f16.
+template <int OUT>
+__device__ __forceinline__ uint32_t pack_pair(uint32_t low, uint32_t high) {
+    if constexpr (OUT == OUT_BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(low), __uint_as_float(high));
+        return *reinterpret_cast<uint32_t *>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(__uint_as_float(low), __uint_as_float(high));
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+}
+
 template <int OUT>
 __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column) {
     if (row >= p.m || column >= p.n) return;
@@ -123,7 +147,7 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
 // KIND: ptx::KIND_*; ELEMENT_FORMAT: the 3-bit format code of the operands for that kind;
 // ACC_FORMAT: 1 = f32, 2 = s32; OUT: OUT_*.
 template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES>
-__device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const Params &p) {
+__device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p) {
     using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "two accumulators of BLOCK_N columns must fit 512 TMEM columns");
     constexpr uint32_t TMEM_COLUMNS = 2 * BLOCK_N;
@@ -141,6 +165,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
     auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
     auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 4 + a) * 8; };
+    const uint32_t staging = base + L::STAGING_OFFSET;
 
     const int warp = threadIdx.x / 32;
     const uint32_t lane = ptx::lane_id();
@@ -298,6 +323,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
         const int quadrant = warp % 4;   // the TMEM lanes this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
+        int stores = 0;                  // TMA stores issued by this warp: picks the staging buffer
         for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
@@ -311,12 +337,59 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BLOCK_N;
+            if (p.vector_stores == 1) {
+                // Coalesced path: every 128 bytes of 32 output rows are staged in shared memory (128-byte swizzle, so
+                // the 32 lanes writing their rows do not collide on banks) and written by one TMA store, which also
+                // clips the box at the edges of C.  Two staging buffers per warp: the next box is filled while the
+                // previous store still reads its buffer.
+                constexpr int COLUMNS_PER_BOX = (OUT == OUT_F32 || OUT == OUT_I32) ? 32 : 64;
+                const int warp_row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32;
 #pragma unroll 1
-            for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
-                uint32_t values[32];
-                ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
-                ptx::tmem_load_wait();
-                store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+                for (int box = 0; box < BLOCK_N / COLUMNS_PER_BOX; box++) {
+                    const int column = tile_n * BLOCK_N + box * COLUMNS_PER_BOX;
+                    uint32_t packed[32];
+                    if constexpr (COLUMNS_PER_BOX == 32) {
+                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
+                        ptx::tmem_load_wait();
+                        add_bias<OUT>(p, packed, column);
+                    } else {
+                        uint32_t low[32], high[32];
+                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
+                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
+                        ptx::tmem_load_wait();
+                        add_bias<OUT>(p, low, column);
+                        add_bias<OUT>(p, high, column + 32);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
+                            packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
+                        }
+                    }
+                    if (warp_row < p.m && column < p.n) {    // warp-uniform: boxes wholly outside C are skipped
+                        const uint32_t buffer = staging + uint32_t(((warp - 2) * 2 + (stores & 1)) * 32 * ROW_BYTES);
+                        stores++;
+                        if (lane == 0) ptx::tma_store_wait_read<1>();       // the store that used this buffer two boxes ago
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
+                            ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), packed[4 * j], packed[4 * j + 1],
+                                                 packed[4 * j + 2], packed[4 * j + 3]);
+                        ptx::fence_async_shared();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_2d(map_c, column, warp_row, buffer);
+                            ptx::tma_store_commit();
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+                    uint32_t values[32];
+                    ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
+                    ptx::tmem_load_wait();
+                    store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+                }
             }
             ptx::tcgen05_fence_before();
             __syncwarp();
@@ -326,6 +399,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
     }
 
     // ---------------------------------------------------------------------- teardown

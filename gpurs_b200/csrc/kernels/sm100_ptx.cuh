@@ -351,3 +351,33 @@ __device__ __forceinline__ uint64_t smem_descriptor_mn_major_sw128(uint32_t addr
 }
 
 }  // namespace ptx
+
+namespace ptx {
+
+// ---- TMA stores (shared -> global), tracked in bulk groups of the issuing thread ------------------------
+
+// Makes this thread's earlier writes to shared memory visible to the TMA unit.
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Stores one box from shared memory to the tensor at (x, y); parts of the box outside the tensor are dropped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int32_t x, int32_t y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Waits until at most PENDING of this thread's store groups still read their shared-memory source.
+template <int PENDING>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory"); }
+
+// Waits until at most PENDING of this thread's store groups are incomplete (their writes performed).
+template <int PENDING>
+__device__ __forceinline__ void tma_store_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+__device__ __forceinline__ void store_shared_v4(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+}  // namespace ptx

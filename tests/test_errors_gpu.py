@@ -107,7 +107,7 @@ def test_external_module_door(gpu, stream):
     assert code_of(lambda: module.kernel("no_such_kernel")) == _ffi.E_UNKNOWN_KERNEL
     kernel = module.kernel("gpurs_gemm_bf16_f32_cg1")
     assert 0 < kernel.registers <= 255
-    shared = 4 * (128 * 128 + 256 * 128) + (2 * 4 + 8) * 8 + 8 + 1024
+    shared = 230400 + 1024   # 4 stages of 48 KiB, barriers, 32 KiB of epilogue staging, alignment slack
     kernel.reserve_shared(shared)
     map_a, map_b = _aligned_tensor_map(), _aligned_tensor_map()
     for tensor_map, buffer, rows, box_rows in ((map_a, a, m, 128), (map_b, b, n, 256)):
@@ -115,13 +115,17 @@ def test_external_module_door(gpu, stream):
         assert gpu._lib.gpurs_tensor_map_encode(gpu._handle, C.addressof(tensor_map), G.BF16, 2, buffer.pointer, dims, strides, box, 3, 3) == 0
     assert C.sizeof(_Params) == 88
     params = _Params(c=c.pointer, ldc=n, m=m, n=n, k=k, tiles_m=m // 128, tiles_n=n // 256, raster_rows=16, vector_stores=1, status=status.pointer)
-    kernel.launch(stream, G.LaunchConfig(grid=(4, 1, 1), block=(192, 1, 1), shared_bytes=shared), [map_a, map_b, params])
+    # the dense entries also take a descriptor of C for their TMA-store epilogue: 32 rows x 128 bytes per box
+    map_c = _aligned_tensor_map()
+    dims, strides, box = (C.c_uint64 * 2)(n, m), (C.c_uint64 * 1)(n * 4), (C.c_uint32 * 2)(32, 32)
+    assert gpu._lib.gpurs_tensor_map_encode(gpu._handle, C.addressof(map_c), G.F32, 2, c.pointer, dims, strides, box, 3, 3) == 0
+    kernel.launch(stream, G.LaunchConfig(grid=(4, 1, 1), block=(192, 1, 1), shared_bytes=shared), [map_a, map_b, map_c, params])
     stream.synchronize()
     got = c.download().reshape(m, n).astype(np.float64)
     expected = O.matmul_rows(O.FMT_BF16, a_bits, b_bits, n, k, np.arange(m))
     assert np.abs(got - expected).max() / np.abs(expected).max() < 1e-5
     assert (status.download() == 0).all()
-    assert code_of(lambda: kernel.launch(stream, G.LaunchConfig(grid=(0, 1, 1), block=(192, 1, 1)), [map_a, map_b, params])) == _ffi.E_INVALID_VIEW
+    assert code_of(lambda: kernel.launch(stream, G.LaunchConfig(grid=(0, 1, 1), block=(192, 1, 1)), [map_a, map_b, map_c, params])) == _ffi.E_INVALID_VIEW
 
 
 def test_streams_events_and_copies(gpu):
