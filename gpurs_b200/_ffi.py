@@ -87,6 +87,7 @@ SIGNATURES = {
     "gpurs_metadata_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64]),
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_self_test_timeout": (C.c_int, [_P]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),
     "gpurs_last_error": (C.c_int, [C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), C.POINTER(C.c_char_p)]),

@@ -438,3 +438,19 @@ extern "C" int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t
     void *arguments[6] = {&source_pointer, &source_pitch, &code_pointer, &scale_pointer, &row_count, &depth};
     return runtime::launch(kernel, stream, &config, arguments);
 }
+
+extern "C" int gpurs_self_test_timeout(gpurs_stream *stream) {
+    if (!stream) return fail("gpurs_self_test_timeout", GPURS_E_INVALID_ARGUMENT, "null stream");
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_wait_probe", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = 1;
+    config.block[0] = 32;
+    void *status = reinterpret_cast<void *>(gpu->status);
+    void *arguments[1] = {&status};
+    return runtime::launch(kernel, stream, &config, arguments);
+}

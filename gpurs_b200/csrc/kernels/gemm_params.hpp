@@ -14,6 +14,7 @@ enum : uint32_t {
     STATUS_PRODUCER_TIMEOUT = 1,
     STATUS_MMA_TIMEOUT = 2,
     STATUS_EPILOGUE_TIMEOUT = 3,
+    STATUS_PROBE_TIMEOUT = 4,     // the self-test kernel (diagnostics.cu)
 };
 
 // Kernel parameter block of the tile kernels (after the TMA descriptors).  Hosts that launch an entry themselves

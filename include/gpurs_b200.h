@@ -242,6 +242,11 @@ int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_t n, uint64
  * first bounded wait that gave up.  Synchronises the device. */
 int gpurs_status_read(gpurs_gpu *gpu, uint32_t status[4]);
 
+/* Self-test of the bounded device waits (no counterpart in the reference, whose device waits are unbounded): enqueues a
+ * one-warp kernel whose wait can never be satisfied.  After about 1.5 s the wait gives up, the kernel records status code 4
+ * and returns; the next gpurs_stream_synchronize reports GPURS_E_DEVICE_TIMEOUT and the context stays usable. */
+int gpurs_self_test_timeout(gpurs_stream *stream);
+
 /* Number of kernels this library has launched through `gpu` so far. */
 uint64_t gpurs_launch_count(gpurs_gpu *gpu);
 
