@@ -47,6 +47,7 @@ WORKLOADS = {
     "f32_1024": ("f32", "f32", 1024, 1024, 1024),
     "f16_skinny_16x4096x4096": ("f16", "f32", 16, 4096, 4096),   # the reference's decode-shaped example, bias included
     "f16_skinny_16x16384x16384": ("f16", "f32", 16, 16384, 16384),   # same shape class with a weight (512 MiB) larger than L2
+    "f16_grouped_16384x4096x4096_8e": ("f16", "f16", 16384, 4096, 4096),   # 16384 routed rows over 8 experts (mixture of experts)
     "sparse24_bf16_2048x8192x8192": ("bf16", "bf16", 2048, 8192, 8192),   # one GPU's shard of 16384 x 8192 (2:4) x 8192
 }
 DEFAULT_WORKLOAD = "bf16_8192"
@@ -193,7 +194,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
 
         m = row_shard(m, world, rank)[1]     # the workload's M split over the ranks, B still replicated
     element = {"bf16": G.BF16, "f16": G.F16, "i8": G.I8, "e4m3": G.E4M3, "f32": G.F32}[kind]
-    out_element = {"bf16": G.BF16, "f32": G.F32, "i32": G.I32}[out]
+    out_element = {"bf16": G.BF16, "f16": G.F16, "f32": G.F32, "i32": G.I32}[out]
     element_bytes, out_bytes = G.host.ELEMENT_BYTES[element], G.host.ELEMENT_BYTES[out_element]
 
     dist = None
@@ -236,19 +237,31 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
         options.scale_a = gpu.upload(rng.uniform(3.0, 4.5, m * k_blocks).astype(np.float32) / np.float32(448.0))
         options.scale_b = gpu.upload(rng.uniform(4.0, 5.0, ((n + 127) // 128) * k_blocks).astype(np.float32) / np.float32(448.0))
 
+    launch = lambda: G.matmul(stream, a, b, c, shape, options)
+    if "grouped" in args.workload:
+        # m routed rows over 8 experts of uneven size; activations = m rows, routing a seeded permutation; B holds the 8 weights
+        experts = 8
+        rng = np.random.default_rng(11)
+        counts = rng.multinomial(m, np.ones(experts) / experts)
+        offsets = gpu.upload(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+        routes = gpu.upload(rng.permutation(m).astype(np.int32))
+        b_host = synthetic_operand(kind, experts * n, k, 2)
+        b = gpu.upload(b_host, element)
+        launch = lambda: G.matmul_grouped(stream, a, routes, offsets, b, c, m, m, n, k, experts)
+
     def barrier():
         stream.synchronize()
         if dist is not None:
             dist.barrier()
 
     for _ in range(max(args.warmup, 3)):
-        G.matmul(stream, a, b, c, shape, options)
+        launch()
     barrier()
     launches_before = gpu.launches
     with ClockSampler(local_rank) as clocks:
         start = stream.record_timed()
         for _ in range(args.steps):
-            G.matmul(stream, a, b, c, shape, options)
+            launch()
         end = stream.record_timed()
         stream.synchronize()
     milliseconds = start.elapsed_ms(end)
@@ -281,7 +294,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     def e2e_step():
         stream.copy_to_device(a, pinned[0].value, a_host.nbytes)
         stream.copy_to_device(b, pinned[1].value, b_host.nbytes)
-        G.matmul(stream, a, b, c, shape, options)
+        launch()
         stream.copy_to_host(pinned[2].value, c, m * n * out_bytes)
 
     e2e_step()

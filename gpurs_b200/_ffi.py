@@ -46,6 +46,11 @@ class MatmulDesc(C.Structure):
     ]
 
 
+class GroupedDesc(C.Structure):
+    _fields_ = [("a_type", C.c_int32), ("c_type", C.c_int32), ("rows", C.c_uint64), ("tokens", C.c_uint64), ("n", C.c_uint64),
+                ("k", C.c_uint64), ("experts", C.c_uint64), ("lda", C.c_uint64), ("ldc", C.c_uint64)]
+
+
 _P = C.c_void_p
 _PP = C.POINTER(C.c_void_p)
 _U64P = C.POINTER(C.c_uint64)
@@ -87,6 +92,7 @@ SIGNATURES = {
     "gpurs_metadata_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64]),
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_matmul_grouped": (C.c_int, [_P, C.POINTER(GroupedDesc), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_self_test_timeout": (C.c_int, [_P]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),

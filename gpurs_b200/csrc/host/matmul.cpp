@@ -454,3 +454,76 @@ extern "C" int gpurs_self_test_timeout(gpurs_stream *stream) {
     void *arguments[1] = {&status};
     return runtime::launch(kernel, stream, &config, arguments);
 }
+
+namespace {
+// Host mirror of gemm::GroupedParams (kernels/gemm_grouped_tcgen05.cuh).
+struct GroupedParams {
+    void *c;
+    long long ldc;
+    const void *input;
+    long long lda;
+    const unsigned int *routes;
+    const unsigned int *offsets;
+    unsigned int *status;
+    int rows, tokens, n, k, experts, tiles_n, vector_stores;
+};
+}  // namespace
+
+extern "C" int gpurs_matmul_grouped(gpurs_stream *stream, const gpurs_grouped_desc *desc, gpurs_device_ptr input, gpurs_device_ptr routes,
+                                    gpurs_device_ptr offsets, gpurs_device_ptr weight, gpurs_device_ptr output) {
+    const char *const op = "gpurs_matmul_grouped";
+    if (!stream || !desc) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream or descriptor");
+    if (desc->a_type != GPURS_F16 && desc->a_type != GPURS_BF16) return fail(op, GPURS_E_INVALID_ARGUMENT, "16-bit operands only");
+    if (desc->c_type != desc->a_type && desc->c_type != GPURS_F32) return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported output type");
+    const uint64_t rows = desc->rows, tokens = desc->tokens, n = desc->n, k = desc->k, experts = desc->experts;
+    if (rows > 0x7fffffffull || tokens > 0x7fffffffull || k > 0x7fffffffull || experts > 65536 || experts * n > 0x7fffffffull)
+        return fail(op, GPURS_E_SIZE_OVERFLOW, "a dimension exceeds what the kernel indexes");
+    if (rows == 0 || n == 0 || experts == 0) return GPURS_OK;
+    if (k == 0 || tokens == 0) return fail(op, GPURS_E_INVALID_VIEW, "empty depth or no input rows");
+    const uint64_t lda = desc->lda ? desc->lda : k, ldc = desc->ldc ? desc->ldc : n;
+    if (lda < k || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (!input || !routes || !offsets || !weight || !output) return fail(op, GPURS_E_INVALID_ARGUMENT, "null argument");
+    const uint64_t ob = desc->c_type == GPURS_F32 ? 4 : 2;
+    if (k % 8 || input % 16 || weight % 16 || (lda * 2) % 16 || routes % 4 || offsets % 4 || output % ob)
+        return fail(op, GPURS_E_INVALID_VIEW, "k must be a multiple of 8, operands 16-byte aligned with 16-byte row pitches");
+    const uint64_t out_bytes = ((rows - 1) * ldc + n) * ob;
+    if (overlap(output, out_bytes, input, ((tokens - 1) * lda + k) * 2) || overlap(output, out_bytes, weight, experts * n * k * 2) ||
+        overlap(output, out_bytes, routes, rows * 4) || overlap(output, out_bytes, offsets, (experts + 1) * 4))
+        return fail(op, GPURS_E_ALIASING, "the output overlaps an input");
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    char name[96];
+    std::snprintf(name, sizeof name, "gpurs_gemm_grouped_%s_%s", desc->a_type == GPURS_F16 ? "f16" : "bf16",
+                  desc->c_type == GPURS_F32 ? "f32" : (desc->a_type == GPURS_F16 ? "f16" : "bf16"));
+    const uint32_t shared_bytes = gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
+    if (result != GPURS_OK) return result;
+    alignas(64) CUtensorMap map_w;
+    const uint64_t dims_w[2] = {k, experts * n}, stride_w[1] = {k * 2};
+    const uint32_t box_w[2] = {64, uint32_t(gemm::BLOCK_N)};
+    result = gpurs_tensor_map_encode(gpu, &map_w, desc->a_type, 2, weight, dims_w, stride_w, box_w, 3, 3);
+    if (result != GPURS_OK) return result;
+    GroupedParams params;
+    std::memset(&params, 0, sizeof params);
+    params.c = reinterpret_cast<void *>(output);
+    params.ldc = (long long)ldc;
+    params.input = reinterpret_cast<const void *>(input);
+    params.lda = (long long)lda;
+    params.routes = reinterpret_cast<const unsigned int *>(routes);
+    params.offsets = reinterpret_cast<const unsigned int *>(offsets);
+    params.status = reinterpret_cast<unsigned int *>(gpu->status);
+    params.rows = int(rows), params.tokens = int(tokens), params.n = int(n), params.k = int(k), params.experts = int(experts);
+    params.tiles_n = int((n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
+    params.vector_stores = (output % 16 == 0 && (ldc * ob) % 16 == 0) ? 1 : 0;
+    // The tile count depends on the offsets, which live on the device: at most one ragged tile per expert beyond
+    // rows / 128.  The persistent blocks stop at the real count.
+    const uint64_t tile_bound = ((rows + gemm::BLOCK_M - 1) / gemm::BLOCK_M + experts) * uint64_t(params.tiles_n);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::min<uint64_t>(tile_bound, uint64_t(gpu->multiprocessors)));
+    config.block[0] = gemm::GROUPED_THREADS;
+    config.shared_bytes = shared_bytes;
+    void *arguments[2] = {&map_w, &params};
+    return runtime::launch(kernel, stream, &config, arguments);
+}

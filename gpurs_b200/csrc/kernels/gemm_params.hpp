@@ -42,6 +42,7 @@ constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swi
 constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma
 constexpr int NUM_THREADS = 192;
 constexpr int EPILOGUE_WARPS = 4;
+constexpr int GROUPED_THREADS = 320;  // grouped kernel: weight producer, MMA issuer, 4 epilogue warps, 4 gather warps
 constexpr int SCALED_THREADS = 384;  // promotion kernels: warpgroup 0 (producer warp, MMA warp, two idle), 8 promotion warps
 constexpr int BLOCK_N = 256;       // columns per tile
 constexpr int STAGES_SINGLE = 4;   // pipeline depth of the one-CTA kernels (48 KiB per stage)

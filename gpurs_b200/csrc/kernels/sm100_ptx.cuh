@@ -381,3 +381,20 @@ __device__ __forceinline__ void store_shared_v4(uint32_t address, uint32_t a, ui
 }
 
 }  // namespace ptx
+
+namespace ptx {
+
+// ---- per-thread asynchronous copies (global -> shared, 16 bytes), for gathered rows --------------------
+
+// Copies `valid` (0 or 16) bytes from `source` and fills the rest of the 16 with zeros; does not block.
+__device__ __forceinline__ void copy_async_16(uint32_t dst, const void *source, uint32_t valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(source), "r"(valid) : "memory");
+}
+
+// Arrives on `bar` once every copy_async_16 this thread has issued so far has landed.  Counts as one of the
+// arrivals the barrier was initialised to expect.
+__device__ __forceinline__ void copy_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+}  // namespace ptx

@@ -317,6 +317,16 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 
+def matmul_grouped(stream: Stream, inputs: DeviceBuffer, routes: DeviceBuffer, offsets: DeviceBuffer, weight: DeviceBuffer,
+                   output: DeviceBuffer, rows: int, tokens: int, n: int, k: int, experts: int) -> None:
+    """output[r] = inputs[routes[r]] @ weight[e]^T for offsets[e] <= r < offsets[e + 1]: the grouped (mixture-of-experts)
+    product of the reference's `experts` example (examples/ada/examples/grouped_matrix.rs:30-60).  `routes` and `offsets`
+    are I32 buffers holding unsigned values; weight is [experts][n][k]."""
+    desc = _ffi.GroupedDesc(inputs.element, output.element, rows, tokens, n, k, experts, 0, 0)
+    _check(stream.gpu._lib.gpurs_matmul_grouped(stream._handle, C.byref(desc), inputs.pointer, routes.pointer, offsets.pointer,
+                                                weight.pointer, output.pointer))
+
+
 def quantize_e4m3(stream: Stream, source: DeviceBuffer, rows: int, k: int, block_rows: int, ld: int = 0):
     """Block quantisation of a rows x k fp32 matrix on the device: returns (codes, scales) with one fp32 scale per
     block_rows x 128 block (block_rows = 1 for the left operand of a block-scaled product, 128 for the right one)."""

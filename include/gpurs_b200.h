@@ -238,6 +238,22 @@ int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_t m, uint64
 int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_t n, uint64_t k, gpurs_device_ptr a,
                             gpurs_device_ptr b, gpurs_device_ptr c);
 
+/* ---- grouped (mixture-of-experts) product ----------------------------------------------------------- */
+
+/* output[r, :] = input[routes[r], :] * weight[e]^T for offsets[e] <= r < offsets[e + 1]: the reference's `experts`
+ * example (examples/ada/examples/grouped_matrix.rs:30-60).  input is tokens x k, weight [experts][n][k] (k contiguous),
+ * output rows x n, all row-major; routes (u32 [rows]) and offsets (u32 [experts + 1], ascending, offsets[experts] <= rows)
+ * live on the device.  Route values beyond tokens - 1 are clamped. */
+typedef struct gpurs_grouped_desc {
+    int32_t a_type;       /* GPURS_F16 or GPURS_BF16 (input and weight) */
+    int32_t c_type;       /* the same 16-bit type, or GPURS_F32 */
+    uint64_t rows, tokens, n, k, experts;
+    uint64_t lda, ldc;    /* row pitches of input and output in elements; 0 = contiguous */
+} gpurs_grouped_desc;
+
+int gpurs_matmul_grouped(gpurs_stream *stream, const gpurs_grouped_desc *desc, gpurs_device_ptr input, gpurs_device_ptr routes,
+                         gpurs_device_ptr offsets, gpurs_device_ptr weight, gpurs_device_ptr output);
+
 /* Reads and clears the device status word: [0] code (0 = none), [1] block, [2] tile, [3] K-block of the
  * first bounded wait that gave up.  Synchronises the device. */
 int gpurs_status_read(gpurs_gpu *gpu, uint32_t status[4]);
