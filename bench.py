@@ -347,6 +347,37 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
         gather_ms = float(worst.item()) / args.steps
         gather = {"ms_per_step": gather_ms, "value": world * flops_per_step / (gather_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                   "bytes_received_per_gpu": int((world - 1) * shard_bytes), "collective": "ncclAllGather, in place, after the GEMM on the same stream"}
+        # The same result from ONE kernel per GPU: the epilogue stores every box of C into all GPUs' copies over NVLink.
+        dense_tiles = not any(word in args.workload for word in ("sparse24", "grouped", "skinny", "e4m3_scaled"))
+        if dense_tiles and (kind, out) in (("bf16", "bf16"), ("i8", "i32"), ("f16", "f32"), ("e4m3", "bf16")):
+            def exchange(handle):
+                handles = [None] * world
+                dist.all_gather_object(handles, handle)
+                return handles
+
+            gathered = G.GatheredMatrix(gpu, out_element, world * m, n, rank, world, exchange)
+            fused_step = lambda: G.matmul_allgather(stream, a, b, gathered, shape, rank * m, options)
+            for _ in range(3):
+                fused_step()
+            barrier()
+            start = stream.record_timed()
+            for _ in range(args.steps):
+                fused_step()
+            end = stream.record_timed()
+            stream.synchronize()
+            worst = torch.tensor([start.elapsed_ms(end)], device="cuda")
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            fused_ms = float(worst.item()) / args.steps
+            # every rank's copy must equal what the collective gathered, bit for bit
+            same = bool(np.array_equal(gathered.local.download().view(np.uint8), full.cpu().numpy()))
+            agree = torch.tensor([1 if same else 0], device="cuda")
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            gather["fused"] = {"ms_per_step": fused_ms, "value": world * flops_per_step / (fused_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                               "bytes_sent_per_gpu": int((world - 1) * shard_bytes), "equals_collective_result": bool(agree.item()),
+                               "how": "gpurs_matmul_allgather: one kernel per GPU, remote TMA stores from the epilogue"}
+            dist.barrier()
+            gathered.close()
         del c_block, borrowed
     status = gpu.status()
 

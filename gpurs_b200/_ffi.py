@@ -51,6 +51,11 @@ class GroupedDesc(C.Structure):
                 ("k", C.c_uint64), ("experts", C.c_uint64), ("lda", C.c_uint64), ("ldc", C.c_uint64)]
 
 
+class GatherDesc(C.Structure):
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("row_offset", C.c_uint64), ("total_rows", C.c_uint64),
+                ("ld_full", C.c_uint64), ("full", C.c_uint64 * 8)]
+
+
 _P = C.c_void_p
 _PP = C.POINTER(C.c_void_p)
 _U64P = C.POINTER(C.c_uint64)
@@ -79,6 +84,9 @@ SIGNATURES = {
     "gpurs_fill_u8": (C.c_int, [_P, C.c_uint64, C.c_uint8, C.c_size_t]),
     "gpurs_host_alloc": (C.c_int, [_P, C.c_size_t, _PP]),
     "gpurs_host_free": (C.c_int, [_P, _P]),
+    "gpurs_ipc_export": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_uint8)]),
+    "gpurs_ipc_open": (C.c_int, [_P, C.POINTER(C.c_uint8), _U64P]),
+    "gpurs_ipc_close": (C.c_int, [_P, C.c_uint64]),
     "gpurs_tensor_map_encode": (C.c_int, [_P, _P, C.c_int, C.c_uint32, C.c_uint64, _U64P, _U64P, C.POINTER(C.c_uint32), C.c_int, C.c_int]),
     "gpurs_module_load": (C.c_int, [_P, _P, C.c_size_t, _PP]),
     "gpurs_module_free": (None, [_P]),
@@ -93,6 +101,7 @@ SIGNATURES = {
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_grouped": (C.c_int, [_P, C.POINTER(GroupedDesc), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_matmul_allgather": (C.c_int, [_P, C.POINTER(MatmulDesc), C.POINTER(GatherDesc), C.c_uint64, C.c_uint64]),
     "gpurs_self_test_timeout": (C.c_int, [_P]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),

@@ -34,6 +34,9 @@ namespace driver {
     X(cuMemsetD8Async)            \
     X(cuMemHostAlloc)             \
     X(cuMemFreeHost)              \
+    X(cuIpcGetMemHandle)          \
+    X(cuIpcOpenMemHandle)         \
+    X(cuIpcCloseMemHandle)        \
     X(cuTensorMapEncodeTiled)     \
     X(cuModuleLoadData)           \
     X(cuModuleUnload)             \

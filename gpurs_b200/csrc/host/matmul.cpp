@@ -34,6 +34,13 @@ bool choose(int a_type, int c_type, Choice &choice) {
     return false;
 }
 
+// Host mirror of gemm::PushTargets (kernels/gemm_tcgen05.cuh).
+struct PushTargets {
+    alignas(64) CUtensorMap maps[gemm::MAX_PUSH_TARGETS];
+    int count;
+    int row_offset;
+};
+
 // Half-open byte ranges [begin, end) overlap?
 bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { return a < b + b_bytes && b < a + a_bytes; }
 
@@ -46,7 +53,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const int cta_group = g.cta_group;
     const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
     char name[96];
-    std::snprintf(name, sizeof name, "%s_cg%d", g.stem, cta_group);
+    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : "%s_cg%d", g.stem, cta_group);
     const bool sparse = g.metadata != 0;
     const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
                                   : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
@@ -130,6 +137,22 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         const uint32_t box_c[2] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32};
         result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, 2, g.c, dims_c, stride_c, box_c, 3, 3);
         if (result != GPURS_OK) return result;
+    }
+    if (g.gather) {
+        // One descriptor of the whole gathered matrix per GPU; the kernel stores each box of its block to all of them.
+        PushTargets targets;
+        std::memset(&targets, 0, sizeof targets);
+        const uint64_t pitch = g.gather->ld_full ? g.gather->ld_full : g.n;
+        const uint64_t dims_c[2] = {g.n, g.gather->total_rows}, stride_c[1] = {pitch * ob};
+        const uint32_t box_c[2] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32};
+        for (uint32_t t = 0; t < g.gather->world; t++) {
+            result = gpurs_tensor_map_encode(gpu, &targets.maps[t], g.output_type, 2, g.gather->full[t], dims_c, stride_c, box_c, 3, 3);
+            if (result != GPURS_OK) return result;
+        }
+        targets.count = int(g.gather->world);
+        targets.row_offset = int(g.gather->row_offset);
+        void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
+        return runtime::launch(kernel, stream, &config, push_arguments);
     }
     void *arguments[3] = {&map_a, &map_b, &params};
     void *dense_arguments[4] = {&map_a, &map_b, &map_c, &params};
@@ -232,9 +255,12 @@ int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gp
 
 }  // namespace
 
-extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
-                            gpurs_device_ptr c) {
-    const char *const op = "gpurs_matmul";
+namespace {
+
+// The checks and the dispatch shared by gpurs_matmul and gpurs_matmul_allgather (`gather` non-null: C is this call's
+// block of rows of a matrix that every GPU of the box keeps, and the kernel stores the block to all of them).
+int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
+                   gpurs_device_ptr c, const gpurs_gather_desc *gather) {
     if (!stream || !desc) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream or descriptor");
     gpurs_gpu *gpu = stream->gpu;
     Choice choice;
@@ -269,8 +295,12 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     int result = GPURS_OK;
     if (k == 0) {
         // An empty sum: the product is all zeros.
-        for (uint64_t row = 0; row < (ldc == n ? 1 : m); row++)
-            GPURS_TRY(gpu->api, cuMemsetD8Async(c + row * ldc * ob, 0, (ldc == n ? m * n : n) * ob, stream->handle));
+        // (for a gathering product: the block of every GPU's copy)
+        for (uint32_t target = 0; target < (gather ? gather->world : 1u); target++) {
+            const gpurs_device_ptr block = gather ? c - gather->full[gather->rank] + gather->full[target] : c;
+            for (uint64_t row = 0; row < (ldc == n ? 1 : m); row++)
+                GPURS_TRY(gpu->api, cuMemsetD8Async(block + row * ldc * ob, 0, (ldc == n ? m * n : n) * ob, stream->handle));
+        }
         return GPURS_OK;
     }
     if (!a || !b) return fail(op, GPURS_E_INVALID_ARGUMENT, "null operand");
@@ -302,6 +332,16 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
         return fail(op, GPURS_E_INVALID_ARGUMENT, "a k x n right operand is supported by the dense 16-bit and 8-bit tile kernels only");
     if (group == GPURS_ALGO_SKINNY && !skinny_possible)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm needs m <= 64, 16-bit dense operands and fp32 output");
+    if (gather) {
+        // The push epilogue exists for the CTA-pair tile kernels of these type pairs, and it stores whole boxes of 32 rows.
+        const bool typed = (desc->a_type == GPURS_BF16 && desc->c_type == GPURS_BF16) || (desc->a_type == GPURS_F16 && desc->c_type == GPURS_F32) ||
+                           (desc->a_type == GPURS_I8 && desc->c_type == GPURS_I32) || (desc->a_type == GPURS_E4M3 && desc->c_type == GPURS_BF16);
+        if (!typed || sparse || promoted)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product supports dense bf16->bf16, f16->f32, i8->i32 and unscaled e4m3->bf16");
+        if (group != GPURS_ALGO_AUTO && group != GPURS_ALGO_CTA_PAIR)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product runs on the CTA-pair kernels only");
+        group = GPURS_ALGO_CTA_PAIR;
+    }
     if (group == GPURS_ALGO_AUTO && skinny_possible) group = GPURS_ALGO_SKINNY;
     if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR && group != GPURS_ALGO_SKINNY)
@@ -324,6 +364,7 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
     gemm.max_ctas = desc->max_ctas;
     gemm.bias = desc->bias;
     gemm.b_row_major = b_row_major;
+    gemm.gather = gather;
     if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
     if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
     gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints
@@ -363,6 +404,48 @@ extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc,
         return result != GPURS_OK ? result : released;
     }
     return launch_gemm(stream, gemm);
+}
+
+}  // namespace
+
+extern "C" int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
+                            gpurs_device_ptr c) {
+    return matmul_checked("gpurs_matmul", stream, desc, a, b, c, nullptr);
+}
+
+extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_desc *desc, const gpurs_gather_desc *gather,
+                                      gpurs_device_ptr a, gpurs_device_ptr b) {
+    const char *const op = "gpurs_matmul_allgather";
+    if (!stream || !desc || !gather) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream or descriptor");
+    if (gather->world < 1 || gather->world > uint32_t(gemm::MAX_PUSH_TARGETS) || gather->rank >= gather->world)
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "world must be 1..8 and rank below it");
+    const uint64_t m = desc->m, n = desc->n;
+    const uint64_t pitch = gather->ld_full ? gather->ld_full : n;
+    if (pitch < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (gather->total_rows > 0x7fffffffull) return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
+    if (gather->row_offset > gather->total_rows || m > gather->total_rows - gather->row_offset)
+        return fail(op, GPURS_E_LENGTH_MISMATCH, "the block of rows does not fit in the gathered matrix");
+    // The epilogue stores boxes of 32 rows: a block that ended inside a box would overwrite the next block's first rows.
+    if (gather->row_offset + m != gather->total_rows && m % 32)
+        return fail(op, GPURS_E_INVALID_VIEW, "every block of rows but the last must be a multiple of 32 rows");
+    if (desc->ldc && desc->ldc != pitch) return fail(op, GPURS_E_INVALID_VIEW, "ldc must be 0 or the pitch of the gathered matrix");
+    const uint64_t ob = (desc->c_type == GPURS_BF16 || desc->c_type == GPURS_F16) ? 2 : 4;
+    for (uint32_t t = 0; t < gather->world; t++) {
+        if (!gather->full[t]) return fail(op, GPURS_E_INVALID_ARGUMENT, "null output");
+        if (gather->full[t] % 16 || (pitch * ob) % 16)
+            return fail(op, GPURS_E_INVALID_VIEW, "the gathered matrices need 16-byte aligned bases and row pitches");
+    }
+    // No copy of the result may lie over an operand (the rank's own copy is checked again with exact extents below).
+    const uint64_t eb = desc->a_type == GPURS_F32 ? 4 : (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) ? 2 : 1;
+    const uint64_t a_bytes = m * (desc->lda ? desc->lda : desc->k) * eb;
+    const uint64_t b_bytes = (desc->b_row_major == 1 ? desc->k * (desc->ldb ? desc->ldb : n) : n * (desc->ldb ? desc->ldb : desc->k)) * eb;
+    for (uint32_t t = 0; t < gather->world; t++)
+        if (overlap(gather->full[t], gather->total_rows * pitch * ob, a, a_bytes) || overlap(gather->full[t], gather->total_rows * pitch * ob, b, b_bytes))
+            return fail(op, GPURS_E_ALIASING, "the output overlaps an operand");
+    gpurs_matmul_desc local = *desc;
+    local.ldc = pitch;
+    local.c_len = 0;
+    return matmul_checked(op, stream, &local, a, b, gather->full[gather->rank] + gather->row_offset * pitch * ob, gather);
 }
 
 extern "C" size_t gpurs_metadata_bytes(uint64_t m, uint64_t k) {

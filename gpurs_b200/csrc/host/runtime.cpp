@@ -427,6 +427,37 @@ int gpurs_host_free(gpurs_gpu *gpu, void *pointer) {
     return GPURS_OK;
 }
 
+// ---- inter-process memory --------------------------------------------------------------------------
+
+int gpurs_ipc_export(gpurs_gpu *gpu, gpurs_device_ptr pointer, uint8_t handle[64]) {
+    if (!gpu || !pointer || !handle) return fail("gpurs_ipc_export", GPURS_E_INVALID_ARGUMENT, "null argument");
+    static_assert(sizeof(CUipcMemHandle) == 64, "the handle is 64 bytes");
+    Enter enter(gpu);
+    CUipcMemHandle raw;
+    GPURS_TRY(gpu->api, cuIpcGetMemHandle(&raw, pointer));
+    std::memcpy(handle, &raw, sizeof raw);
+    return GPURS_OK;
+}
+
+int gpurs_ipc_open(gpurs_gpu *gpu, const uint8_t handle[64], gpurs_device_ptr *out) {
+    if (!gpu || !handle || !out) return fail("gpurs_ipc_open", GPURS_E_INVALID_ARGUMENT, "null argument");
+    Enter enter(gpu);
+    CUipcMemHandle raw;
+    std::memcpy(&raw, handle, sizeof raw);
+    CUdeviceptr pointer = 0;
+    GPURS_TRY(gpu->api, cuIpcOpenMemHandle(&pointer, raw, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS));
+    *out = pointer;
+    return GPURS_OK;
+}
+
+int gpurs_ipc_close(gpurs_gpu *gpu, gpurs_device_ptr pointer) {
+    if (!gpu) return fail("gpurs_ipc_close", GPURS_E_INVALID_ARGUMENT, "null gpu");
+    if (!pointer) return GPURS_OK;
+    Enter enter(gpu);
+    GPURS_TRY(gpu->api, cuIpcCloseMemHandle(pointer));
+    return GPURS_OK;
+}
+
 // ---- TMA descriptors ----------------------------------------------------------------------------
 
 int gpurs_tensor_map_encode(gpurs_gpu *gpu, void *descriptor, int element_type, uint32_t rank, gpurs_device_ptr address,

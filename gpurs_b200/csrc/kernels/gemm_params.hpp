@@ -37,6 +37,8 @@ struct Params {
 };
 static_assert(sizeof(Params) == 88, "the parameter block is part of the kernel image's interface");
 
+constexpr int MAX_PUSH_TARGETS = 8;   // GPUs of one box
+
 constexpr int BLOCK_M = 128;       // rows per CTA (= TMEM lanes)
 constexpr int ROW_BYTES = 128;     // bytes of K per stage row: one 128-byte swizzle span
 constexpr int MMA_K_BYTES = 32;    // bytes of K per tcgen05.mma

@@ -24,3 +24,17 @@ GPURS_GEMM_PAIR(gpurs_gemm_tf32_f32, ptx::KIND_TF32, 2, 1, gemm::OUT_F32)
 GPURS_GEMM_PAIR(gpurs_gemm_i8_i32, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
 GPURS_GEMM_PAIR(gpurs_gemm_e4m3_f32, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_F32)
 GPURS_GEMM_PAIR(gpurs_gemm_e4m3_bf16, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)
+
+// "Push" entries: the CTA-pair kernels with an epilogue that stores every box of C to all GPUs of the box (see
+// gemm::PushTargets).  They require 16-byte aligned output rows (the TMA-store epilogue).
+#define GPURS_GEMM_PUSH_KERNEL(NAME, KIND, FORMAT, ACC, OUT)                                                        \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                              \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                      \
+         const __grid_constant__ gemm::PushTargets targets, const __grid_constant__ gemm::Params params) {          \
+        gemm::gemm_body<KIND, FORMAT, ACC, OUT, gemm::BLOCK_N, 2, gemm::STAGES_PAIR, true>(&map_a, &map_b, nullptr, params, &targets); \
+    }
+
+GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_bf16_bf16_push_cg2, ptx::KIND_F16, 1, 1, gemm::OUT_BF16)
+GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_f16_f32_push_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F32)
+GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_i8_i32_push_cg2, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
+GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_e4m3_bf16_push_cg2, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)

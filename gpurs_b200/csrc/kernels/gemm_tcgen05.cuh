@@ -28,6 +28,16 @@
 
 namespace gemm {
 
+// Destinations of the "push" epilogue of an M-sharded product: a descriptor of the whole gathered matrix on every GPU
+// of the box (this GPU's own copy included).  Every finished box of C is stored to all of them, `row_offset` rows down,
+// so that when the kernels of all ranks have finished every GPU holds the complete matrix: the all-gather that would
+// follow the GEMM rides on the GEMM's own epilogue, tile by tile, as plain remote stores over NVLink.
+struct PushTargets {
+    CUtensorMap maps[MAX_PUSH_TARGETS];
+    int count;
+    int row_offset;
+};
+
 // Instruction descriptor: accumulator format (1 = f32, 2 = s32) at bit 4, A and B element formats at
 // bits 7 and 10, both operands K-major, N/8 at bit 17, M/16 at bit 24 (M counts both CTAs of a pair).
 __host__ __device__ constexpr uint32_t instruction_descriptor(int accumulator_format, int element_format, int mma_m, int mma_n) {
@@ -146,8 +156,9 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
 
 // KIND: ptx::KIND_*; ELEMENT_FORMAT: the 3-bit format code of the operands for that kind;
 // ACC_FORMAT: 1 = f32, 2 = s32; OUT: OUT_*.
-template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES>
-__device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p) {
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false>
+__device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p,
+                                          const PushTargets *targets = nullptr) {
     using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
     static_assert(BLOCK_N == 128 || BLOCK_N == 256, "two accumulators of BLOCK_N columns must fit 512 TMEM columns");
     constexpr uint32_t TMEM_COLUMNS = 2 * BLOCK_N;
@@ -377,7 +388,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         ptx::fence_async_shared();
                         __syncwarp();
                         if (lane == 0) {
-                            ptx::tma_store_2d(map_c, column, warp_row, buffer);
+                            if constexpr (PUSH) {
+                                // one staged box, one store per GPU of the box (remote ones travel over NVLink)
+                                for (int t = 0; t < targets->count; t++) ptx::tma_store_2d(&targets->maps[t], column, targets->row_offset + warp_row, buffer);
+                            } else {
+                                ptx::tma_store_2d(map_c, column, warp_row, buffer);
+                            }
                             ptx::tma_store_commit();
                         }
                     }

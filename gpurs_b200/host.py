@@ -317,6 +317,63 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 
+class GatheredMatrix:
+    """A total_rows x n matrix of which every GPU of one box keeps a copy.  Each process allocates its own copy and maps
+    the others' through CUDA IPC; `exchange(handle: bytes) -> list[bytes]` hands this rank's 64-byte handle to the other
+    ranks and returns all ranks' handles in rank order (an all-gather of objects of any process group will do).
+
+    No counterpart in the reference, which drives one GPU."""
+
+    def __init__(self, gpu: "Gpu", element: int, total_rows: int, n: int, rank: int, world: int, exchange):
+        self.gpu, self.element, self.total_rows, self.n, self.rank, self.world = gpu, element, total_rows, n, rank, world
+        self.local = gpu.zeros(element, total_rows * n)
+        handle = (C.c_uint8 * 64)()
+        _check(gpu._lib.gpurs_ipc_export(gpu._handle, self.local.pointer, handle))
+        handles = exchange(bytes(handle))
+        if len(handles) != world:
+            raise ValueError("exchange must return one handle per rank")
+        self.pointers = []
+        for peer, raw in enumerate(handles):
+            if peer == rank:
+                self.pointers.append(self.local.pointer)
+                continue
+            pointer = C.c_uint64()
+            _check(gpu._lib.gpurs_ipc_open(gpu._handle, (C.c_uint8 * 64).from_buffer_copy(raw), C.byref(pointer)))
+            self.pointers.append(pointer.value)
+
+    def close(self) -> None:
+        """Unmap the peers' copies.  Call on every rank, after the last product into the matrix has completed everywhere."""
+        for peer, pointer in enumerate(self.pointers):
+            if peer != self.rank and pointer and self.gpu._handle:
+                self.gpu._lib.gpurs_ipc_close(self.gpu._handle, pointer)
+        self.pointers = []
+
+
+def matmul_allgather(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, gathered: GatheredMatrix, shape, row_offset: int,
+                     options: MatmulOptions | None = None) -> None:
+    """This rank's block of rows of the gathered matrix, C[row_offset : row_offset + m, :] = A[m, k] * B[n, k]^T, computed
+    and stored into EVERY rank's copy by one kernel (the all-gather rides on the GEMM's epilogue as remote stores over
+    NVLink).  The matrix is complete everywhere once every rank has synchronised its stream and the ranks have met at
+    a barrier.  shape = [m, n, k] of the local product."""
+    options = options or MatmulOptions()
+    m, n, k = (int(x) for x in shape)
+    if n != gathered.n:
+        raise GpursErrorLocal(_ffi.E_INVALID_ARGUMENT, "n differs from the gathered matrix")
+    desc = _ffi.MatmulDesc()
+    desc.a_type, desc.c_type = a.element, gathered.element
+    desc.m, desc.n, desc.k = m, n, k
+    desc.lda, desc.ldb = options.lda, options.ldb
+    desc.a_len, desc.b_len = a.len, b.len
+    desc.algorithm, desc.max_ctas, desc.raster_rows = options.algorithm, options.max_ctas, options.raster_rows
+    desc.b_row_major = 1 if options.b_row_major else 0
+    desc.bias = options.bias.pointer if options.bias else 0
+    gather = _ffi.GatherDesc()
+    gather.world, gather.rank, gather.row_offset, gather.total_rows, gather.ld_full = gathered.world, gathered.rank, row_offset, gathered.total_rows, 0
+    for peer, pointer in enumerate(gathered.pointers):
+        gather.full[peer] = pointer
+    _check(stream.gpu._lib.gpurs_matmul_allgather(stream._handle, C.byref(desc), C.byref(gather), a.pointer, b.pointer))
+
+
 def matmul_grouped(stream: Stream, inputs: DeviceBuffer, routes: DeviceBuffer, offsets: DeviceBuffer, weight: DeviceBuffer,
                    output: DeviceBuffer, rows: int, tokens: int, n: int, k: int, experts: int) -> None:
     """output[r] = inputs[routes[r]] @ weight[e]^T for offsets[e] <= r < offsets[e + 1]: the grouped (mixture-of-experts)

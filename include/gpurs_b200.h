@@ -109,6 +109,16 @@ int gpurs_fill_u8(gpurs_stream *stream, gpurs_device_ptr destination, uint8_t va
 int gpurs_host_alloc(gpurs_gpu *gpu, size_t bytes, void **out);
 int gpurs_host_free(gpurs_gpu *gpu, void *pointer);
 
+/* ---- sharing device memory between the processes of one box (no counterpart in the reference, which is
+ *      single-process and single-GPU) ------------------------------------------------------------------ */
+
+/* A 64-byte handle another process on the same machine can open to reach `pointer` (an allocation made with
+ * gpurs_alloc / gpurs_upload / gpurs_zeros), and the reverse.  A pointer returned by gpurs_ipc_open addresses the peer
+ * GPU's memory over NVLink and must be closed before the owner frees the allocation. */
+int gpurs_ipc_export(gpurs_gpu *gpu, gpurs_device_ptr pointer, uint8_t handle[64]);
+int gpurs_ipc_open(gpurs_gpu *gpu, const uint8_t handle[64], gpurs_device_ptr *out);
+int gpurs_ipc_close(gpurs_gpu *gpu, gpurs_device_ptr pointer);
+
 /* ---- TMA descriptors ------------------------------------------------------------------------- */
 
 /* Generalises `driver::try_tensor_map` (crates/driver/src/memory.rs:325-354), which is fixed to rank 2,
@@ -253,6 +263,31 @@ typedef struct gpurs_grouped_desc {
 
 int gpurs_matmul_grouped(gpurs_stream *stream, const gpurs_grouped_desc *desc, gpurs_device_ptr input, gpurs_device_ptr routes,
                          gpurs_device_ptr offsets, gpurs_device_ptr weight, gpurs_device_ptr output);
+
+/* ---- product whose result every GPU of the box receives ---------------------------------------------- */
+
+/* No counterpart in the reference, which drives one GPU.  The M-sharded product of a box of GPUs followed by the
+ * all-gather of C, as one kernel per GPU instead of a kernel and a collective.  Each GPU multiplies its block of rows of A by the replicated B and stores every finished 32-row box of C into the
+ * block's place in the copy of the whole matrix that EVERY GPU keeps: the local copy through L2, the remote ones as
+ * plain stores over NVLink, while the tensor cores work on the next tile.  No kernel waits on another GPU; when the
+ * calls of all ranks have completed (each rank synchronises its stream, then the ranks meet at a host barrier), every
+ * copy holds the whole matrix.
+ *   full[t]  the gathered matrix (total_rows x n, pitch ld_full) on GPU t as an address valid in THIS process: the
+ *            rank's own allocation for t == rank, gpurs_ipc_open of the owner's handle otherwise (peers of one box).
+ * `desc` describes the local product as for gpurs_matmul (m = rows of this block; ldc 0 or ld_full; c_len ignored).
+ * Supported: dense bf16->bf16, f16->f32, i8->i32, unscaled e4m3->bf16; bases and pitches of the gathered matrices
+ * multiples of 16 bytes; every block but the last a multiple of 32 rows. */
+typedef struct gpurs_gather_desc {
+    uint32_t world;              /* GPUs that receive the result, 1..8 */
+    uint32_t rank;               /* the one this call runs on */
+    uint64_t row_offset;         /* first row of this call's block within the gathered matrix */
+    uint64_t total_rows;         /* rows of the gathered matrix */
+    uint64_t ld_full;            /* its row pitch in elements; 0 = n */
+    gpurs_device_ptr full[8];
+} gpurs_gather_desc;
+
+int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_desc *desc, const gpurs_gather_desc *gather,
+                           gpurs_device_ptr a, gpurs_device_ptr b);
 
 /* Reads and clears the device status word: [0] code (0 = none), [1] block, [2] tile, [3] K-block of the
  * first bounded wait that gave up.  Synchronises the device. */
