@@ -84,6 +84,10 @@ SIGNATURES = {
     "gpurs_fill_u8": (C.c_int, [_P, C.c_uint64, C.c_uint8, C.c_size_t]),
     "gpurs_host_alloc": (C.c_int, [_P, C.c_size_t, _PP]),
     "gpurs_host_free": (C.c_int, [_P, _P]),
+    "gpurs_stream_capture_begin": (C.c_int, [_P]),
+    "gpurs_stream_capture_end": (C.c_int, [_P, _PP]),
+    "gpurs_graph_launch": (C.c_int, [_P, _P]),
+    "gpurs_graph_free": (None, [_P]),
     "gpurs_ipc_export": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_uint8)]),
     "gpurs_ipc_open": (C.c_int, [_P, C.POINTER(C.c_uint8), _U64P]),
     "gpurs_ipc_close": (C.c_int, [_P, C.c_uint64]),

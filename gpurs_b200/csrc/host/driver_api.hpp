@@ -22,6 +22,14 @@ namespace driver {
     X(cuStreamDestroy)            \
     X(cuStreamSynchronize)        \
     X(cuStreamWaitEvent)          \
+    X(cuStreamIsCapturing)        \
+    X(cuStreamBeginCapture)       \
+    X(cuStreamEndCapture)         \
+    X(cuGraphInstantiate)         \
+    X(cuGraphLaunch)              \
+    X(cuGraphExecDestroy)         \
+    X(cuGraphDestroy)             \
+    X(cuGraphGetNodes)            \
     X(cuEventCreate)              \
     X(cuEventRecord)              \
     X(cuEventSynchronize)         \

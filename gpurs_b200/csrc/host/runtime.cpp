@@ -97,6 +97,17 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
 static int scratch_acquire(gpurs_stream *stream, gpurs_gpu::Scratch &scratch, size_t bytes, bool zeroed, CUdeviceptr *out) {
     gpurs_gpu *gpu = stream->gpu;
     const driver::Api *api = gpu->api;
+    // Work recorded into a graph runs later, perhaps many times: it cannot be ordered by an event recorded now, and the
+    // block must not move under it.  The graph remembers that it borrows the block and orders itself at every replay.
+    CUstreamCaptureStatus capture = CU_STREAM_CAPTURE_STATUS_NONE;
+    GPURS_TRY(api, cuStreamIsCapturing(stream->handle, &capture));
+    if (capture == CU_STREAM_CAPTURE_STATUS_ACTIVE) {
+        if (scratch.bytes < bytes)
+            return fail("capture", GPURS_E_INVALID_ARGUMENT, "scratch memory cannot grow during a capture: run the same product once before capturing it");
+        scratch.captured = true;
+        *out = scratch.pointer;
+        return GPURS_OK;
+    }
     if (scratch.bytes < bytes) {
         // Nobody may still be using the old block when it is replaced.
         GPURS_TRY(api, cuCtxSynchronize());
@@ -119,6 +130,9 @@ static int scratch_acquire(gpurs_stream *stream, gpurs_gpu::Scratch &scratch, si
 }
 
 static int scratch_release(gpurs_stream *stream, gpurs_gpu::Scratch &scratch) {
+    CUstreamCaptureStatus capture = CU_STREAM_CAPTURE_STATUS_NONE;
+    GPURS_TRY(stream->gpu->api, cuStreamIsCapturing(stream->handle, &capture));
+    if (capture == CU_STREAM_CAPTURE_STATUS_ACTIVE) return GPURS_OK;
     GPURS_TRY(stream->gpu->api, cuEventRecord(scratch.event, stream->handle));
     scratch.used = true;
     return GPURS_OK;
@@ -275,6 +289,73 @@ int gpurs_stream_synchronize(gpurs_stream *stream) {
     if (result != GPURS_OK) return result;
     if (status[0] != 0) return fail("gpurs_stream_synchronize", GPURS_E_DEVICE_TIMEOUT, "a bounded wait inside a kernel gave up");
     return GPURS_OK;
+}
+
+// ---- graphs ---------------------------------------------------------------------------------------
+
+int gpurs_stream_capture_begin(gpurs_stream *stream) {
+    if (!stream) return fail("gpurs_stream_capture_begin", GPURS_E_INVALID_ARGUMENT, "null stream");
+    gpurs_gpu *gpu = stream->gpu;
+    Enter enter(gpu);
+    gpu->workspace.captured = gpu->turns.captured = false;
+    // Relaxed mode: this library looks kernels up and sets their attributes lazily, which stricter modes forbid
+    // while any capture is in progress.
+    GPURS_TRY(gpu->api, cuStreamBeginCapture(stream->handle, CU_STREAM_CAPTURE_MODE_RELAXED));
+    return GPURS_OK;
+}
+
+int gpurs_stream_capture_end(gpurs_stream *stream, gpurs_graph **out) {
+    if (!stream || !out) return fail("gpurs_stream_capture_end", GPURS_E_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    gpurs_gpu *gpu = stream->gpu;
+    Enter enter(gpu);
+    CUgraph graph = nullptr;
+    GPURS_TRY(gpu->api, cuStreamEndCapture(stream->handle, &graph));
+    if (!graph) return fail("gpurs_stream_capture_end", GPURS_E_INVALID_ARGUMENT, "the capture was invalidated");
+    size_t nodes = 0;
+    CUresult code = gpu->api->cuGraphGetNodes(graph, nullptr, &nodes);
+    CUgraphExec executable = nullptr;
+    if (code == CUDA_SUCCESS) code = gpu->api->cuGraphInstantiate(&executable, graph, 0);
+    if (code != CUDA_SUCCESS) {
+        gpu->api->cuGraphDestroy(graph);
+        return runtime::fail_driver(gpu->api, "cuGraphInstantiate", code);
+    }
+    gpurs_graph *result = new (std::nothrow) gpurs_graph{gpu, graph, executable, nodes, gpu->workspace.captured, gpu->turns.captured};
+    gpu->workspace.captured = gpu->turns.captured = false;
+    if (!result) {
+        gpu->api->cuGraphExecDestroy(executable);
+        gpu->api->cuGraphDestroy(graph);
+        return fail("gpurs_stream_capture_end", GPURS_E_INVALID_ARGUMENT, "out of host memory");
+    }
+    *out = result;
+    return GPURS_OK;
+}
+
+int gpurs_graph_launch(gpurs_graph *graph, gpurs_stream *stream) {
+    if (!graph || !stream) return fail("gpurs_graph_launch", GPURS_E_INVALID_ARGUMENT, "null argument");
+    if (graph->gpu != stream->gpu) return fail("gpurs_graph_launch", GPURS_E_CONTEXT_MISMATCH, "graph and stream belong to different gpu handles");
+    gpurs_gpu *gpu = graph->gpu;
+    Enter enter(gpu);
+    // A graph that borrows the handle's scratch takes its turn like any other borrower.
+    gpurs_gpu::Scratch *borrowed[2] = {graph->uses_workspace ? &gpu->workspace : nullptr, graph->uses_turns ? &gpu->turns : nullptr};
+    for (gpurs_gpu::Scratch *scratch : borrowed)
+        if (scratch && scratch->used) GPURS_TRY(gpu->api, cuStreamWaitEvent(stream->handle, scratch->event, 0));
+    GPURS_TRY(gpu->api, cuGraphLaunch(graph->executable, stream->handle));
+    for (gpurs_gpu::Scratch *scratch : borrowed)
+        if (scratch) {
+            GPURS_TRY(gpu->api, cuEventRecord(scratch->event, stream->handle));
+            scratch->used = true;
+        }
+    gpu->launches += graph->nodes;
+    return GPURS_OK;
+}
+
+void gpurs_graph_free(gpurs_graph *graph) {
+    if (!graph) return;
+    Enter enter(graph->gpu);
+    graph->gpu->api->cuGraphExecDestroy(graph->executable);
+    graph->gpu->api->cuGraphDestroy(graph->graph);
+    delete graph;
 }
 
 int gpurs_status_read(gpurs_gpu *gpu, uint32_t status[4]) {

@@ -36,6 +36,7 @@ struct gpurs_gpu {
         size_t bytes = 0;
         CUevent event = nullptr;
         bool used = false;
+        bool captured = false;   // borrowed by work recorded into the capture now in progress
     };
     Scratch workspace;   // grow-only: the hi/lo split copies of fp32 operands
     Scratch turns;       // fixed: the turn counters of split-K products, zero between launches
@@ -45,6 +46,15 @@ struct gpurs_stream {
     gpurs_gpu *gpu;
     CUstream handle;
     bool owned;
+};
+
+// A captured and instantiated sequence of operations.
+struct gpurs_graph {
+    gpurs_gpu *gpu;
+    CUgraph graph;
+    CUgraphExec executable;
+    size_t nodes;                // operations recorded: what one replay adds to the launch count
+    bool uses_workspace, uses_turns;
 };
 
 struct gpurs_event {

@@ -98,6 +98,22 @@ class Stream:
         _check(self.gpu._lib.gpurs_event_record_timed(self._handle, C.byref(handle)))
         return Event(self.gpu, handle)
 
+    def capture(self, record) -> "Graph":
+        """Run `record(stream)` with this stream recording instead of executing, and return the recording
+        (`Stream::capture`, crates/gpurs/src/host/graph/capture.rs:112-149).  Buffers the recorded operations use must
+        stay alive and in place while the graph exists."""
+        _check(self.gpu._lib.gpurs_stream_capture_begin(self._handle))
+        handle = C.c_void_p()
+        try:
+            record(self)
+        except BaseException:
+            # the capture must end whatever happened; what was recorded so far is dropped
+            if self.gpu._lib.gpurs_stream_capture_end(self._handle, C.byref(handle)) == _ffi.OK:
+                self.gpu._lib.gpurs_graph_free(handle)
+            raise
+        _check(self.gpu._lib.gpurs_stream_capture_end(self._handle, C.byref(handle)))
+        return Graph(self.gpu, handle)
+
     @property
     def raw(self) -> int:
         return self.gpu._lib.gpurs_stream_raw(self._handle) or 0
@@ -111,6 +127,33 @@ class Stream:
     def __del__(self):
         if getattr(self, "_handle", None) and self.gpu._handle:
             self.gpu._lib.gpurs_stream_free(self._handle)
+            self._handle = None
+
+
+class GraphExec:
+    """An instantiated recording (`GraphExec`, crates/gpurs/src/host/graph/exec.rs:15-72)."""
+
+    def __init__(self, graph: "Graph"):
+        self._graph = graph
+
+    def launch(self, stream: "Stream") -> None:
+        """Enqueue one replay of the whole recording on `stream`; does not wait."""
+        _check(self._graph.gpu._lib.gpurs_graph_launch(self._graph._handle, stream._handle))
+
+
+class Graph:
+    """What `Stream.capture` returns (`Graph`, crates/gpurs/src/host/graph/capture.rs:99-110).  The library instantiates
+    at the end of the capture, so `instantiate` only hands out the launcher."""
+
+    def __init__(self, gpu: "Gpu", handle):
+        self.gpu, self._handle = gpu, handle
+
+    def instantiate(self) -> GraphExec:
+        return GraphExec(self)
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and self.gpu._handle:
+            self.gpu._lib.gpurs_graph_free(self._handle)
             self._handle = None
 
 

@@ -109,6 +109,24 @@ int gpurs_fill_u8(gpurs_stream *stream, gpurs_device_ptr destination, uint8_t va
 int gpurs_host_alloc(gpurs_gpu *gpu, size_t bytes, void **out);
 int gpurs_host_free(gpurs_gpu *gpu, void *pointer);
 
+/* ---- graphs ------------------------------------------------------------------------------------------ */
+
+/* Record the operations enqueued on `stream` between begin and end (products, quantiser, compressor, copies, fills)
+ * instead of running them, then replay the recording with one submission: `Stream::capture` + `Graph::instantiate` +
+ * `GraphExec::launch` of the reference (crates/gpurs/src/host/graph/capture.rs:110-149,272-282; graph/exec.rs:48-72).
+ * The recording keeps the addresses and shapes it was made with; the caller keeps those buffers alive and unchanged in
+ * place while the graph exists.  One capture at a time per gpu handle.  Products that borrow the handle's scratch (fp32
+ * operands at full precision, split-K) must have run once with the same shapes before they are captured, because the
+ * scratch cannot grow inside a capture (GPURS_E_INVALID_ARGUMENT otherwise); a replay takes its turn on the scratch like
+ * any other call.  Calls that wait for the device (download, status_read, stream_synchronize) are not capturable. */
+typedef struct gpurs_graph gpurs_graph;
+int gpurs_stream_capture_begin(gpurs_stream *stream);
+/* Ends the capture and instantiates the recording. */
+int gpurs_stream_capture_end(gpurs_stream *stream, gpurs_graph **out);
+/* Enqueues one replay of the whole recording on `stream`; does not wait. */
+int gpurs_graph_launch(gpurs_graph *graph, gpurs_stream *stream);
+void gpurs_graph_free(gpurs_graph *graph);
+
 /* ---- sharing device memory between the processes of one box (no counterpart in the reference, which is
  *      single-process and single-GPU) ------------------------------------------------------------------ */
 
