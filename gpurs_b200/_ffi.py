@@ -43,6 +43,7 @@ class MatmulDesc(C.Structure):
         ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
         ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
+        ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("reserved", C.c_int32),
     ]
 
 
@@ -105,6 +106,7 @@ SIGNATURES = {
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_grouped": (C.c_int, [_P, C.POINTER(GroupedDesc), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "gpurs_matmul_host": (C.c_int, [_P, C.POINTER(MatmulDesc), _P, _P, _P, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_allgather": (C.c_int, [_P, C.POINTER(MatmulDesc), C.POINTER(GatherDesc), C.c_uint64, C.c_uint64]),
     "gpurs_self_test_timeout": (C.c_int, [_P]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),

@@ -178,6 +178,9 @@ struct MatmulOptions {
     int algorithm = GPURS_ALGO_AUTO;
     int precision = GPURS_PRECISION_DEFAULT;
     gpurs_device_ptr scale_a = 0, scale_b = 0, metadata = 0;
+    bool b_row_major = false;                                        // B given as k x n
+    gpurs_device_ptr bias = 0, row_scale = 0, column_scale = 0;      // epilogue: acc * alpha * row_scale[r] * column_scale[c] + bias[c]
+    float alpha = 0.0f;                                              // 0 = 1
 };
 
 // C[m, n] = sum_k A[m, k] * B[n, k]; shape = {m, n, k}.  A is m x k, B the n x k "right_transposed" operand of
@@ -195,6 +198,8 @@ void matmul(const Stream &stream, const DeviceBuffer<A> &a, const DeviceBuffer<A
     desc.algorithm = options.algorithm;
     desc.precision = options.precision;
     desc.scale_a = options.scale_a, desc.scale_b = options.scale_b, desc.metadata = options.metadata;
+    desc.b_row_major = options.b_row_major ? 1 : 0;
+    desc.bias = options.bias, desc.row_scale = options.row_scale, desc.column_scale = options.column_scale, desc.alpha = options.alpha;
     check(gpurs_matmul(stream.raw(), &desc, a.address(), b.address(), c.address()));
 }
 

@@ -16,6 +16,8 @@ struct Gemm {
     gpurs_device_ptr scale_a = 0, scale_b = 0;   // block-scaled E4M3 only
     int threads = gemm::NUM_THREADS;
     gpurs_device_ptr bias = 0;                   // optional fp32 [n]
+    gpurs_device_ptr row_scale = 0, column_scale = 0;   // optional fp32 [m] and [n]
+    float alpha = 0.0f;                          // 0 = none
     bool b_row_major = false;                    // B stored k x n
     int l2_policy = 0;                           // Params::l2_policy
     gpurs_device_ptr metadata = 0;               // 2:4-sparse A only: `a` then holds the kept values, k the logical depth

@@ -113,6 +113,10 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.l2_policy = g.l2_policy;
     params.b_row_major = g.b_row_major ? 1 : 0;
     params.bias = reinterpret_cast<const float *>(g.bias);
+    params.row_scale = reinterpret_cast<const float *>(g.row_scale);
+    params.column_scale = reinterpret_cast<const float *>(g.column_scale);
+    params.alpha = g.alpha;
+    params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
     uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
@@ -325,7 +329,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
                                  desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && !b_row_major && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
-                                 c % 4 == 0;
+                                 c % 4 == 0 && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
     // N-major reading of 32-bit elements needs a different shared-memory swizzle (32-byte atoms) that these kernels
     // do not set up; measured: the plain 128-byte swizzle yields zeros for TF32.
     if (b_row_major && (sparse || promoted || desc->a_type == GPURS_F32))
@@ -348,6 +352,10 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     if (desc->bias && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "a bias is for floating-point outputs");
     if (desc->bias % 4) return fail(op, GPURS_E_INVALID_VIEW, "the bias must be 4-byte aligned");
+    const bool scaled_output = desc->row_scale || desc->column_scale || (desc->alpha != 0.0f && desc->alpha != 1.0f);
+    if (scaled_output && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "output scales are for floating-point outputs");
+    if (desc->row_scale % 4 || desc->column_scale % 4) return fail(op, GPURS_E_INVALID_VIEW, "output scales must be 4-byte aligned");
+    if (desc->alpha != desc->alpha) return fail(op, GPURS_E_INVALID_ARGUMENT, "alpha is not a number");
     if (desc->precision != GPURS_PRECISION_DEFAULT && desc->precision != GPURS_PRECISION_TF32)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown precision");
     Gemm gemm;
@@ -363,6 +371,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.raster_rows = desc->raster_rows;
     gemm.max_ctas = desc->max_ctas;
     gemm.bias = desc->bias;
+    gemm.row_scale = desc->row_scale, gemm.column_scale = desc->column_scale, gemm.alpha = desc->alpha;
     gemm.b_row_major = b_row_major;
     gemm.gather = gather;
     if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
@@ -446,6 +455,83 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
     local.ldc = pitch;
     local.c_len = 0;
     return matmul_checked(op, stream, &local, a, b, gather->full[gather->rank] + gather->row_offset * pitch * ob, gather);
+}
+
+// Operands and result in HOST memory: copy in, multiply, copy out, with the three overlapped.  B goes up first, then A
+// in blocks of rows; each block is multiplied as soon as it has arrived and its rows of C start their way back while the
+// next block of A is still arriving, so the call costs about the longer of the two transfer directions instead of
+// their sum plus the product.  The reference's host writes the same steps one after the other
+// (examples/blackwell/examples/blackwell_matrix.rs:58-83: upload, upload, zeros, launch, download).
+extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *desc, const void *host_a, const void *host_b, void *host_c,
+                                 gpurs_device_ptr a, gpurs_device_ptr b, gpurs_device_ptr c) {
+    const char *const op = "gpurs_matmul_host";
+    if (!stream || !desc) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream or descriptor");
+    Choice choice;
+    if (!choose(desc->a_type, desc->c_type, choice))
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
+    if (desc->metadata) return fail(op, GPURS_E_INVALID_ARGUMENT, "a 2:4-sparse operand is prepared on the device: use gpurs_matmul");
+    const uint64_t m = desc->m, n = desc->n, k = desc->k;
+    if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
+        return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
+    if (m == 0 || n == 0) return GPURS_OK;
+    if (!host_c || !c || (k && (!host_a || !host_b || !a || !b))) return fail(op, GPURS_E_INVALID_ARGUMENT, "null operand");
+    const bool b_row_major = desc->b_row_major == 1;
+    const uint64_t b_rows = b_row_major ? k : n, b_columns = b_row_major ? n : k;
+    const uint64_t lda = desc->lda ? desc->lda : k, ldb = desc->ldb ? desc->ldb : b_columns, ldc = desc->ldc ? desc->ldc : n;
+    if (lda < k || ldb < b_columns || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    const uint64_t eb = uint64_t(choice.element_bytes), ob = uint64_t(choice.output_bytes);
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+
+    // Blocks of rows: about eight per call, whole CTA-pair tiles each; products that prepare B per call (fp32 operands,
+    // whose split copy of B would be rebuilt for every block) and decode shapes go in one piece.
+    const bool whole = (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT) || m <= 512;
+    const uint64_t block_rows = whole ? m : std::max<uint64_t>(256, ((m + 7) / 8 + 255) / 256 * 256);
+    const uint64_t blocks = (m + block_rows - 1) / block_rows;
+    int result = runtime::copy_pipeline(gpu, 2 * blocks + 3);
+    if (result != GPURS_OK) return result;
+    const driver::Api *api = gpu->api;
+    CUevent *events = gpu->events.data();
+    CUevent begun = events[0], b_arrived = events[1], finished = events[2];
+
+    // Both helper streams start after the work already on the caller's stream (it may still be using the buffers).
+    GPURS_TRY(api, cuEventRecord(begun, stream->handle));
+    GPURS_TRY(api, cuStreamWaitEvent(gpu->copy_in, begun, 0));
+    GPURS_TRY(api, cuStreamWaitEvent(gpu->copy_out, begun, 0));
+    auto join = [&]() -> int {
+        // whatever happened, the caller's stream continues only after both helper streams have drained
+        GPURS_TRY(api, cuEventRecord(finished, gpu->copy_out));
+        GPURS_TRY(api, cuStreamWaitEvent(stream->handle, finished, 0));
+        GPURS_TRY(api, cuEventRecord(finished, gpu->copy_in));
+        GPURS_TRY(api, cuStreamWaitEvent(stream->handle, finished, 0));
+        return GPURS_OK;
+    };
+    if (k) {
+        GPURS_TRY(api, cuMemcpyHtoDAsync(b, host_b, ((b_rows - 1) * ldb + b_columns) * eb, gpu->copy_in));
+        GPURS_TRY(api, cuEventRecord(b_arrived, gpu->copy_in));
+        GPURS_TRY(api, cuStreamWaitEvent(stream->handle, b_arrived, 0));
+    }
+    gpurs_matmul_desc local = *desc;
+    local.a_len = local.b_len = local.c_len = 0;
+    for (uint64_t block = 0; block < blocks && result == GPURS_OK; block++) {
+        const uint64_t first = block * block_rows, rows = std::min(block_rows, m - first);
+        CUevent a_arrived = events[3 + 2 * block], c_ready = events[4 + 2 * block];
+        if (k) {
+            GPURS_TRY(api, cuMemcpyHtoDAsync(a + first * lda * eb, static_cast<const uint8_t *>(host_a) + first * lda * eb,
+                                             ((rows - 1) * lda + k) * eb, gpu->copy_in));
+            GPURS_TRY(api, cuEventRecord(a_arrived, gpu->copy_in));
+            GPURS_TRY(api, cuStreamWaitEvent(stream->handle, a_arrived, 0));
+        }
+        local.m = rows;
+        result = matmul_checked(op, stream, &local, a + first * lda * eb, b, c + first * ldc * ob, nullptr);
+        if (result != GPURS_OK) break;
+        GPURS_TRY(api, cuEventRecord(c_ready, stream->handle));
+        GPURS_TRY(api, cuStreamWaitEvent(gpu->copy_out, c_ready, 0));
+        GPURS_TRY(api, cuMemcpyDtoHAsync(static_cast<uint8_t *>(host_c) + first * ldc * ob, c + first * ldc * ob,
+                                         ((rows - 1) * ldc + n) * ob, gpu->copy_out));
+    }
+    const int joined = join();
+    return result != GPURS_OK ? result : joined;
 }
 
 extern "C" size_t gpurs_metadata_bytes(uint64_t m, uint64_t k) {

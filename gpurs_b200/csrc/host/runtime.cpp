@@ -143,6 +143,17 @@ int workspace_release(gpurs_stream *stream) { return scratch_release(stream, str
 int turns_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out) { return scratch_acquire(stream, stream->gpu->turns, bytes, true, out); }
 int turns_release(gpurs_stream *stream) { return scratch_release(stream, stream->gpu->turns); }
 
+int copy_pipeline(gpurs_gpu *gpu, size_t count) {
+    if (!gpu->copy_in) GPURS_TRY(gpu->api, cuStreamCreate(&gpu->copy_in, CU_STREAM_NON_BLOCKING));
+    if (!gpu->copy_out) GPURS_TRY(gpu->api, cuStreamCreate(&gpu->copy_out, CU_STREAM_NON_BLOCKING));
+    while (gpu->events.size() < count) {
+        CUevent event = nullptr;
+        GPURS_TRY(gpu->api, cuEventCreate(&event, CU_EVENT_DISABLE_TIMING));
+        gpu->events.push_back(event);
+    }
+    return GPURS_OK;
+}
+
 }  // namespace runtime
 
 using runtime::Enter;
@@ -224,6 +235,9 @@ void gpurs_gpu_free(gpurs_gpu *gpu) {
             if (scratch->event) gpu->api->cuEventDestroy(scratch->event);
         }
         gpu->api->cuStreamDestroy(gpu->transfer);
+        if (gpu->copy_in) gpu->api->cuStreamDestroy(gpu->copy_in);
+        if (gpu->copy_out) gpu->api->cuStreamDestroy(gpu->copy_out);
+        for (CUevent event : gpu->events) gpu->api->cuEventDestroy(event);
     }
     gpu->api->cuDevicePrimaryCtxRelease(gpu->device);
     delete gpu;

@@ -5,6 +5,7 @@
 
 #include <map>
 #include <string>
+#include <vector>
 
 struct gpurs_module {
     gpurs_gpu *gpu;
@@ -38,6 +39,10 @@ struct gpurs_gpu {
         bool used = false;
         bool captured = false;   // borrowed by work recorded into the capture now in progress
     };
+    // Helper streams and events of the host-buffer product (created on first use): copies in and out run beside the
+    // caller's stream and are tied to it by events.
+    CUstream copy_in = nullptr, copy_out = nullptr;
+    std::vector<CUevent> events;
     Scratch workspace;   // grow-only: the hi/lo split copies of fp32 operands
     Scratch turns;       // fixed: the turn counters of split-K products, zero between launches
 };
@@ -97,6 +102,8 @@ int workspace_release(gpurs_stream *stream);
 // The same for the block of zero-initialised turn counters (`bytes` is fixed after the first call).
 int turns_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out);
 int turns_release(gpurs_stream *stream);
+// At least `count` reusable events (no timing) in gpu->events, and the two helper streams.
+int copy_pipeline(gpurs_gpu *gpu, size_t count);
 
 }  // namespace runtime
 

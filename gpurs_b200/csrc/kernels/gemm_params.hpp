@@ -34,8 +34,14 @@ struct Params {
     const float *bias;       // optional fp32 [N], added to every row before the output rounding (float outputs), or null
     int l2_policy;           // dense kernels: 0 no hint; 1 keep A (evict last), stream B (evict first); 2 the reverse; 3 keep both
     int reserved;            // 0
+    // Epilogue algebra on float outputs, applied in this order before the output rounding (each optional):
+    //     value * alpha * row_scale[row] * column_scale[column] + bias[column]
+    const float *row_scale;     // fp32 [M] or null: e.g. a per-token activation scale
+    const float *column_scale;  // fp32 [N] or null: e.g. a per-channel weight scale
+    float alpha;                // used when scaled_by_alpha != 0
+    int scaled_by_alpha;
 };
-static_assert(sizeof(Params) == 88, "the parameter block is part of the kernel image's interface");
+static_assert(sizeof(Params) == 112, "the parameter block is part of the kernel image's interface");
 
 constexpr int MAX_PUSH_TARGETS = 8;   // GPUs of one box
 

@@ -210,18 +210,21 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                     ptx::tmem_load_32x32(address + uint32_t(pair * 64), first);
                     ptx::tmem_load_32x32(address + uint32_t(pair * 64 + 32), second);
                     ptx::tmem_load_wait();
+                    if (pair == SCALE_BLOCK / 64 - 1) {
+                        // the last values have left the accumulator: hand it back before the remaining arithmetic
+                        ptx::tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(slot));
+                            else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(slot), 0));
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         // two columns per instruction (fma.rn.f32x2): half the issue slots of scalar FMAs
                         ptx::fma2(sums[pair * 64 + i], sums[pair * 64 + i + 1], first[i], first[i + 1], scale);
                         ptx::fma2(sums[pair * 64 + 32 + i], sums[pair * 64 + 32 + i + 1], second[i], second[i + 1], scale);
                     }
-                }
-                ptx::tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(slot));
-                    else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(slot), 0));
                 }
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 scale = next_scale;

@@ -78,14 +78,29 @@ __device__ __forceinline__ void tmem_load_columns(uint32_t address, uint32_t (&v
     else ptx::tmem_load_32x64(address, values);
 }
 
-// Adds the optional bias (fp32 per output column) to 32 accumulator columns starting at `column`.
+// The epilogue algebra on 32 accumulator columns of one output row, starting at `column`:
+// value * (alpha * row_scale[row]) * column_scale[column] + bias[column], each part optional (float outputs only),
+// every step rounded to fp32 on its own (no fused multiply-add), so that a host can reproduce the result exactly.
+// The reference offers the same steps on its accumulator tiles: scale, scale_rows, scale_columns, add_columns
+// (crates/gpurs/src/gpu/tensor/warp/accumulators.rs:86-110).
 template <int OUT>
-__device__ __forceinline__ void add_bias(const Params &p, uint32_t (&acc)[32], int column) {
+__device__ __forceinline__ void apply_epilogue(const Params &p, uint32_t (&acc)[32], int row, int column) {
     if constexpr (OUT != OUT_I32) {
+        if (p.scaled_by_alpha != 0 || p.row_scale != nullptr) {
+            float factor = p.scaled_by_alpha != 0 ? p.alpha : 1.0f;
+            if (p.row_scale != nullptr) factor = __fmul_rn(factor, __ldg(p.row_scale + min(row, p.m - 1)));
+#pragma unroll
+            for (int i = 0; i < 32; i++) acc[i] = __float_as_uint(__fmul_rn(__uint_as_float(acc[i]), factor));
+        }
+        if (p.column_scale != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n) acc[i] = __float_as_uint(__fmul_rn(__uint_as_float(acc[i]), __ldg(p.column_scale + column + i)));
+        }
         if (p.bias != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; i++)
-                if (column + i < p.n) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __ldg(p.bias + column + i));
+                if (column + i < p.n) acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), __ldg(p.bias + column + i)));
         }
     }
 }
@@ -109,14 +124,7 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
     uint32_t acc[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) acc[i] = source[i];
-    if constexpr (OUT != OUT_I32) {
-        // optional bias, one fp32 per output column, added before the output rounding
-        if (p.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; i++)
-                if (column + i < p.n) acc[i] = __float_as_uint(__uint_as_float(acc[i]) + __ldg(p.bias + column + i));
-        }
-    }
+    apply_epilogue<OUT>(p, acc, row, column);
     if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
         uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + size_t(row) * p.ldc + column;
         if (whole) {
@@ -362,14 +370,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     if constexpr (COLUMNS_PER_BOX == 32) {
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
                         ptx::tmem_load_wait();
-                        add_bias<OUT>(p, packed, column);
+                        apply_epilogue<OUT>(p, packed, row, column);
                     } else {
                         uint32_t low[32], high[32];
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
                         ptx::tmem_load_wait();
-                        add_bias<OUT>(p, low, column);
-                        add_bias<OUT>(p, high, column + 32);
+                        apply_epilogue<OUT>(p, low, row, column);
+                        apply_epilogue<OUT>(p, high, row, column + 32);
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);

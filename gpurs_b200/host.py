@@ -327,6 +327,9 @@ class MatmulOptions:
     scale_a: DeviceBuffer | None = None
     scale_b: DeviceBuffer | None = None
     bias: DeviceBuffer | None = None       # fp32 [n], added to every row of C
+    row_scale: DeviceBuffer | None = None      # fp32 [m]: C = acc * alpha * row_scale[row] * column_scale[column] + bias[column]
+    column_scale: DeviceBuffer | None = None   # fp32 [n]
+    alpha: float = 0.0                         # 0 = 1
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
@@ -357,7 +360,35 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.l2_policy = options.l2_policy
     desc.b_row_major = 1 if options.b_row_major else 0
     desc.bias = options.bias.pointer if options.bias else 0
+    desc.row_scale = options.row_scale.pointer if options.row_scale else 0
+    desc.column_scale = options.column_scale.pointer if options.column_scale else 0
+    desc.alpha = options.alpha
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
+
+
+def matmul_host(stream: Stream, host_a: int, host_b: int, host_c: int, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, shape,
+                options: MatmulOptions | None = None) -> None:
+    """The product with operands and result in host memory (addresses `host_a`, `host_b`, `host_c`, page-locked for
+    the copies to overlap), staged through the device buffers a, b, c: the upload / upload / launch / download of the
+    reference's example (examples/blackwell/examples/blackwell_matrix.rs:58-83) as one call that overlaps the copy in,
+    the product and the copy out by blocks of rows.  Does not wait: synchronise `stream` before reading `host_c`."""
+    options = options or MatmulOptions()
+    m, n, k = (int(x) for x in shape)
+    desc = _ffi.MatmulDesc()
+    desc.a_type, desc.c_type = a.element, c.element
+    desc.m, desc.n, desc.k = m, n, k
+    desc.lda, desc.ldb, desc.ldc = options.lda, options.ldb, options.ldc
+    desc.algorithm, desc.max_ctas = options.algorithm, options.max_ctas
+    desc.precision, desc.raster_rows = options.precision, options.raster_rows
+    desc.scale_a = options.scale_a.pointer if options.scale_a else 0
+    desc.scale_b = options.scale_b.pointer if options.scale_b else 0
+    desc.l2_policy = options.l2_policy
+    desc.b_row_major = 1 if options.b_row_major else 0
+    desc.bias = options.bias.pointer if options.bias else 0
+    desc.row_scale = options.row_scale.pointer if options.row_scale else 0
+    desc.column_scale = options.column_scale.pointer if options.column_scale else 0
+    desc.alpha = options.alpha
+    _check(stream.gpu._lib.gpurs_matmul_host(stream._handle, C.byref(desc), host_a, host_b, host_c, a.pointer, b.pointer, c.pointer))
 
 
 class GatheredMatrix:
@@ -410,6 +441,9 @@ def matmul_allgather(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, gathered:
     desc.algorithm, desc.max_ctas, desc.raster_rows = options.algorithm, options.max_ctas, options.raster_rows
     desc.b_row_major = 1 if options.b_row_major else 0
     desc.bias = options.bias.pointer if options.bias else 0
+    desc.row_scale = options.row_scale.pointer if options.row_scale else 0
+    desc.column_scale = options.column_scale.pointer if options.column_scale else 0
+    desc.alpha = options.alpha
     gather = _ffi.GatherDesc()
     gather.world, gather.rank, gather.row_offset, gather.total_rows, gather.ld_full = gathered.world, gathered.rank, row_offset, gathered.total_rows, 0
     for peer, pointer in enumerate(gathered.pointers):

@@ -217,6 +217,14 @@ typedef struct gpurs_matmul_desc {
                                         kernels only */
     gpurs_device_ptr bias;           /* optional fp32 [n] added to every row of C before the output rounding (float outputs;
                                         the epilogue of the reference's skinny example, examples/ada/examples/skinny_matrix.rs:60-64) */
+    /* More epilogue algebra for float outputs, the steps the reference offers on accumulator tiles (`scale`, `scale_rows`,
+     * `scale_columns`, crates/gpurs/src/gpu/tensor/warp/accumulators.rs:86-110).  Applied before the bias and the output
+     * rounding: C = acc * alpha * row_scale[row] * column_scale[column] + bias[column].  Tile kernels only (a product with
+     * any of the three does not take the split-K path). */
+    gpurs_device_ptr row_scale;      /* optional fp32 [m], e.g. a per-token activation scale */
+    gpurs_device_ptr column_scale;   /* optional fp32 [n], e.g. a per-channel weight scale */
+    float alpha;                     /* scalar factor; 0 is read as 1, so that a zeroed descriptor scales by nothing */
+    int32_t reserved;                /* 0 */
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
@@ -226,6 +234,19 @@ typedef struct gpurs_matmul_desc {
  * It does not wait. */
 int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
                  gpurs_device_ptr c);
+
+/* The same product with operands and result in HOST memory, staged through the caller's device buffers a, b, c (sized
+ * and pitched exactly like the host arrays): what the reference's example writes as upload, upload, zeros, launch,
+ * download (examples/blackwell/examples/blackwell_matrix.rs:58-83), as one call that overlaps the three.  B is copied
+ * first, then A in blocks of rows; every block is multiplied as soon as it has arrived, and its rows of C travel back
+ * while the next block of A is still on its way, so the call costs about the longer transfer direction instead of both
+ * plus the product.  Copies run on two streams of the handle, tied to `stream` by events: everything is ordered after
+ * the work already on `stream`, and `stream` continues after the last copy; the call does not wait.  The host arrays
+ * must stay valid until then and should be page-locked (gpurs_host_alloc), or the copies do not overlap.  Scales and
+ * bias in `desc` are device-resident as for gpurs_matmul; a 2:4-sparse operand is not accepted (it is prepared on the
+ * device).  a_len / b_len / c_len of `desc` are ignored. */
+int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *desc, const void *host_a, const void *host_b, void *host_c,
+                      gpurs_device_ptr a, gpurs_device_ptr b, gpurs_device_ptr c);
 
 /* ---- FP8 block quantisation ------------------------------------------------------------------------ */
 
