@@ -42,6 +42,7 @@ namespace driver {
     X(cuMemsetD8Async)            \
     X(cuMemHostAlloc)             \
     X(cuMemFreeHost)              \
+    X(cuMemcpy2DAsync)            \
     X(cuIpcGetMemHandle)          \
     X(cuIpcOpenMemHandle)         \
     X(cuIpcCloseMemHandle)        \

@@ -506,8 +506,26 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         GPURS_TRY(api, cuStreamWaitEvent(stream->handle, finished, 0));
         return GPURS_OK;
     };
+    // Copies of `rows` rows of `row_bytes` bytes at a pitch of `pitch` bytes on both sides: only the rows move, whatever
+    // lies between them (in host or device memory) stays as it is.
+    auto copy_rows = [&](bool to_device, CUdeviceptr device, const void *host, uint64_t rows, uint64_t row_bytes, uint64_t pitch, CUstream on) -> CUresult {
+        if (pitch == row_bytes)
+            return to_device ? api->cuMemcpyHtoDAsync(device, host, rows * row_bytes, on)
+                             : api->cuMemcpyDtoHAsync(const_cast<void *>(host), device, rows * row_bytes, on);
+        CUDA_MEMCPY2D copy;
+        std::memset(&copy, 0, sizeof copy);
+        copy.srcMemoryType = to_device ? CU_MEMORYTYPE_HOST : CU_MEMORYTYPE_DEVICE;
+        copy.dstMemoryType = to_device ? CU_MEMORYTYPE_DEVICE : CU_MEMORYTYPE_HOST;
+        if (to_device) copy.srcHost = host, copy.dstDevice = device;
+        else copy.srcDevice = device, copy.dstHost = const_cast<void *>(host);
+        copy.srcPitch = copy.dstPitch = pitch;
+        copy.WidthInBytes = row_bytes;
+        copy.Height = rows;
+        return api->cuMemcpy2DAsync(&copy, on);
+    };
+    auto driver_failed = [&](CUresult code) { return runtime::fail_driver(api, "gpurs_matmul_host copy", code); };
     if (k) {
-        GPURS_TRY(api, cuMemcpyHtoDAsync(b, host_b, ((b_rows - 1) * ldb + b_columns) * eb, gpu->copy_in));
+        if (CUresult code = copy_rows(true, b, host_b, b_rows, b_columns * eb, ldb * eb, gpu->copy_in)) return driver_failed(code);
         GPURS_TRY(api, cuEventRecord(b_arrived, gpu->copy_in));
         GPURS_TRY(api, cuStreamWaitEvent(stream->handle, b_arrived, 0));
     }
@@ -517,8 +535,8 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         const uint64_t first = block * block_rows, rows = std::min(block_rows, m - first);
         CUevent a_arrived = events[3 + 2 * block], c_ready = events[4 + 2 * block];
         if (k) {
-            GPURS_TRY(api, cuMemcpyHtoDAsync(a + first * lda * eb, static_cast<const uint8_t *>(host_a) + first * lda * eb,
-                                             ((rows - 1) * lda + k) * eb, gpu->copy_in));
+            if (CUresult code = copy_rows(true, a + first * lda * eb, static_cast<const uint8_t *>(host_a) + first * lda * eb, rows, k * eb, lda * eb, gpu->copy_in))
+                return driver_failed(code);
             GPURS_TRY(api, cuEventRecord(a_arrived, gpu->copy_in));
             GPURS_TRY(api, cuStreamWaitEvent(stream->handle, a_arrived, 0));
         }
@@ -527,8 +545,8 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         if (result != GPURS_OK) break;
         GPURS_TRY(api, cuEventRecord(c_ready, stream->handle));
         GPURS_TRY(api, cuStreamWaitEvent(gpu->copy_out, c_ready, 0));
-        GPURS_TRY(api, cuMemcpyDtoHAsync(static_cast<uint8_t *>(host_c) + first * ldc * ob, c + first * ldc * ob,
-                                         ((rows - 1) * ldc + n) * ob, gpu->copy_out));
+        if (CUresult code = copy_rows(false, c + first * ldc * ob, static_cast<uint8_t *>(host_c) + first * ldc * ob, rows, n * ob, ldc * ob, gpu->copy_out))
+            return driver_failed(code);
     }
     const int joined = join();
     return result != GPURS_OK ? result : joined;
