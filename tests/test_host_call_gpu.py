@@ -59,6 +59,37 @@ def test_host_call_equals_the_device_call(gpu, stream, kind, out, m, n, k):
     assert np.array_equal(got.view(np.uint8), expected.view(np.uint8))
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 512, 384), (256, 2048, 256), (640, 1536, 128)])
+def test_block_scales_follow_their_blocks(gpu, stream, m, n, k):
+    """Block-scaled FP8 by blocks of rows (m > n: A's scale rows move with the block) and by blocks of columns (n > m:
+    B's scale rows do), with per-row, per-column and bias vectors on top."""
+    a_bits, b_bits = make_operands("e4m3", m, n, k)
+    rng = np.random.default_rng(4)
+    k_blocks = (k + 127) // 128
+    options = dict(scale_a=gpu.upload(rng.uniform(0.5, 2.0, m * k_blocks).astype(np.float32)),
+                   scale_b=gpu.upload(rng.uniform(0.5, 2.0, ((n + 127) // 128) * k_blocks).astype(np.float32)),
+                   row_scale=gpu.upload(rng.uniform(0.5, 2.0, m).astype(np.float32)),
+                   column_scale=gpu.upload(rng.uniform(0.5, 2.0, n).astype(np.float32)),
+                   bias=gpu.upload(rng.normal(0, 3, n).astype(np.float32)))
+    expected = run_matmul(gpu, stream, "e4m3", "bf16", a_bits, b_bits, m, n, k, **options)
+    got = host_product(gpu, stream, "e4m3", "bf16", a_bits, b_bits, m, n, k, **options)
+    assert np.array_equal(got, expected)
+
+
+@pytest.mark.parametrize("kind,out,m,n,k", [("f16", "f32", 16, 4096, 1024), ("bf16", "bf16", 300, 3000, 192), ("i8", "i32", 128, 1280, 256)])
+def test_wide_products_go_by_blocks_of_columns(gpu, stream, kind, out, m, n, k):
+    """n > m: A goes up whole and B in blocks of its rows; the decode shape (m = 16) runs the split-K kernel per block."""
+    a_bits, b_bits = make_operands(kind, m, n, k)
+    options = {} if out == "i32" else {"bias": gpu.upload((np.arange(n) / 16.0).astype(np.float32))}
+    expected = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, **options)
+    got = host_product(gpu, stream, kind, out, a_bits, b_bits, m, n, k, **options)
+    if kind == "f16" and m == 16:
+        # split-K sums depend on how many splits a launch uses, which depends on the block's width: compare with tolerance
+        assert np.abs(got.astype(np.float64) - expected.astype(np.float64)).max() <= 1e-3 * np.abs(expected).max()
+    else:
+        assert np.array_equal(got.view(np.uint8), expected.view(np.uint8))
+
+
 def test_int8_host_call_matches_the_oracle(gpu, stream):
     m, n, k = 1536, 384, 512
     a_bits, b_bits = make_operands("i8", m, n, k)
