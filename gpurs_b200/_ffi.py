@@ -43,7 +43,8 @@ class MatmulDesc(C.Structure):
         ("algorithm", C.c_int32), ("max_ctas", C.c_int32), ("precision", C.c_int32), ("raster_rows", C.c_int32),
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
         ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
-        ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("reserved", C.c_int32),
+        ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("batches", C.c_int32),
+        ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_c", C.c_uint64),
     ]
 
 

@@ -53,7 +53,8 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const int cta_group = g.cta_group;
     const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
     char name[96];
-    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : "%s_cg%d", g.stem, cta_group);
+    const bool batched = g.batches > 1;
+    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : "%s_cg%d", g.stem, cta_group);
     const bool sparse = g.metadata != 0;
     const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
                                   : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
@@ -78,10 +79,21 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         dims_b[0] = g.n, dims_b[1] = g.k;
         box_b[0] = uint32_t(gemm::ROW_BYTES / g.element_bytes), box_b[1] = block_k;
     }
-    result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 2, g.a, dims_a, stride_a, box_a, 3, 3);
-    if (result != GPURS_OK) return result;
-    result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 2, g.b, dims_b, stride_b, box_b, 3, 3);
-    if (result != GPURS_OK) return result;
+    if (batched) {
+        // rank 3: (k, rows, batch), boxes one matrix deep; rows beyond a matrix read as zero, not as the next matrix
+        const uint64_t dims_a3[3] = {g.k, g.m, g.batches}, dims_b3[3] = {g.k, g.n, g.batches};
+        const uint64_t stride_a3[2] = {g.lda * eb, g.stride_a * eb}, stride_b3[2] = {g.ldb * eb, g.stride_b * eb};
+        const uint32_t box_a3[3] = {box_a[0], box_a[1], 1}, box_b3[3] = {box_b[0], box_b[1], 1};
+        result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 3, g.a, dims_a3, stride_a3, box_a3, 3, 3);
+        if (result != GPURS_OK) return result;
+        result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 3, g.b, dims_b3, stride_b3, box_b3, 3, 3);
+        if (result != GPURS_OK) return result;
+    } else {
+        result = gpurs_tensor_map_encode(gpu, &map_a, g.element_type, 2, g.a, dims_a, stride_a, box_a, 3, 3);
+        if (result != GPURS_OK) return result;
+        result = gpurs_tensor_map_encode(gpu, &map_b, g.element_type, 2, g.b, dims_b, stride_b, box_b, 3, 3);
+        if (result != GPURS_OK) return result;
+    }
 
     if (sparse) {
         // The metadata as rows of 16 bytes, 128 rows per block, no swizzle: block (row block, K block) starts at
@@ -106,7 +118,9 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     // Bands of 2048 rows by default: with one tile per SM in flight, the tiles running together then
     // cover about 2048 x 2304 outputs, a near-square patch whose A and B panels are shared through L2.
     params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16 / cta_group;
-    params.vector_stores = (g.c % 16 == 0 && (g.ldc * ob) % 16 == 0) ? 1 : 0;
+    params.vector_stores = (g.c % 16 == 0 && (g.ldc * ob) % 16 == 0 && (!batched || (g.stride_c * ob) % 16 == 0)) ? 1 : 0;
+    params.batches = int(g.batches);
+    params.batch_stride_c = (long long)g.stride_c;
     params.status = reinterpret_cast<unsigned int *>(gpu->status);
     params.scale_a = reinterpret_cast<const float *>(g.scale_a);
     params.scale_b = reinterpret_cast<const float *>(g.scale_b);
@@ -118,7 +132,8 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.alpha = g.alpha;
     params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
 
-    const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
+    const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n) * g.batches;
+    if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
     uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     uint64_t clusters = std::max<uint64_t>(1, ctas / cta_group);
     clusters = std::min(clusters, tiles);
@@ -137,9 +152,9 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     alignas(64) CUtensorMap map_c;
     std::memset(&map_c, 0, sizeof map_c);
     if (takes_output_map && params.vector_stores == 1) {
-        const uint64_t dims_c[2] = {g.n, g.m}, stride_c[1] = {g.ldc * ob};
-        const uint32_t box_c[2] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32};
-        result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, 2, g.c, dims_c, stride_c, box_c, 3, 3);
+        const uint64_t dims_c[3] = {g.n, g.m, g.batches}, stride_c[2] = {g.ldc * ob, g.stride_c * ob};
+        const uint32_t box_c[3] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32, 1};
+        result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, batched ? 3 : 2, g.c, dims_c, stride_c, box_c, 3, 3);
         if (result != GPURS_OK) return result;
     }
     if (g.gather) {
@@ -288,8 +303,18 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     const uint64_t lda = desc->lda ? desc->lda : a_columns, ldb = desc->ldb ? desc->ldb : b_columns, ldc = desc->ldc ? desc->ldc : n;
     if (lda < a_columns || ldb < b_columns || ldc < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
     // Extent of each operand in elements: the last row ends at (rows - 1) * pitch + columns.
-    const uint64_t a_extent = m ? (m - 1) * lda + a_columns : 0, b_extent = b_rows ? (b_rows - 1) * ldb + b_columns : 0,
-                   c_extent = m ? (m - 1) * ldc + n : 0;
+    uint64_t a_extent = m ? (m - 1) * lda + a_columns : 0, b_extent = b_rows ? (b_rows - 1) * ldb + b_columns : 0,
+             c_extent = m ? (m - 1) * ldc + n : 0;
+    // A batch: matrix i starts stride_* elements after matrix i - 1 (packed when 0); matrices of one operand may not overlap.
+    if (desc->batches < 0 || desc->batches > 65535) return fail(op, GPURS_E_INVALID_ARGUMENT, "batches must be 0..65535");
+    const uint64_t batches = desc->batches > 1 ? uint64_t(desc->batches) : 1;
+    const uint64_t stride_a = desc->stride_a ? desc->stride_a : m * lda, stride_b = desc->stride_b ? desc->stride_b : b_rows * ldb,
+                   stride_c = desc->stride_c ? desc->stride_c : m * ldc;
+    if (batches > 1) {
+        if (stride_a < a_extent || stride_b < b_extent || stride_c < c_extent)
+            return fail(op, GPURS_E_INVALID_VIEW, "a batch stride is smaller than the matrix");
+        a_extent += (batches - 1) * stride_a, b_extent += (batches - 1) * stride_b, c_extent += (batches - 1) * stride_c;
+    }
     if ((desc->a_len && desc->a_len < a_extent) || (desc->b_len && desc->b_len < b_extent) || (desc->c_len && desc->c_len < c_extent))
         return fail(op, GPURS_E_LENGTH_MISMATCH, "a slice is shorter than the matrix it is said to hold");
     if (m == 0 || n == 0) return GPURS_OK;
@@ -302,8 +327,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         // (for a gathering product: the block of every GPU's copy)
         for (uint32_t target = 0; target < (gather ? gather->world : 1u); target++) {
             const gpurs_device_ptr block = gather ? c - gather->full[gather->rank] + gather->full[target] : c;
-            for (uint64_t row = 0; row < (ldc == n ? 1 : m); row++)
-                GPURS_TRY(gpu->api, cuMemsetD8Async(block + row * ldc * ob, 0, (ldc == n ? m * n : n) * ob, stream->handle));
+            for (uint64_t batch = 0; batch < batches; batch++)
+                for (uint64_t row = 0; row < (ldc == n ? 1 : m); row++)
+                    GPURS_TRY(gpu->api, cuMemsetD8Async(block + (batch * stride_c + row * ldc) * ob, 0, (ldc == n ? m * n : n) * ob, stream->handle));
         }
         return GPURS_OK;
     }
@@ -329,13 +355,21 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
                                  desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && !b_row_major && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
-                                 c % 4 == 0 && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
+                                 c % 4 == 0 && batches == 1 && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
     // N-major reading of 32-bit elements needs a different shared-memory swizzle (32-byte atoms) that these kernels
     // do not set up; measured: the plain 128-byte swizzle yields zeros for TF32.
     if (b_row_major && (sparse || promoted || desc->a_type == GPURS_F32))
         return fail(op, GPURS_E_INVALID_ARGUMENT, "a k x n right operand is supported by the dense 16-bit and 8-bit tile kernels only");
     if (group == GPURS_ALGO_SKINNY && !skinny_possible)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm needs m <= 64, 16-bit dense operands and fp32 output");
+    if (batches > 1) {
+        const bool typed = (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) && (desc->c_type == GPURS_F32 || desc->c_type == desc->a_type);
+        if (!typed || sparse || promoted || b_row_major || gather || desc->l2_policy % 4 != 0)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "a batch is supported for dense f16 / bf16 operands (n x k right operand, no L2 hints)");
+        if ((stride_a * eb) % 16 || (stride_b * eb) % 16) return fail(op, GPURS_E_INVALID_VIEW, "operand bases and row pitches must be multiples of 16 bytes");
+        if ((stride_c * ob) % ob) return fail(op, GPURS_E_INVALID_VIEW, "the output is not aligned to its element size");
+        if (group == GPURS_ALGO_SKINNY) return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm takes a single product");
+    }
     if (gather) {
         // The push epilogue exists for the CTA-pair tile kernels of these type pairs, and it stores whole boxes of 32 rows.
         const bool typed = (desc->a_type == GPURS_BF16 && desc->c_type == GPURS_BF16) || (desc->a_type == GPURS_F16 && desc->c_type == GPURS_F32) ||
@@ -374,6 +408,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.row_scale = desc->row_scale, gemm.column_scale = desc->column_scale, gemm.alpha = desc->alpha;
     gemm.b_row_major = b_row_major;
     gemm.gather = gather;
+    gemm.batches = batches, gemm.stride_a = stride_a, gemm.stride_b = stride_b, gemm.stride_c = stride_c;
     if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
     if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
     gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints
@@ -457,9 +492,9 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
     return matmul_checked(op, stream, &local, a, b, gather->full[gather->rank] + gather->row_offset * pitch * ob, gather);
 }
 
-// Operands and result in HOST memory: copy in, multiply, copy out, with the three overlapped.  B goes up first, then A
-// in blocks of rows; each block is multiplied as soon as it has arrived and its rows of C start their way back while the
-// next block of A is still arriving, so the call costs about the longer of the two transfer directions instead of
+// Operands and result in HOST memory: copy in, multiply, copy out, with the three overlapped.  One operand goes up whole,
+// the other in blocks; each block is multiplied as soon as it has arrived and its part of C starts its way back while
+// the next block is still arriving, so the call costs about the longer of the two transfer directions instead of
 // their sum plus the product.  The reference's host writes the same steps one after the other
 // (examples/blackwell/examples/blackwell_matrix.rs:58-83: upload, upload, zeros, launch, download).
 extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *desc, const void *host_a, const void *host_b, void *host_c,
@@ -470,6 +505,7 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
     if (!choose(desc->a_type, desc->c_type, choice))
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
     if (desc->metadata) return fail(op, GPURS_E_INVALID_ARGUMENT, "a 2:4-sparse operand is prepared on the device: use gpurs_matmul");
+    if (desc->batches > 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "the host-buffer product takes a single product");
     const uint64_t m = desc->m, n = desc->n, k = desc->k;
     if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
         return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");

@@ -33,15 +33,16 @@ struct Params {
     const float *scale_b;    // block-scaled FP8 only: [ceil(N/128)][ceil(K/128)]
     const float *bias;       // optional fp32 [N], added to every row before the output rounding (float outputs), or null
     int l2_policy;           // dense kernels: 0 no hint; 1 keep A (evict last), stream B (evict first); 2 the reverse; 3 keep both
-    int reserved;            // 0
+    int batches;             // batched entries: number of matrices (0 or 1 = one); every other entry ignores it
     // Epilogue algebra on float outputs, applied in this order before the output rounding (each optional):
     //     value * alpha * row_scale[row] * column_scale[column] + bias[column]
     const float *row_scale;     // fp32 [M] or null: e.g. a per-token activation scale
     const float *column_scale;  // fp32 [N] or null: e.g. a per-channel weight scale
     float alpha;                // used when scaled_by_alpha != 0
     int scaled_by_alpha;
+    long long batch_stride_c;   // batched entries: elements between successive outputs (for the per-lane store path)
 };
-static_assert(sizeof(Params) == 112, "the parameter block is part of the kernel image's interface");
+static_assert(sizeof(Params) == 120, "the parameter block is part of the kernel image's interface");
 
 constexpr int MAX_PUSH_TARGETS = 8;   // GPUs of one box
 

@@ -38,3 +38,20 @@ GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_bf16_bf16_push_cg2, ptx::KIND_F16, 1, 1, gemm:
 GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_f16_f32_push_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F32)
 GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_i8_i32_push_cg2, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
 GPURS_GEMM_PUSH_KERNEL(gpurs_gemm_e4m3_bf16_push_cg2, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)
+
+// Batched entries: rank-3 descriptors (z = batch) for A, B and C; tiles of all matrices share one persistent grid.
+#define GPURS_GEMM_BATCHED_KERNEL(NAME, KIND, FORMAT, ACC, OUT, GROUP, STAGES)                                      \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                              \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                      \
+         const __grid_constant__ CUtensorMap map_c, const __grid_constant__ gemm::Params params) {                  \
+        gemm::gemm_body<KIND, FORMAT, ACC, OUT, gemm::BLOCK_N, GROUP, STAGES, false, true>(&map_a, &map_b, &map_c, params); \
+    }
+
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_bf16_bf16_batched_cg1, ptx::KIND_F16, 1, 1, gemm::OUT_BF16, 1, gemm::STAGES_SINGLE)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_bf16_bf16_batched_cg2, ptx::KIND_F16, 1, 1, gemm::OUT_BF16, 2, gemm::STAGES_PAIR)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_bf16_f32_batched_cg1, ptx::KIND_F16, 1, 1, gemm::OUT_F32, 1, gemm::STAGES_SINGLE)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_bf16_f32_batched_cg2, ptx::KIND_F16, 1, 1, gemm::OUT_F32, 2, gemm::STAGES_PAIR)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f16_batched_cg1, ptx::KIND_F16, 0, 1, gemm::OUT_F16, 1, gemm::STAGES_SINGLE)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f16_batched_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F16, 2, gemm::STAGES_PAIR)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f32_batched_cg1, ptx::KIND_F16, 0, 1, gemm::OUT_F32, 1, gemm::STAGES_SINGLE)
+GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f32_batched_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F32, 2, gemm::STAGES_PAIR)

@@ -118,7 +118,7 @@ __device__ __forceinline__ uint32_t pack_pair(uint32_t low, uint32_t high) {
 }
 
 template <int OUT>
-__device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column) {
+__device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column, long long element_offset = 0) {
     if (row >= p.m || column >= p.n) return;
     const bool whole = column + 32 <= p.n && p.vector_stores;
     uint32_t acc[32];
@@ -126,7 +126,7 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
     for (int i = 0; i < 32; i++) acc[i] = source[i];
     apply_epilogue<OUT>(p, acc, row, column);
     if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
-        uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + size_t(row) * p.ldc + column;
+        uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + element_offset + size_t(row) * p.ldc + column;
         if (whole) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -149,7 +149,7 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
                 packed[i] = *reinterpret_cast<uint32_t *>(&v);
             }
         }
-        uint16_t *out = reinterpret_cast<uint16_t *>(p.c) + size_t(row) * p.ldc + column;
+        uint16_t *out = reinterpret_cast<uint16_t *>(p.c) + element_offset + size_t(row) * p.ldc + column;
         if (whole) {
 #pragma unroll
             for (int i = 0; i < 4; i++)
@@ -164,7 +164,9 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
 
 // KIND: ptx::KIND_*; ELEMENT_FORMAT: the 3-bit format code of the operands for that kind;
 // ACC_FORMAT: 1 = f32, 2 = s32; OUT: OUT_*.
-template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false>
+// PUSH: the epilogue stores every box to all GPUs' copies (PushTargets).  BATCHED: the operands and the output are batches
+// of matrices described by rank-3 tensor maps (z = batch); tiles are numbered batch by batch.
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false, bool BATCHED = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p,
                                           const PushTargets *targets = nullptr) {
     using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
@@ -192,7 +194,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     const bool leader = cta_rank == 0;
     const int cluster_id = blockIdx.x / CTA_GROUP;
     const int cluster_count = gridDim.x / CTA_GROUP;
-    const int tile_count = p.tiles_m * p.tiles_n;
+    const int tiles_per_matrix = p.tiles_m * p.tiles_n;
+    const int tile_count = BATCHED ? tiles_per_matrix * max(p.batches, 1) : tiles_per_matrix;
     const int element_bytes = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
     const int block_k = ROW_BYTES / element_bytes;
     const int k_blocks = (p.k + block_k - 1) / block_k;
@@ -242,7 +245,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             const uint64_t policy_b = (p.l2_policy == 2 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
                 int tile_m, tile_n;
-                tile_position(tile, p, tile_m, tile_n);
+                const int batch = BATCHED ? tile / tiles_per_matrix : 0;
+                tile_position(tile - batch * tiles_per_matrix, p, tile_m, tile_n);
                 const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
                 const int row_b = tile_n * BLOCK_N + int(cta_rank) * L::B_ROWS;
                 for (int kb = 0; kb < k_blocks; kb++) {
@@ -251,7 +255,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         ok = false;
                         break;
                     }
-                    if constexpr (CTA_GROUP == 1) {
+                    if constexpr (BATCHED) {
+                        if constexpr (CTA_GROUP == 1) {
+                            ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+                            ptx::tma_load_3d(stage_a(stage), map_a, kb * block_k, row_a, batch, full_bar(stage));
+                            ptx::tma_load_3d(stage_b(stage), map_b, kb * block_k, row_b, batch, full_bar(stage));
+                        } else {
+                            if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+                            const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
+                            ptx::tma_load_3d_pair(stage_a(stage), map_a, kb * block_k, row_a, batch, leader_bar);
+                            ptx::tma_load_3d_pair(stage_b(stage), map_b, kb * block_k, row_b, batch, leader_bar);
+                        }
+                    } else if constexpr (CTA_GROUP == 1) {
                         ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
                         if (hinted) {
                             ptx::tma_load_2d_hint(stage_a(stage), map_a, kb * block_k, row_a, full_bar(stage), policy_a);
@@ -345,7 +360,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
         int stores = 0;                  // TMA stores issued by this warp: picks the staging buffer
         for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
             int tile_m, tile_n;
-            tile_position(tile, p, tile_m, tile_n);
+            const int batch = BATCHED ? tile / tiles_per_matrix : 0;
+            tile_position(tile - batch * tiles_per_matrix, p, tile_m, tile_n);
             // Every lane waits (each needs the barrier's acquire); the vote keeps the warp together
             // for the warp-wide tcgen05.ld that follows.
             const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
@@ -399,6 +415,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                             if constexpr (PUSH) {
                                 // one staged box, one store per GPU of the box (remote ones travel over NVLink)
                                 for (int t = 0; t < targets->count; t++) ptx::tma_store_2d(&targets->maps[t], column, targets->row_offset + warp_row, buffer);
+                            } else if constexpr (BATCHED) {
+                                ptx::tma_store_3d(map_c, column, warp_row, batch, buffer);
                             } else {
                                 ptx::tma_store_2d(map_c, column, warp_row, buffer);
                             }
@@ -412,7 +430,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     uint32_t values[32];
                     ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
                     ptx::tmem_load_wait();
-                    store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+                    store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32, BATCHED ? batch * p.batch_stride_c : 0ll);
                 }
             }
             ptx::tcgen05_fence_before();

@@ -131,6 +131,21 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// The same two loads for rank-3 tensors (x, y, z = innermost to outermost), used for batches of matrices: z is the batch.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y, int32_t z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y, int32_t z, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // ---- tensor memory --------------------------------------------------------------------------
 
 template <int CTA_GROUP>
@@ -363,6 +378,12 @@ __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int32_t x, int32_t y, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int32_t x, int32_t y, int32_t z, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
 

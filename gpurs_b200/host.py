@@ -330,6 +330,10 @@ class MatmulOptions:
     row_scale: DeviceBuffer | None = None      # fp32 [m]: C = acc * alpha * row_scale[row] * column_scale[column] + bias[column]
     column_scale: DeviceBuffer | None = None   # fp32 [n]
     alpha: float = 0.0                         # 0 = 1
+    batches: int = 0                           # > 1: a batch of products of one shape in one launch
+    stride_a: int = 0                          # elements between successive matrices; 0 = packed
+    stride_b: int = 0
+    stride_c: int = 0
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
@@ -363,6 +367,8 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.row_scale = options.row_scale.pointer if options.row_scale else 0
     desc.column_scale = options.column_scale.pointer if options.column_scale else 0
     desc.alpha = options.alpha
+    desc.batches = options.batches
+    desc.stride_a, desc.stride_b, desc.stride_c = options.stride_a, options.stride_b, options.stride_c
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 

@@ -224,7 +224,13 @@ typedef struct gpurs_matmul_desc {
     gpurs_device_ptr row_scale;      /* optional fp32 [m], e.g. a per-token activation scale */
     gpurs_device_ptr column_scale;   /* optional fp32 [n], e.g. a per-channel weight scale */
     float alpha;                     /* scalar factor; 0 is read as 1, so that a zeroed descriptor scales by nothing */
-    int32_t reserved;                /* 0 */
+    /* A batch of products of one shape, C[i] = A[i] * B[i]^T for i < batches, as ONE launch whose persistent grid walks the
+     * tiles of all matrices (`OutputMatrix::batched` + `Tile::batch`, crates/gpurs/src/gpu/tensor/output/matrix.rs:94-99,
+     * schedule/grid.rs:57-66).  Matrix i of each operand starts stride_* elements after matrix i - 1; 0 = packed (m * lda,
+     * n * ldb, m * ldc).  Dense f16 / bf16 operands on the tile kernels; strides must keep every matrix 16-byte aligned.
+     * bias, row_scale and column_scale, if given, apply to every matrix alike; a_len / b_len / c_len cover the whole batch. */
+    int32_t batches;                 /* 0 or 1 = a single product */
+    uint64_t stride_a, stride_b, stride_c;
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
@@ -237,10 +243,11 @@ int gpurs_matmul(gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_devi
 
 /* The same product with operands and result in HOST memory, staged through the caller's device buffers a, b, c (sized
  * and pitched exactly like the host arrays): what the reference's example writes as upload, upload, zeros, launch,
- * download (examples/blackwell/examples/blackwell_matrix.rs:58-83), as one call that overlaps the three.  B is copied
- * first, then A in blocks of rows; every block is multiplied as soon as it has arrived, and its rows of C travel back
- * while the next block of A is still on its way, so the call costs about the longer transfer direction instead of both
- * plus the product.  Copies run on two streams of the handle, tied to `stream` by events: everything is ordered after
+ * download (examples/blackwell/examples/blackwell_matrix.rs:58-83), as one call that overlaps the three.  The smaller
+ * operand is copied first, then the larger one in blocks (rows of A, or rows of B = columns of C); every block is
+ * multiplied as soon as it has arrived, and its part of C travels back while the next block is still on its way, so the
+ * call costs about the longer transfer direction instead of both plus the product.  Rows at a pitch are copied row by
+ * row: bytes between rows are left alone in host and device memory.  Copies run on two streams of the handle, tied to `stream` by events: everything is ordered after
  * the work already on `stream`, and `stream` continues after the last copy; the call does not wait.  The host arrays
  * must stay valid until then and should be page-locked (gpurs_host_alloc), or the copies do not overlap.  Scales and
  * bias in `desc` are device-resident as for gpurs_matmul; a 2:4-sparse operand is not accepted (it is prepared on the
