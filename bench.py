@@ -213,7 +213,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     a, b = gpu.upload(a_host, element), gpu.upload(b_host, element)
     c = gpu.allocate(out_element, m * n)
     shape = [m, n, k]
-    options = G.MatmulOptions(algorithm=args.algorithm, raster_rows=args.raster_rows, l2_policy=args.l2_policy)
+    options = G.MatmulOptions(algorithm=args.algorithm | (G.ALGO_WHOLE_TILES if args.whole_tiles else 0), raster_rows=args.raster_rows,
+                              l2_policy=args.l2_policy)
     if "skinny" in args.workload:
         options.bias = gpu.upload((np.arange(n) / 64.0).astype(np.float32))
     if args.workload.startswith("sparse24"):
@@ -446,6 +447,7 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--algorithm", type=int, default=0, help="0 auto, 1 single-CTA tiles, 2 CTA-pair tiles")
+    parser.add_argument("--whole-tiles", action="store_true", help="never split the last round's tiles along K (no stream-K)")
     parser.add_argument("--raster-rows", type=int, default=0, help="tile rows walked together (0 = library default)")
     parser.add_argument("--l2-policy", type=int, default=0, help="0 default, 1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 none")
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"],

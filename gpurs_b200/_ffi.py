@@ -26,6 +26,7 @@ E_DRIVER_UNAVAILABLE = 100011
 
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
 ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
+ALGO_WHOLE_TILES = 0x100   # flag: never split the last round's tiles along K
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -44,7 +45,7 @@ class MatmulDesc(C.Structure):
         ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("metadata", C.c_uint64),
         ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
         ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("batches", C.c_int32),
-        ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_c", C.c_uint64),
+        ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_c", C.c_uint64), ("row_absmax", C.c_uint64),
     ]
 
 

@@ -56,7 +56,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         # kernels as one translation unit list into a single image instead.
         unit = scratch / "all_kernels.cu"
         unit.write_text("".join(f'#include "{k}"\n' for k in kernels))
-        _run([nvcc, *NVCC_FLAGS, "-I", str(CSRC / "kernels"), "-fatbin", "-o", str(IMAGE), str(unit)], log)
+        # --no-compress: the entry names stay readable in the image (a host, or a test without a GPU, can list them)
+        _run([nvcc, *NVCC_FLAGS, "--no-compress", "-I", str(CSRC / "kernels"), "-fatbin", "-o", str(IMAGE), str(unit)], log)
         (scratch / "ptxas.log").write_text(log[-1])
         del objects
     if force or not LIBRARY.exists() or LIBRARY.stat().st_mtime < max(_newest(host_deps), IMAGE.stat().st_mtime):

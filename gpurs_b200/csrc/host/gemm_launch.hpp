@@ -18,7 +18,9 @@ struct Gemm {
     gpurs_device_ptr bias = 0;                   // optional fp32 [n]
     gpurs_device_ptr row_scale = 0, column_scale = 0;   // optional fp32 [m] and [n]
     float alpha = 0.0f;                          // 0 = none
+    gpurs_device_ptr row_absmax = 0;             // optional fp32 [m], atomic max of |C[row, :]|
     uint64_t batches = 1, stride_a = 0, stride_b = 0, stride_c = 0;   // batched entries: matrices and the elements between them
+    bool whole_tiles = false;                    // never split the last round's tiles along K
     bool b_row_major = false;                    // B stored k x n
     int l2_policy = 0;                           // Params::l2_policy
     gpurs_device_ptr metadata = 0;               // 2:4-sparse A only: `a` then holds the kept values, k the logical depth

@@ -3,6 +3,7 @@
 // example's own set-up (examples/blackwell/examples/blackwell_matrix.rs:58-83): check the arguments,
 // describe A and B to the TMA unit, pick the launch geometry and enqueue one kernel.
 #include "gemm_launch.hpp"
+#include "../kernels/gemm_schedule.hpp"
 
 #include <algorithm>
 #include <cstdio>
@@ -54,7 +55,16 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
     char name[96];
     const bool batched = g.batches > 1;
-    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : "%s_cg%d", g.stem, cta_group);
+    // Stream-K: decided here from the tile count and the grid, by the same arithmetic the kernel uses to find its work.
+    const uint64_t tile_rows_ = uint64_t(gemm::BLOCK_M) * cta_group;
+    const uint64_t all_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
+    const uint64_t wanted_ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    const uint64_t grid_clusters = std::min(std::max<uint64_t>(1, wanted_ctas / cta_group), std::max<uint64_t>(all_tiles, 1));
+    const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
+    gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters));
+    const bool stream_k = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull &&
+                          schedule.split_tiles > 0;
+    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? "%s_sk_cg%d" : "%s_cg%d", g.stem, cta_group);
     const bool sparse = g.metadata != 0;
     const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
                                   : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
@@ -131,6 +141,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.column_scale = reinterpret_cast<const float *>(g.column_scale);
     params.alpha = g.alpha;
     params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
+    params.row_absmax = reinterpret_cast<float *>(g.row_absmax);
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n) * g.batches;
     if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
@@ -172,6 +183,23 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         targets.row_offset = int(g.gather->row_offset);
         void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
         return runtime::launch(kernel, stream, &config, push_arguments);
+    }
+    if (stream_k) {
+        // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch
+        const int most = gemm::max_contributors(schedule);
+        const size_t partial_bytes = size_t(schedule.split_tiles) * most * tile_rows * gemm::BLOCK_N * 4;
+        CUdeviceptr partials = 0, counters = 0;
+        result = runtime::workspace_acquire(stream, partial_bytes, &partials);
+        if (result != GPURS_OK) return result;
+        result = runtime::turns_acquire(stream, std::max<size_t>(size_t(schedule.split_tiles) * 4 * cta_group * sizeof(uint32_t), 4096), &counters);
+        if (result != GPURS_OK) return result;
+        params.partials = reinterpret_cast<void *>(partials);
+        params.split_counters = reinterpret_cast<unsigned int *>(counters);
+        params.max_contributors = most;
+        void *stream_arguments[4] = {&map_a, &map_b, &map_c, &params};
+        result = runtime::launch(kernel, stream, &config, stream_arguments);
+        const int released = runtime::workspace_release(stream), turned = runtime::turns_release(stream);
+        return result != GPURS_OK ? result : released != GPURS_OK ? released : turned;
     }
     void *arguments[3] = {&map_a, &map_b, &params};
     void *dense_arguments[4] = {&map_a, &map_b, &map_c, &params};
@@ -348,14 +376,15 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (desc->scale_a && desc->a_type != GPURS_E4M3) return fail(op, GPURS_E_INVALID_ARGUMENT, "scales are for E4M3 operands only");
     if (desc->scale_a && (desc->scale_a % 4 || desc->scale_b % 4)) return fail(op, GPURS_E_INVALID_VIEW, "scale arrays must be 4-byte aligned");
 
-    int group = desc->algorithm;
+    int group = desc->algorithm & 0xff;
+    if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     // Kernels that promote every K-block to registers hand an accumulator back and forth once per block;
     // across a CTA pair that hand-off costs more than the pair saves, so they default to one-CTA tiles.
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
                                  desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && !b_row_major && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
-                                 c % 4 == 0 && batches == 1 && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
+                                 c % 4 == 0 && batches == 1 && !desc->row_absmax && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
     // N-major reading of 32-bit elements needs a different shared-memory swizzle (32-byte atoms) that these kernels
     // do not set up; measured: the plain 128-byte swizzle yields zeros for TF32.
     if (b_row_major && (sparse || promoted || desc->a_type == GPURS_F32))
@@ -390,6 +419,13 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (scaled_output && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "output scales are for floating-point outputs");
     if (desc->row_scale % 4 || desc->column_scale % 4) return fail(op, GPURS_E_INVALID_VIEW, "output scales must be 4-byte aligned");
     if (desc->alpha != desc->alpha) return fail(op, GPURS_E_INVALID_ARGUMENT, "alpha is not a number");
+    if (desc->row_absmax) {
+        if (desc->c_type == GPURS_I32 || sparse || promoted || batches > 1 || group == GPURS_ALGO_SKINNY)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the row reduction is for single dense products with float outputs on the tile kernels");
+        if (desc->row_absmax % 4) return fail(op, GPURS_E_INVALID_VIEW, "the row reduction must be 4-byte aligned");
+        if (overlap(desc->row_absmax, m * sizeof(float), c, c_extent * ob))
+            return fail(op, GPURS_E_ALIASING, "the row reduction overlaps the output");
+    }
     if (desc->precision != GPURS_PRECISION_DEFAULT && desc->precision != GPURS_PRECISION_TF32)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown precision");
     Gemm gemm;
@@ -406,6 +442,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.max_ctas = desc->max_ctas;
     gemm.bias = desc->bias;
     gemm.row_scale = desc->row_scale, gemm.column_scale = desc->column_scale, gemm.alpha = desc->alpha;
+    gemm.row_absmax = desc->row_absmax;
+    gemm.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0;
     gemm.b_row_major = b_row_major;
     gemm.gather = gather;
     gemm.batches = batches, gemm.stride_a = stride_a, gemm.stride_b = stride_b, gemm.stride_c = stride_c;

@@ -41,8 +41,17 @@ struct Params {
     float alpha;                // used when scaled_by_alpha != 0
     int scaled_by_alpha;
     long long batch_stride_c;   // batched entries: elements between successive outputs (for the per-lane store path)
+    float *row_absmax;          // dense tile kernels, float outputs: fp32 [M] or null; max |value| of each output row (after the
+                                // algebra above, before the output rounding) is folded in with an atomic max, so the caller
+                                // zeroes it first.  What a per-row quantiser of C needs, without reading C again.
+    // Stream-K entries only: scratch for the partial tiles of the split round, [split tile][contributor][tile rows][BLOCK_N]
+    // 32-bit sums; one arrival counter per split tile and epilogue warp (zero between launches); contributors allotted per tile.
+    void *partials;
+    unsigned int *split_counters;
+    int max_contributors;
+    int reserved;               // 0
 };
-static_assert(sizeof(Params) == 120, "the parameter block is part of the kernel image's interface");
+static_assert(sizeof(Params) == 152, "the parameter block is part of the kernel image's interface");
 
 constexpr int MAX_PUSH_TARGETS = 8;   // GPUs of one box
 

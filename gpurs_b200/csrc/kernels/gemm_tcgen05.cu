@@ -55,3 +55,22 @@ GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f16_batched_cg1, ptx::KIND_F16, 0, 1, g
 GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f16_batched_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F16, 2, gemm::STAGES_PAIR)
 GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f32_batched_cg1, ptx::KIND_F16, 0, 1, gemm::OUT_F32, 1, gemm::STAGES_SINGLE)
 GPURS_GEMM_BATCHED_KERNEL(gpurs_gemm_f16_f32_batched_cg2, ptx::KIND_F16, 0, 1, gemm::OUT_F32, 2, gemm::STAGES_PAIR)
+
+// Stream-K entries: the tiles of the last, partial round are split along K over the whole grid (gemm_schedule.hpp).
+#define GPURS_GEMM_STREAMK_KERNEL(NAME, KIND, FORMAT, ACC, OUT, GROUP, STAGES)                                      \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                              \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                      \
+         const __grid_constant__ CUtensorMap map_c, const __grid_constant__ gemm::Params params) {                  \
+        gemm::gemm_body<KIND, FORMAT, ACC, OUT, gemm::BLOCK_N, GROUP, STAGES, false, false, true>(&map_a, &map_b, &map_c, params); \
+    }
+#define GPURS_GEMM_STREAMK_PAIR(STEM, KIND, FORMAT, ACC, OUT)                                       \
+    GPURS_GEMM_STREAMK_KERNEL(STEM##_sk_cg1, KIND, FORMAT, ACC, OUT, 1, gemm::STAGES_SINGLE)         \
+    GPURS_GEMM_STREAMK_KERNEL(STEM##_sk_cg2, KIND, FORMAT, ACC, OUT, 2, gemm::STAGES_PAIR)
+
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_f16_f32, ptx::KIND_F16, 0, 1, gemm::OUT_F32)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_f16_f16, ptx::KIND_F16, 0, 1, gemm::OUT_F16)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_bf16_f32, ptx::KIND_F16, 1, 1, gemm::OUT_F32)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_bf16_bf16, ptx::KIND_F16, 1, 1, gemm::OUT_BF16)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_i8_i32, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_e4m3_f32, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_F32)
+GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_e4m3_bf16, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)

@@ -22,6 +22,7 @@
 // CTA's own tensor memory.  No TMA load is multicast; every CTA fetches its own operands.
 #pragma once
 #include "gemm_params.hpp"
+#include "gemm_schedule.hpp"
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -117,14 +118,23 @@ __device__ __forceinline__ uint32_t pack_pair(uint32_t low, uint32_t high) {
     }
 }
 
-template <int OUT>
+// max(running, |acc[i]|) over the columns of this chunk that exist (`reduce_rows` of the reference's accumulator tiles,
+// crates/gpurs/src/gpu/tensor/warp/accumulators.rs:112-128, with max |.| as the operation).
+__device__ __forceinline__ float fold_absmax(const Params &p, const uint32_t (&acc)[32], int column, float running) {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+        if (column + i < p.n) running = fmaxf(running, fabsf(__uint_as_float(acc[i])));
+    return running;
+}
+
+template <int OUT, bool APPLY = true>
 __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column, long long element_offset = 0) {
     if (row >= p.m || column >= p.n) return;
     const bool whole = column + 32 <= p.n && p.vector_stores;
     uint32_t acc[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) acc[i] = source[i];
-    apply_epilogue<OUT>(p, acc, row, column);
+    if constexpr (APPLY) apply_epilogue<OUT>(p, acc, row, column);
     if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
         uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + element_offset + size_t(row) * p.ldc + column;
         if (whole) {
@@ -162,11 +172,68 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
     }
 }
 
+// One piece of work of a CTA group: K-blocks [kb_begin, kb_end) of a tile.  split_tile >= 0 marks a tile of the split round
+// that `contributors` groups share; this group is number `contributor` of them.
+struct WorkItem {
+    int tile, kb_begin, kb_end;
+    int split_tile, contributor, contributors;
+};
+
+// Walks the work of one CTA group in order: with STREAMK first its share of the K-blocks of the split round (first, so that
+// adding the parts up overlaps the whole tiles that follow instead of ending the kernel), then its whole tiles (tile =
+// group, group + groups, ...).  All three roles of a CTA walk the same sequence.
+template <bool STREAMK>
+struct WorkWalker {
+    StreamSchedule schedule;
+    int group, groups, next_tile, whole_tiles;
+    long long unit, unit_end;
+
+    __device__ __forceinline__ WorkWalker(int tile_count, int k_blocks, int group_, int groups_) : group(group_), groups(groups_), next_tile(group_) {
+        schedule.k_blocks = k_blocks;
+        whole_tiles = tile_count;
+        unit = unit_end = 0;
+        if constexpr (STREAMK) {
+            schedule = make_stream_schedule(tile_count, k_blocks, groups_);
+            whole_tiles = schedule.whole_tiles;
+            if (schedule.split_tiles > 0 && group_ < schedule.clusters) {
+                unit = schedule.first_unit(group_);
+                unit_end = schedule.first_unit(group_ + 1);
+            }
+        }
+    }
+
+    __device__ __forceinline__ bool next(WorkItem &item) {
+        if constexpr (STREAMK) {
+            if (unit < unit_end) {
+                const int r = int(unit / schedule.k_blocks);
+                item.tile = whole_tiles + r;
+                item.kb_begin = int(unit - (long long)r * schedule.k_blocks);
+                const long long take = min((long long)(schedule.k_blocks - item.kb_begin), unit_end - unit);
+                item.kb_end = item.kb_begin + int(take);
+                item.contributors = schedule.contributors(r);
+                item.contributor = group - schedule.first_contributor(r);
+                item.split_tile = item.contributors > 1 ? r : -1;
+                unit += take;
+                return true;
+            }
+        }
+        if (next_tile < whole_tiles) {
+            item.tile = next_tile, item.kb_begin = 0, item.kb_end = schedule.k_blocks;
+            item.split_tile = -1, item.contributor = 0, item.contributors = 1;
+            next_tile += groups;
+            return true;
+        }
+        return false;
+    }
+};
+
 // KIND: ptx::KIND_*; ELEMENT_FORMAT: the 3-bit format code of the operands for that kind;
 // ACC_FORMAT: 1 = f32, 2 = s32; OUT: OUT_*.
 // PUSH: the epilogue stores every box to all GPUs' copies (PushTargets).  BATCHED: the operands and the output are batches
 // of matrices described by rank-3 tensor maps (z = batch); tiles are numbered batch by batch.
-template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false, bool BATCHED = false>
+// STREAMK: the tiles of the last, partial round are split along K over all CTA groups (gemm_schedule.hpp).
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false, bool BATCHED = false,
+          bool STREAMK = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p,
                                           const PushTargets *targets = nullptr) {
     using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
@@ -243,13 +310,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             const bool hinted = p.l2_policy != 0;
             const uint64_t policy_a = (p.l2_policy == 1 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
             const uint64_t policy_b = (p.l2_policy == 2 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
                 int tile_m, tile_n;
                 const int batch = BATCHED ? tile / tiles_per_matrix : 0;
                 tile_position(tile - batch * tiles_per_matrix, p, tile_m, tile_n);
                 const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
                 const int row_b = tile_n * BLOCK_N + int(cta_rank) * L::B_ROWS;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
                     if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
                         ok = false;
@@ -315,14 +385,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
                 if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
                     report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
                     break;
                 }
                 ptx::tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(acc) * BLOCK_N;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
                     if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                         report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
                         ok = false;
@@ -340,7 +413,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++) {
                         // advancing A's start address by 32 bytes steps through K inside the swizzle span
                         ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j) * b_step, idesc,
-                                                          uint32_t((kb | j) != 0));
+                                                          uint32_t(kb != item.kb_begin || j != 0));
                     }
                     if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
                     else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
@@ -358,7 +431,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
         int acc = 0;
         uint32_t acc_phase = 0;
         int stores = 0;                  // TMA stores issued by this warp: picks the staging buffer
-        for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
+        WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+        WorkItem item;
+        while (walker.next(item)) {
+            const int tile = item.tile;
             int tile_m, tile_n;
             const int batch = BATCHED ? tile / tiles_per_matrix : 0;
             tile_position(tile - batch * tiles_per_matrix, p, tile_m, tile_n);
@@ -372,7 +448,27 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BLOCK_N;
-            if (p.vector_stores == 1) {
+            const bool reduce = OUT != OUT_I32 && p.row_absmax != nullptr;
+            float row_max = 0.0f;
+            const bool shared_tile = STREAMK && item.split_tile >= 0;
+            // A tile of the split round holds only this group's K-blocks: its 32-bit sums go to scratch as they are.
+            constexpr int TILE_ROWS = BLOCK_M * CTA_GROUP;
+            const int row_in_tile = int(cta_rank) * BLOCK_M + quadrant * 32 + int(lane);
+            if (shared_tile) {
+                // one part = [BLOCK_N / 4 groups of four columns][TILE_ROWS rows] of 16 bytes: the 32 lanes (rows) of a
+                // warp write, and later read, 512 contiguous bytes per instruction
+                uint4 *mine = reinterpret_cast<uint4 *>(p.partials) +
+                              (size_t(item.split_tile) * p.max_contributors + item.contributor) * (TILE_ROWS * BLOCK_N / 4) + row_in_tile;
+#pragma unroll 1
+                for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+                    uint32_t values[32];
+                    ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
+                    ptx::tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        mine[size_t(chunk * 8 + i) * TILE_ROWS] = make_uint4(values[4 * i], values[4 * i + 1], values[4 * i + 2], values[4 * i + 3]);
+                }
+            } else if (p.vector_stores == 1) {
                 // Coalesced path: every 128 bytes of 32 output rows are staged in shared memory (128-byte swizzle, so
                 // the 32 lanes writing their rows do not collide on banks) and written by one TMA store, which also
                 // clips the box at the edges of C.  Two staging buffers per warp: the next box is filled while the
@@ -387,6 +483,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
                         ptx::tmem_load_wait();
                         apply_epilogue<OUT>(p, packed, row, column);
+                        if (reduce) row_max = fold_absmax(p, packed, column, row_max);
                     } else {
                         uint32_t low[32], high[32];
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
@@ -394,6 +491,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         ptx::tmem_load_wait();
                         apply_epilogue<OUT>(p, low, row, column);
                         apply_epilogue<OUT>(p, high, row, column + 32);
+                        if (reduce) row_max = fold_absmax(p, high, column + 32, fold_absmax(p, low, column, row_max));
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
@@ -430,9 +528,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     uint32_t values[32];
                     ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
                     ptx::tmem_load_wait();
-                    store_chunk<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32, BATCHED ? batch * p.batch_stride_c : 0ll);
+                    apply_epilogue<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+                    if (reduce) row_max = fold_absmax(p, values, tile_n * BLOCK_N + chunk * 32, row_max);
+                    store_chunk<OUT, false>(p, values, row, tile_n * BLOCK_N + chunk * 32, BATCHED ? batch * p.batch_stride_c : 0ll);
                 }
             }
+            // non-negative floats order like their bit patterns, so an unsigned atomic max folds the tile's part in
+            if (reduce && row < p.m) atomicMax(reinterpret_cast<unsigned int *>(p.row_absmax) + row, __float_as_uint(row_max));
             ptx::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -440,6 +542,59 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                 else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if constexpr (STREAMK) {
+                if (shared_tile) {
+                    // Whoever brings the last part of these 32 rows adds the parts up, in the contributors' order (so the
+                    // sum does not depend on who was last), and finishes the rows.  Nobody waits for anybody.
+                    unsigned int *counter = p.split_counters + item.split_tile * (4 * CTA_GROUP) + int(cta_rank) * 4 + quadrant;
+                    __threadfence();
+                    __syncwarp();
+                    unsigned int earlier = 0;
+                    if (lane == 0) earlier = atomicAdd(counter, 1u);
+                    earlier = __shfl_sync(0xffffffffu, earlier, 0);
+                    if (earlier == unsigned(item.contributors - 1)) {
+                        __threadfence();
+                        if (lane == 0) *counter = 0;       // ready for the next launch
+                        const uint4 *parts = reinterpret_cast<const uint4 *>(p.partials) +
+                                             size_t(item.split_tile) * p.max_contributors * (TILE_ROWS * BLOCK_N / 4) + row_in_tile;
+                        constexpr size_t PART = size_t(TILE_ROWS) * BLOCK_N / 4;      // one part, in 16-byte units
+#pragma unroll 1
+                        for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+                            uint32_t sum[32];
+#pragma unroll
+                            for (int i = 0; i < 32; i++) sum[i] = 0;    // +0.0f / 0: the first part is added to it exactly
+                            // four parts' loads in flight at a time, added in the contributors' order
+                            for (int first = 0; first < item.contributors; first += 4) {
+                                uint4 loaded[4][8];
+#pragma unroll
+                                for (int q = 0; q < 4; q++)
+                                    if (first + q < item.contributors) {
+#pragma unroll
+                                        for (int i = 0; i < 8; i++) loaded[q][i] = __ldcg(parts + size_t(first + q) * PART + size_t(chunk * 8 + i) * TILE_ROWS);
+                                    }
+#pragma unroll
+                                for (int q = 0; q < 4; q++)
+                                    if (first + q < item.contributors) {
+#pragma unroll
+                                        for (int i = 0; i < 8; i++) {
+                                            const uint32_t w[4] = {loaded[q][i].x, loaded[q][i].y, loaded[q][i].z, loaded[q][i].w};
+#pragma unroll
+                                            for (int j = 0; j < 4; j++) {
+                                                if constexpr (ACC_FORMAT == 2) sum[4 * i + j] += w[j];      // s32 sums wrap like the tensor core's
+                                                else sum[4 * i + j] = __float_as_uint(__fadd_rn(__uint_as_float(sum[4 * i + j]), __uint_as_float(w[j])));
+                                            }
+                                        }
+                                    }
+                            }
+                            const int column = tile_n * BLOCK_N + chunk * 32;
+                            apply_epilogue<OUT>(p, sum, row, column);
+                            if (reduce) row_max = fold_absmax(p, sum, column, row_max);
+                            store_chunk<OUT, false>(p, sum, row, column);
+                        }
+                        if (reduce && row < p.m) atomicMax(reinterpret_cast<unsigned int *>(p.row_absmax) + row, __float_as_uint(row_max));
+                    }
+                }
+            }
         }
         if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
     }

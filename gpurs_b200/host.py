@@ -334,6 +334,7 @@ class MatmulOptions:
     stride_a: int = 0                          # elements between successive matrices; 0 = packed
     stride_b: int = 0
     stride_c: int = 0
+    row_absmax: DeviceBuffer | None = None     # fp32 [m], zeroed by the caller: max |C[row, :]| is folded in
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
@@ -369,6 +370,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.alpha = options.alpha
     desc.batches = options.batches
     desc.stride_a, desc.stride_b, desc.stride_c = options.stride_a, options.stride_b, options.stride_c
+    desc.row_absmax = options.row_absmax.pointer if options.row_absmax else 0
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 

@@ -181,8 +181,14 @@ enum {
     GPURS_ALGO_AUTO = 0,
     GPURS_ALGO_SINGLE_CTA = 1,  /* 128 x 256 tiles, one CTA per tile (tcgen05 cta_group::1) */
     GPURS_ALGO_CTA_PAIR = 2,    /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
-    GPURS_ALGO_SKINNY = 3       /* m <= 64, 16-bit operands, fp32 output: B fills the tensor core's rows, K is split among CTAs
+    GPURS_ALGO_SKINNY = 3,      /* m <= 64, 16-bit operands, fp32 output: B fills the tensor core's rows, K is split among CTAs
                                    and the splits add in order (the reference's SplitDepth + TileLock); AUTO picks it */
+    /* Flag, or-ed to one of the above.  By default, when the tile count leaves the last round of the persistent grid more
+     * than a quarter empty (and at least one whole round precedes it), the dense tile kernels split the K-blocks of that
+     * round's tiles over the whole grid and add the parts up in a fixed order ("stream-K", the reference's
+     * schedule/stream.rs): faster, deterministic for a given shape, but the low bits of a floating-point result then
+     * depend on the shape.  With this flag every tile is multiplied whole by one CTA or CTA pair. */
+    GPURS_ALGO_WHOLE_TILES = 0x100
 };
 
 /* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */
@@ -231,6 +237,11 @@ typedef struct gpurs_matmul_desc {
      * bias, row_scale and column_scale, if given, apply to every matrix alike; a_len / b_len / c_len cover the whole batch. */
     int32_t batches;                 /* 0 or 1 = a single product */
     uint64_t stride_a, stride_b, stride_c;
+    /* Row reduction of the result (`reduce_rows` on the reference's accumulator tiles, warp/accumulators.rs:112-128, with
+     * max |.| as the operation): fp32 [m], folded in with an atomic max of |C[row, :]| taken after the algebra above and
+     * before the output rounding.  The caller zeroes the array first; it may be folded into by several products.  What a
+     * per-row quantiser of C needs without reading C again.  Dense tile kernels, float outputs, single products. */
+    gpurs_device_ptr row_absmax;
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's

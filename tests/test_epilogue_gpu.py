@@ -127,3 +127,36 @@ def test_integer_outputs_take_no_scales(gpu, stream):
         assert raised.value.code == _ffi.E_INVALID_ARGUMENT
     assert np.array_equal(run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, alpha=1.0),
                           run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k))
+
+
+@pytest.mark.parametrize("kind,out", [("f16", "f32"), ("bf16", "bf16")])
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 128), (300, 260, 96), (129, 77, 64)])
+def test_row_absmax_is_the_maximum_of_what_was_stored(gpu, stream, kind, out, m, n, k):
+    """max |.| per output row over all column tiles, taken from the fp32 values before the output rounding (so for a
+    bf16 output it is at least the stored maximum and within one rounding of it); folding a second product in keeps
+    the larger of the two."""
+    a_bits, b_bits = make_operands(kind, m, n, k)
+    rows, columns, bias = vectors(m, n, seed=13)
+    scales = dict(row_scale=gpu.upload(rows), column_scale=gpu.upload(columns), bias=gpu.upload(bias))
+    exact = expected_from(run_matmul(gpu, stream, kind, "f32", a_bits, b_bits, m, n, k), m, n, None, rows, columns, bias).reshape(m, n)
+    absmax = gpu.zeros(G.F32, m)
+    run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, row_absmax=absmax, **scales)
+    assert np.array_equal(absmax.download(), np.abs(exact).max(axis=1))
+    run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, row_absmax=absmax, alpha=0.5, **scales)     # smaller values: no change
+    assert np.array_equal(absmax.download(), np.abs(exact).max(axis=1))
+
+
+def test_row_absmax_is_refused_where_it_is_not_computed(gpu, stream):
+    m = n = k = 128
+    absmax = gpu.zeros(G.F32, m)
+    a_bits, b_bits = make_operands("i8", m, n, k)
+    with pytest.raises(G.GpursError) as raised:
+        run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, row_absmax=absmax)
+    assert raised.value.code == _ffi.E_INVALID_ARGUMENT
+    a_bits, b_bits = make_operands("f32", m, n, k)
+    with pytest.raises(G.GpursError) as raised:
+        run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, row_absmax=absmax)
+    assert raised.value.code == _ffi.E_INVALID_ARGUMENT
+    a_bits, b_bits = make_operands("f16", 16, n, k)
+    got = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, 16, n, k, row_absmax=absmax)      # AUTO leaves the split-K path
+    assert np.array_equal(absmax.download()[:16], np.abs(got.reshape(16, n)).max(axis=1))

@@ -75,12 +75,12 @@ def test_tensor_map_encode_checks(gpu):
 
 
 class _Params(C.Structure):
-    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp (120 bytes)
+    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp (128 bytes)
     _fields_ = [("c", C.c_uint64), ("ldc", C.c_longlong), ("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("tiles_m", C.c_int),
                 ("tiles_n", C.c_int), ("raster_rows", C.c_int), ("vector_stores", C.c_int), ("b_row_major", C.c_int), ("status", C.c_uint64),
                 ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("bias", C.c_uint64), ("l2_policy", C.c_int), ("batches", C.c_int),
                 ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("scaled_by_alpha", C.c_int),
-                ("batch_stride_c", C.c_longlong)]
+                ("batch_stride_c", C.c_longlong), ("row_absmax", C.c_uint64)]
 
 
 class _TensorMap(C.Structure):
@@ -115,7 +115,7 @@ def test_external_module_door(gpu, stream):
     for tensor_map, buffer, rows, box_rows in ((map_a, a, m, 128), (map_b, b, n, 256)):
         dims, strides, box = (C.c_uint64 * 2)(k, rows), (C.c_uint64 * 1)(k * 2), (C.c_uint32 * 2)(64, box_rows)
         assert gpu._lib.gpurs_tensor_map_encode(gpu._handle, C.addressof(tensor_map), G.BF16, 2, buffer.pointer, dims, strides, box, 3, 3) == 0
-    assert C.sizeof(_Params) == 120
+    assert C.sizeof(_Params) == 128
     params = _Params(c=c.pointer, ldc=n, m=m, n=n, k=k, tiles_m=m // 128, tiles_n=n // 256, raster_rows=16, vector_stores=1, status=status.pointer)
     # the dense entries also take a descriptor of C for their TMA-store epilogue: 32 rows x 128 bytes per box
     map_c = _aligned_tensor_map()

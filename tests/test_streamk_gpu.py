@@ -1,0 +1,80 @@
+"""Stream-K: when the tile count leaves the last round of the persistent grid mostly empty, the K-blocks of that round's
+tiles are spread over the whole grid and the parts are added up, in a fixed order, by whoever arrives last
+(crates/gpurs/src/gpu/tensor/schedule/stream.rs in the reference).  `max_ctas` shrinks the grid so that small shapes
+exercise it."""
+import numpy as np
+import pytest
+
+import gpurs_b200 as G
+import oracle as O
+from helpers import KINDS, decode_output, make_operands, relative_error, run_matmul
+
+pytestmark = pytest.mark.gpu
+
+# (algorithm, max_ctas, m, n): tiles % groups leaves a mostly empty last round
+GEOMETRIES = [
+    (G.ALGO_CTA_PAIR, 8, 512, 1536),      # 2 x 6 = 12 pair tiles on 4 pairs?  12 % 4 == 0: whole rounds only (control)
+    (G.ALGO_CTA_PAIR, 8, 512, 1280),      # 10 tiles on 4 pairs: 2 split over 4
+    (G.ALGO_CTA_PAIR, 16, 768, 768),      # 9 tiles on 8 pairs: 1 split over 8
+    (G.ALGO_SINGLE_CTA, 6, 640, 768),     # 15 tiles on 6 CTAs: 3 split over 6
+    (G.ALGO_SINGLE_CTA, 7, 1000, 700),    # 8 x 3 = 24 tiles on 7 CTAs: 3 split, ragged edges
+]
+
+
+@pytest.mark.parametrize("algorithm,max_ctas,m,n", GEOMETRIES)
+@pytest.mark.parametrize("k", [128, 1024, 1104])
+def test_int8_parts_add_up_exactly(gpu, stream, algorithm, max_ctas, m, n, k):
+    """Integer sums do not depend on how K was divided: bit-equal to the whole-tile product and to the oracle."""
+    a_bits, b_bits = make_operands("i8", m, n, k)
+    whole = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
+    for _ in range(2):                      # twice: the arrival counters must be back at zero after a launch
+        got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+        assert np.array_equal(got, whole)
+    rows = np.arange(0, m, 37)
+    assert np.array_equal(got.reshape(m, n)[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, n, k, rows).astype(np.int64))
+
+
+@pytest.mark.parametrize("algorithm,max_ctas,m,n", GEOMETRIES[1:])
+def test_exact_inputs_give_the_same_bits(gpu, stream, algorithm, max_ctas, m, n):
+    """The reference example's inputs (multiples of 1/16): every partial sum is exact in fp32, so the split product equals
+    the whole-tile one bit for bit."""
+    k = 2048
+    a_bits, b_bits = make_operands("f16", m, n, k, pattern="example")
+    whole = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
+    got = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+    assert np.array_equal(got, whole)
+
+
+@pytest.mark.parametrize("kind,out,tolerance", [("bf16", "bf16", 1e-2), ("f16", "f32", 1e-3), ("e4m3", "bf16", 2e-2), ("f16", "f16", 1e-2)])
+@pytest.mark.parametrize("algorithm,max_ctas,m,n", GEOMETRIES[1:])
+def test_float_products_stay_within_tolerance_with_epilogue(gpu, stream, kind, out, tolerance, algorithm, max_ctas, m, n):
+    k = 1024
+    a_bits, b_bits = make_operands(kind, m, n, k)
+    bias = (np.arange(n) % 13 - 6).astype(np.float32)
+    rows_scale = (1.0 + (np.arange(m) % 5) / 4.0).astype(np.float32)
+    got = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas, bias=gpu.upload(bias),
+                     row_scale=gpu.upload(rows_scale))
+    rows = np.arange(0, m, 29)
+    expected = O.matmul_rows(KINDS[kind][1], a_bits, b_bits, n, k, rows) * rows_scale[rows, None] + bias[None, :]
+    assert relative_error(decode_output(got, out).reshape(m, n)[rows], expected) <= tolerance
+    # deterministic: the parts are added in the contributors' order whoever arrives last
+    again = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas, bias=gpu.upload(bias),
+                       row_scale=gpu.upload(rows_scale))
+    assert np.array_equal(got, again)
+
+
+def test_full_grid_shape_that_splits(gpu, stream):
+    """The reference example's own size on the full grid: 256 pair tiles on 74 pairs (3.46 rounds): 34 tiles are split."""
+    size = 4096
+    a_bits, b_bits = make_operands("f16", size, size, size, pattern="example")
+    got = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, size, size, size)
+    whole = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, size, size, size, algorithm=G.ALGO_WHOLE_TILES)
+    assert np.array_equal(got, whole)
+    rows = np.arange(0, size, 131)
+    assert np.array_equal(got.reshape(size, size)[rows].astype(np.float64), O.matmul_rows(O.FMT_F16, a_bits, b_bits, size, size, rows))
+
+
+def test_unknown_algorithm_bits_are_refused(gpu, stream):
+    a_bits, b_bits = make_operands("bf16", 128, 128, 64)
+    with pytest.raises(G.GpursError):
+        run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, 128, 128, 64, algorithm=0x200)
