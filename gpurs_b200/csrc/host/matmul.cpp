@@ -182,7 +182,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         targets.count = int(g.gather->world);
         targets.row_offset = int(g.gather->row_offset);
         void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
-        return runtime::launch(kernel, stream, &config, push_arguments);
+        return runtime::launch(kernel, stream, &config, push_arguments, true);
     }
     if (stream_k) {
         // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch
@@ -197,14 +197,14 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         params.split_counters = reinterpret_cast<unsigned int *>(counters);
         params.max_contributors = most;
         void *stream_arguments[4] = {&map_a, &map_b, &map_c, &params};
-        result = runtime::launch(kernel, stream, &config, stream_arguments);
+        result = runtime::launch(kernel, stream, &config, stream_arguments, true);
         const int released = runtime::workspace_release(stream), turned = runtime::turns_release(stream);
         return result != GPURS_OK ? result : released != GPURS_OK ? released : turned;
     }
     void *arguments[3] = {&map_a, &map_b, &params};
     void *dense_arguments[4] = {&map_a, &map_b, &map_c, &params};
     void *sparse_arguments[4] = {&map_a, &map_b, &map_e, &params};
-    return runtime::launch(kernel, stream, &config, sparse ? sparse_arguments : takes_output_map ? dense_arguments : arguments);
+    return runtime::launch(kernel, stream, &config, sparse ? sparse_arguments : takes_output_map ? dense_arguments : arguments, true);
 }
 
 namespace {
@@ -271,7 +271,7 @@ int launch_skinny(gpurs_stream *stream, const launcher::Gemm &g) {
     config.block[0] = gemm::NUM_THREADS;
     config.shared_bytes = shared_bytes;
     void *arguments[3] = {&map_big, &map_small, &params};
-    result = runtime::launch(kernel, stream, &config, arguments);
+    result = runtime::launch(kernel, stream, &config, arguments, true);
     if (splits > 1) {
         const int released = runtime::turns_release(stream), freed = runtime::workspace_release(stream);
         if (result == GPURS_OK) result = released != GPURS_OK ? released : freed;
@@ -813,5 +813,5 @@ extern "C" int gpurs_matmul_grouped(gpurs_stream *stream, const gpurs_grouped_de
     config.block[0] = gemm::GROUPED_THREADS;
     config.shared_bytes = shared_bytes;
     void *arguments[2] = {&map_w, &params};
-    return runtime::launch(kernel, stream, &config, arguments);
+    return runtime::launch(kernel, stream, &config, arguments, true);
 }

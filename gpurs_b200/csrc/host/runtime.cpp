@@ -65,7 +65,7 @@ int builtin_kernel(gpurs_gpu *gpu, const char *name, uint32_t shared_bytes, gpur
     return GPURS_OK;
 }
 
-int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params) {
+int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params, bool programmatic) {
     gpurs_gpu *gpu = stream->gpu;
     CUlaunchConfig launch_config;
     std::memset(&launch_config, 0, sizeof launch_config);
@@ -77,8 +77,9 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
     launch_config.blockDimZ = config->block[2] ? config->block[2] : 1;
     launch_config.sharedMemBytes = config->shared_bytes;
     launch_config.hStream = stream->handle;
-    CUlaunchAttribute attribute;
-    std::memset(&attribute, 0, sizeof attribute);
+    CUlaunchAttribute attributes[2];
+    std::memset(attributes, 0, sizeof attributes);
+    CUlaunchAttribute &attribute = attributes[0];
     const uint32_t cluster_size = (config->cluster[0] ? config->cluster[0] : 1) * (config->cluster[1] ? config->cluster[1] : 1) *
                                   (config->cluster[2] ? config->cluster[2] : 1);
     if (cluster_size > 1) {
@@ -86,9 +87,16 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
         attribute.value.clusterDim.x = config->cluster[0] ? config->cluster[0] : 1;
         attribute.value.clusterDim.y = config->cluster[1] ? config->cluster[1] : 1;
         attribute.value.clusterDim.z = config->cluster[2] ? config->cluster[2] : 1;
-        launch_config.attrs = &attribute;
         launch_config.numAttrs = 1;
     }
+    if (programmatic) {
+        // As the reference launches its kernels (crates/gpurs/src/host/context.rs:270-281): the kernel may begin its
+        // set-up before the previous kernel of the stream has finished.
+        CUlaunchAttribute &serialization = attributes[launch_config.numAttrs++];
+        serialization.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        serialization.value.programmaticStreamSerializationAllowed = 1;
+    }
+    launch_config.attrs = launch_config.numAttrs ? attributes : nullptr;
     GPURS_TRY(gpu->api, cuLaunchKernelEx(&launch_config, kernel->function, params, nullptr));
     gpu->launches++;
     return GPURS_OK;

@@ -93,7 +93,9 @@ int fail(const char *operation, int code, const char *description);
 // The built-in kernel with the given entry name, with `shared_bytes` of dynamic shared memory reserved.
 int builtin_kernel(gpurs_gpu *gpu, const char *name, uint32_t shared_bytes, gpurs_kernel **out);
 
-int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params);
+// `programmatic`: launch with the programmatic-stream-serialization attribute (the kernel must execute
+// griddepcontrol.wait before it touches global memory; the built-in GEMMs do).
+int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config *config, void **params, bool programmatic = false);
 
 // Borrows at least `bytes` of the gpu's scratch for work about to be enqueued on `stream`; the work of
 // the previous borrower is ordered before it.  Call workspace_release once that work is enqueued.

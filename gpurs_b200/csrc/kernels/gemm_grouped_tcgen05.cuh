@@ -96,6 +96,9 @@ __device__ __forceinline__ void gemm_grouped_body(const CUtensorMap *map_w, cons
     __syncthreads();
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched no global memory and may have overlapped the previous kernel of the stream.
+    ptx::grid_dependency_wait();
+    ptx::grid_dependency_launch();
 
     int expert, first_row, end_row, tile_n;
     if (warp == 0) {

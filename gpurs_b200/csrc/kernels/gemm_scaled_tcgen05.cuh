@@ -90,6 +90,9 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     }
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched no global memory and may have overlapped the previous kernel of the stream.
+    ptx::grid_dependency_wait();
+    ptx::grid_dependency_launch();
 
     if (warp < 4) ptx::registers_decrease<PRODUCER_REGISTERS>();
     if (warp == 0) {

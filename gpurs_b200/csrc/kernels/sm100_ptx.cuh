@@ -35,6 +35,13 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
     return r;
 }
 
+// Programmatic dependent launch, as the reference's compiled kernels use it (crates/codegen/src/kernel.rs:161-171): a kernel
+// launched with the programmatic-serialization attribute may start while the previous kernel of the stream is still
+// running; `wait` blocks until that kernel has completed and its memory is visible, `launch` lets the NEXT kernel of the
+// stream start its own set-up.  Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
