@@ -45,6 +45,7 @@ WORKLOADS = {
     "e4m3_unscaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),
     "e4m3_scaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),   # fp32 scales per 1x128 / 128x128 block
     "f32_1024": ("f32", "f32", 1024, 1024, 1024),
+    "f32_4096": ("f32", "f32", 4096, 4096, 4096),
     "f16_skinny_16x4096x4096": ("f16", "f32", 16, 4096, 4096),   # the reference's decode-shaped example, bias included
     "f16_skinny_16x16384x16384": ("f16", "f32", 16, 16384, 16384),   # same shape class with a weight (512 MiB) larger than L2
     "f16_grouped_16384x4096x4096_8e": ("f16", "f16", 16384, 4096, 4096),   # 16384 routed rows over 8 experts (mixture of experts)

@@ -297,7 +297,7 @@ int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gp
     long long source_pitch = (long long)pitch;
     int row_count = int(rows), depth = int(k);
     void *arguments[6] = {&source_pointer, &source_pitch, &destination_pointer, &row_count, &depth, &order};
-    return runtime::launch(kernel, stream, &config, arguments);
+    return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
 }  // namespace
@@ -688,7 +688,7 @@ extern "C" int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_
     long long source_pitch = (long long)pitch;
     int rows = int(m), depth = int(k);
     void *arguments[7] = {&source, &source_pitch, &value_pointer, &metadata_pointer, &violation_pointer, &rows, &depth};
-    return runtime::launch(kernel, stream, &config, arguments);
+    return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
 extern "C" int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, uint32_t block_rows,
@@ -724,7 +724,7 @@ extern "C" int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t
     long long source_pitch = (long long)pitch;
     int row_count = int(rows), depth = int(k);
     void *arguments[6] = {&source_pointer, &source_pitch, &code_pointer, &scale_pointer, &row_count, &depth};
-    return runtime::launch(kernel, stream, &config, arguments);
+    return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
 extern "C" int gpurs_self_test_timeout(gpurs_stream *stream) {

@@ -37,6 +37,11 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     // barriers (four accumulators in flight instead of two).
     constexpr bool SPLIT = false;   // measured: two 128-column products per block ran slower (1359 vs 1665 TFLOP/s) than one of 256
     constexpr int HALVES = SPLIT ? 2 : 1;
+    // K-blocks multiplied into one TMEM accumulator before it is promoted.  Scales change with every block, so a scaled
+    // product promotes every block.  The unscaled form only has to keep the tensor core's truncating fp32 adds short: four
+    // blocks (16 instructions) per accumulator keep that error near 1e-6 relative and cost a quarter of the hand-offs.
+    constexpr int PERIOD = SCALED ? 1 : 4;
+    static_assert(!SPLIT, "the two-halves variant was measured slower and is not wired into the loops below");
     constexpr int MMA_N = BN / HALVES;
     constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, MMA_N);   // f32 accumulate
     constexpr int ELEMENT_BYTES = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
@@ -139,35 +144,37 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
-                for (int kb = 0; kb < k_blocks && ok; kb++) {
-                    if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
-                        report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
+                for (int first = 0; first < k_blocks && ok; first += PERIOD) {
+                    // one accumulator takes PERIOD K-blocks, then goes to the promotion warps
+                    const int slot = acc * 2;
+                    if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(slot), acc_phase ^ 1, abort_flag)) {
+                        report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, first);
                         ok = false;
                         break;
                     }
-                    const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
-#pragma unroll
-                    for (int half = 0; half < HALVES; half++) {
-                        const int slot = acc * 2 + half;
-                        if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(slot), acc_phase ^ 1, abort_flag)) {
+                    ptx::tcgen05_fence_after();
+                    const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
+                    const int last = min(first + PERIOD, k_blocks);
+                    for (int kb = first; kb < last; kb++) {
+                        if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                             report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
                             ok = false;
                             break;
                         }
                         ptx::tcgen05_fence_after();
-                        const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN + uint32_t(half) * MMA_N;
-                        const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage) + uint32_t(half) * MMA_N * ROW_BYTES);
+                        const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
+                        const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
 #pragma unroll
                         for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
                             ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
-                                                              b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(j != 0));
-                        if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(slot));
-                        else ptx::tcgen05_commit_pair(acc_full_bar(slot), 0x3);
+                                                              b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(kb != first || j != 0));
+                        if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                        else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                     if (!ok) break;
-                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
-                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(slot));
+                    else ptx::tcgen05_commit_pair(acc_full_bar(slot), 0x3);
                     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
             }
@@ -193,9 +200,9 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
 #pragma unroll
             for (int i = 0; i < SCALE_BLOCK; i++) sums[i] = 0.0f;
             float scale = SCALED ? __ldg(row_scales) * __ldg(block_scales) : 1.0f;
-            for (int kb = 0; kb < k_blocks; kb++) {
+            for (int kb = 0; kb < k_blocks; kb += PERIOD) {
                 // fetch the next block's scale while waiting for this block's products
-                const int next = min(kb + 1, k_blocks - 1);
+                const int next = min(kb + PERIOD, k_blocks - 1);
                 const float next_scale = SCALED ? __ldg(row_scales + next) * __ldg(block_scales + next) : 1.0f;
                 const int slot = acc * 2 + (SPLIT ? half : 0);
                 const bool ready = ptx::mbarrier_wait(acc_full_bar(slot), acc_phase, abort_flag);

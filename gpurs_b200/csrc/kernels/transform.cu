@@ -3,6 +3,10 @@
 // multiple of the SM count.
 #include <cstdint>
 
+// These kernels are launched with the programmatic-serialization attribute: they may be scheduled while the previous
+// kernel of the stream still runs, wait here for it to complete before touching memory, and let the next kernel in.
+#define GPURS_AFTER_PREVIOUS_KERNEL() asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory")
+
 // Splits fp32 values for a three-pass TF32 product.  Each x becomes hi = tf32(x) (round to nearest,
 // the `cvt.rna.tf32.f32` the reference uses for its TF32 operands, crates/gpurs/src/gpu/float8.rs:250-256)
 // and lo = tf32(x - hi); x - hi is exact in fp32.  The destination row is three K-wide segments,
@@ -12,6 +16,7 @@
 // by about 2^-21 relative.
 extern "C" __global__ void __launch_bounds__(256)
 gpurs_split_tf32(const float *__restrict__ source, long long source_pitch, float *__restrict__ destination, int rows, int k, int order) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
     const long long quads_per_row = k / 4;
     const long long total = (long long)rows * quads_per_row;
     for (long long index = blockIdx.x * (long long)blockDim.x + threadIdx.x; index < total; index += (long long)gridDim.x * blockDim.x) {
@@ -47,6 +52,7 @@ gpurs_split_tf32(const float *__restrict__ source, long long source_pitch, float
 extern "C" __global__ void __launch_bounds__(256)
 gpurs_compress_24(const uint16_t *__restrict__ dense, long long pitch, uint16_t *__restrict__ values, uint8_t *__restrict__ metadata,
                   unsigned int *violations, int rows, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
     const long long spans_per_row = k / 16;
     const long long total = (long long)rows * spans_per_row;
     const int k_blocks = (k + gemm::SPARSE_STAGE_K - 1) / gemm::SPARSE_STAGE_K;
@@ -152,10 +158,12 @@ __device__ __forceinline__ void quantize_e4m3_body(const float *__restrict__ sou
 
 extern "C" __global__ void __launch_bounds__(256)
 gpurs_quantize_e4m3_rows(const float *source, long long pitch, uint8_t *codes, float *scales, int rows, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
     quantize_e4m3_body<1>(source, pitch, codes, scales, rows, k);
 }
 
 extern "C" __global__ void __launch_bounds__(1024)
 gpurs_quantize_e4m3_tiles(const float *source, long long pitch, uint8_t *codes, float *scales, int rows, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
     quantize_e4m3_body<128>(source, pitch, codes, scales, rows, k);
 }
