@@ -60,6 +60,9 @@ GPURS_HOST_DEVICE StreamSchedule make_stream_schedule(int tiles, int k_blocks, i
     // Few tiles over many clusters would cut every tile into many thin parts, and whoever adds them up reads them one
     // after the other: no more than STREAM_MAX_SHARE clusters per tile take part (the rest skip the split round).
     if (split && s.split_tiles * STREAM_MAX_SHARE < clusters) s.clusters = s.split_tiles * STREAM_MAX_SHARE;
+    // Every group that takes part must get at least one unit: a group with an empty share would be counted among a tile's
+    // contributors (they are numbered as a contiguous range) and never arrive.
+    if (split && s.units < s.clusters) s.clusters = int(s.units);
     return s;
 }
 

@@ -78,3 +78,16 @@ def test_unknown_algorithm_bits_are_refused(gpu, stream):
     a_bits, b_bits = make_operands("bf16", 128, 128, 64)
     with pytest.raises(G.GpursError):
         run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, 128, 128, 64, algorithm=0x200)
+
+
+@pytest.mark.parametrize("algorithm,max_ctas,m,n,k", [(G.ALGO_CTA_PAIR, 8, 1280, 256, 256), (G.ALGO_SINGLE_CTA, 16, 2176, 256, 256),
+                                                      (G.ALGO_SINGLE_CTA, 16, 2176, 256, 384)])
+def test_fewer_k_blocks_than_groups(gpu, stream, algorithm, max_ctas, m, n, k):
+    """One tile left over and only two or three K-blocks to deal out: only as many groups take part as there are K-blocks
+    (a group with nothing to do must not be counted among the tile's contributors)."""
+    a_bits, b_bits = make_operands("i8", m, n, k)
+    whole = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
+    got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+    assert np.array_equal(got, whole)
+    rows = np.arange(0, m, 41)
+    assert np.array_equal(got.reshape(m, n)[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, n, k, rows).astype(np.int64))
