@@ -42,6 +42,7 @@ WORKLOADS = {
     "bf16_8192": ("bf16", "bf16", 8192, 8192, 8192),
     "f16_4096_example": ("f16", "f32", 4096, 4096, 4096),
     "int8_8192": ("i8", "i32", 8192, 8192, 8192),
+    "int8_shard_1024x8192x8192": ("i8", "i32", 1024, 8192, 8192),      # one GPU's share of int8_8192 split over 8
     "e4m3_unscaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),
     "e4m3_scaled_4096x7168x7168": ("e4m3", "bf16", 4096, 7168, 7168),   # fp32 scales per 1x128 / 128x128 block
     "f32_1024": ("f32", "f32", 1024, 1024, 1024),

@@ -27,6 +27,7 @@ E_DRIVER_UNAVAILABLE = 100011
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
 ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
 ALGO_WHOLE_TILES = 0x100   # flag: never split the last round's tiles along K
+ALGO_SPLIT_LAST_ROUND = 0x200   # flag: split it whenever it is not full
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
 

@@ -21,6 +21,7 @@ struct Gemm {
     gpurs_device_ptr row_absmax = 0;             // optional fp32 [m], atomic max of |C[row, :]|
     uint64_t batches = 1, stride_a = 0, stride_b = 0, stride_c = 0;   // batched entries: matrices and the elements between them
     bool whole_tiles = false;                    // never split the last round's tiles along K
+    bool force_split = false;                    // split it whenever it is not full, whether or not that pays
     bool b_row_major = false;                    // B stored k x n
     int l2_policy = 0;                           // Params::l2_policy
     gpurs_device_ptr metadata = 0;               // 2:4-sparse A only: `a` then holds the kept values, k the logical depth

@@ -61,9 +61,10 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint64_t wanted_ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     const uint64_t grid_clusters = std::min(std::max<uint64_t>(1, wanted_ctas / cta_group), std::max<uint64_t>(all_tiles, 1));
     const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
-    gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters));
-    const bool stream_k = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull &&
-                          schedule.split_tiles > 0;
+    const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull;
+    const int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
+    gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
+    const bool stream_k = split_tiles > 0;
     std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? "%s_sk_cg%d" : "%s_cg%d", g.stem, cta_group);
     const bool sparse = g.metadata != 0;
     const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
@@ -196,6 +197,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         params.partials = reinterpret_cast<void *>(partials);
         params.split_counters = reinterpret_cast<unsigned int *>(counters);
         params.max_contributors = most;
+        params.split_tiles = split_tiles;
         void *stream_arguments[4] = {&map_a, &map_b, &map_c, &params};
         result = runtime::launch(kernel, stream, &config, stream_arguments, true);
         const int released = runtime::workspace_release(stream), turned = runtime::turns_release(stream);
@@ -377,7 +379,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (desc->scale_a && (desc->scale_a % 4 || desc->scale_b % 4)) return fail(op, GPURS_E_INVALID_VIEW, "scale arrays must be 4-byte aligned");
 
     int group = desc->algorithm & 0xff;
-    if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
+    if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES | GPURS_ALGO_SPLIT_LAST_ROUND)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
+    if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
     // Kernels that promote every K-block to registers hand an accumulator back and forth once per block;
     // across a CTA pair that hand-off costs more than the pair saves, so they default to one-CTA tiles.
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
@@ -444,6 +448,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.row_scale = desc->row_scale, gemm.column_scale = desc->column_scale, gemm.alpha = desc->alpha;
     gemm.row_absmax = desc->row_absmax;
     gemm.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0;
+    gemm.force_split = (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND) != 0;
     gemm.b_row_major = b_row_major;
     gemm.gather = gather;
     gemm.batches = batches, gemm.stride_a = stride_a, gemm.stride_b = stride_b, gemm.stride_c = stride_c;

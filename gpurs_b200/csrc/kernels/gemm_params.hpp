@@ -49,7 +49,7 @@ struct Params {
     void *partials;
     unsigned int *split_counters;
     int max_contributors;
-    int reserved;               // 0
+    int split_tiles;            // tiles of the last round that are split (the host's decision, gemm_schedule.hpp)
 };
 static_assert(sizeof(Params) == 152, "the parameter block is part of the kernel image's interface");
 

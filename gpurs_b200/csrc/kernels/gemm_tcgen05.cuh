@@ -188,12 +188,12 @@ struct WorkWalker {
     int group, groups, next_tile, whole_tiles;
     long long unit, unit_end;
 
-    __device__ __forceinline__ WorkWalker(int tile_count, int k_blocks, int group_, int groups_) : group(group_), groups(groups_), next_tile(group_) {
+    __device__ __forceinline__ WorkWalker(int tile_count, int k_blocks, int group_, int groups_, int split_tiles) : group(group_), groups(groups_), next_tile(group_) {
         schedule.k_blocks = k_blocks;
         whole_tiles = tile_count;
         unit = unit_end = 0;
         if constexpr (STREAMK) {
-            schedule = make_stream_schedule(tile_count, k_blocks, groups_);
+            schedule = make_stream_schedule(tile_count, k_blocks, groups_, split_tiles);
             whole_tiles = schedule.whole_tiles;
             if (schedule.split_tiles > 0 && group_ < schedule.clusters) {
                 unit = schedule.first_unit(group_);
@@ -313,7 +313,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             const bool hinted = p.l2_policy != 0;
             const uint64_t policy_a = (p.l2_policy == 1 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
             const uint64_t policy_b = (p.l2_policy == 2 || p.l2_policy == 3) ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_first();
-            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
             WorkItem item;
             while (ok && walker.next(item)) {
                 const int tile = item.tile;
@@ -388,7 +388,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
             WorkItem item;
             while (ok && walker.next(item)) {
                 const int tile = item.tile;
@@ -434,7 +434,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
         int acc = 0;
         uint32_t acc_phase = 0;
         int stores = 0;                  // TMA stores issued by this warp: picks the staging buffer
-        WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count);
+        WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
         WorkItem item;
         while (walker.next(item)) {
             const int tile = item.tile;

@@ -183,12 +183,14 @@ enum {
     GPURS_ALGO_CTA_PAIR = 2,    /* 256 x 256 tiles shared by a 2-CTA cluster (tcgen05 cta_group::2) */
     GPURS_ALGO_SKINNY = 3,      /* m <= 64, 16-bit operands, fp32 output: B fills the tensor core's rows, K is split among CTAs
                                    and the splits add in order (the reference's SplitDepth + TileLock); AUTO picks it */
-    /* Flag, or-ed to one of the above.  By default, when the tile count leaves the last round of the persistent grid more
-     * than a quarter empty (and at least one whole round precedes it), the dense tile kernels split the K-blocks of that
-     * round's tiles over the whole grid and add the parts up in a fixed order ("stream-K", the reference's
+    /* Flags, or-ed to one of the above.  By default, when the tile count leaves the last round of the persistent grid
+     * idle enough to pay for it (and at least one whole round precedes it), the dense tile kernels split the K-blocks of
+     * that round's tiles over the grid and add the parts up in a fixed order ("stream-K", the reference's
      * schedule/stream.rs): faster, deterministic for a given shape, but the low bits of a floating-point result then
-     * depend on the shape.  With this flag every tile is multiplied whole by one CTA or CTA pair. */
-    GPURS_ALGO_WHOLE_TILES = 0x100
+     * depend on the shape.  WHOLE_TILES: every tile is multiplied whole by one CTA or CTA pair.  SPLIT_LAST_ROUND: the
+     * last round is split whenever it is not full, whether or not that pays. */
+    GPURS_ALGO_WHOLE_TILES = 0x100,
+    GPURS_ALGO_SPLIT_LAST_ROUND = 0x200
 };
 
 /* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */

@@ -13,15 +13,19 @@ HEADER_DIR = ROOT / "gpurs_b200" / "csrc" / "kernels"
 SOURCE = r"""
 #include "gemm_schedule.hpp"
 extern "C" {
+static gemm::StreamSchedule forced(int tiles, int k_blocks, int clusters) {
+    return gemm::make_stream_schedule(tiles, k_blocks, clusters, gemm::stream_split_tiles(tiles, k_blocks, clusters, true));
+}
+int policy_split_tiles(int tiles, int k_blocks, int clusters, int force) { return gemm::stream_split_tiles(tiles, k_blocks, clusters, force != 0); }
 int schedule_summary(int tiles, int k_blocks, int clusters, int *out) {
-    gemm::StreamSchedule s = gemm::make_stream_schedule(tiles, k_blocks, clusters);
+    gemm::StreamSchedule s = forced(tiles, k_blocks, clusters);
     out[0] = s.whole_tiles, out[1] = s.split_tiles, out[2] = s.clusters, out[3] = gemm::max_contributors(s);
     return 0;
 }
-long long schedule_first_unit(int tiles, int k_blocks, int clusters, int c) { return gemm::make_stream_schedule(tiles, k_blocks, clusters).first_unit(c); }
-int schedule_owner(int tiles, int k_blocks, int clusters, long long unit) { return gemm::make_stream_schedule(tiles, k_blocks, clusters).owner(unit); }
+long long schedule_first_unit(int tiles, int k_blocks, int clusters, int c) { return forced(tiles, k_blocks, clusters).first_unit(c); }
+int schedule_owner(int tiles, int k_blocks, int clusters, long long unit) { return forced(tiles, k_blocks, clusters).owner(unit); }
 int schedule_contributors(int tiles, int k_blocks, int clusters, int r, int *first) {
-    gemm::StreamSchedule s = gemm::make_stream_schedule(tiles, k_blocks, clusters);
+    gemm::StreamSchedule s = forced(tiles, k_blocks, clusters);
     *first = s.first_contributor(r);
     return s.contributors(r);
 }
@@ -50,14 +54,17 @@ def summary(lib, tiles, k_blocks, clusters):
 
 
 def test_when_the_last_round_is_split(schedule):
-    # fewer tiles than groups, exact multiples, nearly full last rounds and one-block depths go whole
-    for tiles, k_blocks, clusters in [(60, 64, 74), (148, 64, 74), (1024, 128, 74), (256, 1, 74), (74 * 3 + 60, 64, 74)]:
-        whole, split, _, _ = summary(schedule, tiles, k_blocks, clusters)
-        assert (whole, split) == (tiles, 0)
+    policy = schedule.policy_split_tiles
+    # never: fewer tiles than groups, exact multiples, one-block depths
+    for tiles, k_blocks, clusters in [(60, 64, 74), (148, 64, 74), (256, 1, 74)]:
+        assert policy(tiles, k_blocks, clusters, 0) == 0 and policy(tiles, k_blocks, clusters, 1) == 0
+    # only when forced: the idle share of the last round is worth less than about 30 K-blocks
+    for tiles, k_blocks, clusters in [(1024, 128, 74), (128, 64, 74), (74 * 3 + 60, 64, 74), (10, 8, 4)]:
+        assert policy(tiles, k_blocks, clusters, 0) == 0 and policy(tiles, k_blocks, clusters, 1) == tiles % clusters
     # the reference example on CTA pairs: 256 tiles on 74 groups = 3 whole rounds + 34 tiles over all 74 groups
-    assert summary(schedule, 256, 64, 74)[:3] == (222, 34, 74)
+    assert policy(256, 64, 74, 0) == 34 and summary(schedule, 256, 64, 74)[:3] == (222, 34, 74)
     # FP8 4096 x 7168 x 7168: 448 tiles, 4 left over: at most 4 groups per tile take part
-    assert summary(schedule, 448, 56, 74)[:3] == (444, 4, 16)
+    assert policy(448, 56, 74, 0) == 4 and summary(schedule, 448, 56, 74)[:3] == (444, 4, 16)
 
 
 @pytest.mark.parametrize("tiles,k_blocks,clusters", [(256, 64, 74), (448, 56, 74), (10, 2, 4), (15, 16, 6), (24, 18, 7), (9, 3, 8), (512, 64, 148),

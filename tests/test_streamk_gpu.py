@@ -1,7 +1,7 @@
 """Stream-K: when the tile count leaves the last round of the persistent grid mostly empty, the K-blocks of that round's
 tiles are spread over the whole grid and the parts are added up, in a fixed order, by whoever arrives last
-(crates/gpurs/src/gpu/tensor/schedule/stream.rs in the reference).  `max_ctas` shrinks the grid so that small shapes
-exercise it."""
+(crates/gpurs/src/gpu/tensor/schedule/stream.rs in the reference).  `max_ctas` shrinks the grid and ALGO_SPLIT_LAST_ROUND
+splits whether or not it pays, so that small shapes exercise it."""
 import numpy as np
 import pytest
 
@@ -28,7 +28,7 @@ def test_int8_parts_add_up_exactly(gpu, stream, algorithm, max_ctas, m, n, k):
     a_bits, b_bits = make_operands("i8", m, n, k)
     whole = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
     for _ in range(2):                      # twice: the arrival counters must be back at zero after a launch
-        got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+        got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas)
         assert np.array_equal(got, whole)
     rows = np.arange(0, m, 37)
     assert np.array_equal(got.reshape(m, n)[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, n, k, rows).astype(np.int64))
@@ -41,7 +41,7 @@ def test_exact_inputs_give_the_same_bits(gpu, stream, algorithm, max_ctas, m, n)
     k = 2048
     a_bits, b_bits = make_operands("f16", m, n, k, pattern="example")
     whole = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
-    got = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+    got = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas)
     assert np.array_equal(got, whole)
 
 
@@ -52,13 +52,13 @@ def test_float_products_stay_within_tolerance_with_epilogue(gpu, stream, kind, o
     a_bits, b_bits = make_operands(kind, m, n, k)
     bias = (np.arange(n) % 13 - 6).astype(np.float32)
     rows_scale = (1.0 + (np.arange(m) % 5) / 4.0).astype(np.float32)
-    got = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas, bias=gpu.upload(bias),
+    got = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas, bias=gpu.upload(bias),
                      row_scale=gpu.upload(rows_scale))
     rows = np.arange(0, m, 29)
     expected = O.matmul_rows(KINDS[kind][1], a_bits, b_bits, n, k, rows) * rows_scale[rows, None] + bias[None, :]
     assert relative_error(decode_output(got, out).reshape(m, n)[rows], expected) <= tolerance
     # deterministic: the parts are added in the contributors' order whoever arrives last
-    again = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas, bias=gpu.upload(bias),
+    again = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas, bias=gpu.upload(bias),
                        row_scale=gpu.upload(rows_scale))
     assert np.array_equal(got, again)
 
@@ -76,8 +76,9 @@ def test_full_grid_shape_that_splits(gpu, stream):
 
 def test_unknown_algorithm_bits_are_refused(gpu, stream):
     a_bits, b_bits = make_operands("bf16", 128, 128, 64)
-    with pytest.raises(G.GpursError):
-        run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, 128, 128, 64, algorithm=0x200)
+    for algorithm in (0x400, G.ALGO_WHOLE_TILES | G.ALGO_SPLIT_LAST_ROUND):
+        with pytest.raises(G.GpursError):
+            run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, 128, 128, 64, algorithm=algorithm)
 
 
 @pytest.mark.parametrize("algorithm,max_ctas,m,n,k", [(G.ALGO_CTA_PAIR, 8, 1280, 256, 256), (G.ALGO_SINGLE_CTA, 16, 2176, 256, 256),
@@ -87,7 +88,7 @@ def test_fewer_k_blocks_than_groups(gpu, stream, algorithm, max_ctas, m, n, k):
     (a group with nothing to do must not be counted among the tile's contributors)."""
     a_bits, b_bits = make_operands("i8", m, n, k)
     whole = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
-    got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm, max_ctas=max_ctas)
+    got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas)
     assert np.array_equal(got, whole)
     rows = np.arange(0, m, 41)
     assert np.array_equal(got.reshape(m, n)[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, n, k, rows).astype(np.int64))
