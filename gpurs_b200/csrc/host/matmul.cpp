@@ -84,8 +84,10 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint64_t stride_a[1] = {g.lda * eb}, stride_b[1] = {g.ldb * eb};
     const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)};
     // B as n x k: one box of (128 bytes of k) x (the tile's rows of n).  B as k x n: boxes of (128 bytes of n) x (block_k rows of k).
+    // columns of one tile: 256, or 224 for the sparse kernels (two accumulators plus metadata in tensor memory)
+    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : uint64_t(gemm::BLOCK_N);
     uint64_t dims_b[2] = {g.k, g.n};
-    uint32_t box_b[2] = {block_k, uint32_t(gemm::BLOCK_N / cta_group)};
+    uint32_t box_b[2] = {block_k, uint32_t(block_n / cta_group)};
     if (g.b_row_major) {
         dims_b[0] = g.n, dims_b[1] = g.k;
         box_b[0] = uint32_t(gemm::ROW_BYTES / g.element_bytes), box_b[1] = block_k;
@@ -125,7 +127,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.k = int(g.k);
     const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
     params.tiles_m = int((g.m + tile_rows - 1) / tile_rows);
-    params.tiles_n = int((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
+    params.tiles_n = int((g.n + block_n - 1) / block_n);
     // Bands of 2048 rows by default: with one tile per SM in flight, the tiles running together then
     // cover about 2048 x 2304 outputs, a near-square patch whose A and B panels are shared through L2.
     params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16 / cta_group;

@@ -91,10 +91,13 @@ constexpr int skinny_shared_bytes(int tokens) { return 8 * (BLOCK_M * ROW_BYTES 
 constexpr int SKINNY_MAX_ROWS = 64;      // m up to which the skinny kernels are used
 constexpr int SKINNY_MAX_TILES = 4096;   // turn counters kept per gpu handle
 
-// 2:4 sparse kernels (gemm_sparse_tcgen05.cuh): dynamic shared memory of the one-CTA (2 stages of 82 KiB) and
-// CTA-pair (4 stages of 50 KiB) entries, and the size of one metadata block (128 rows x 128 logical K).
-constexpr int SPARSE_SHARED_SINGLE = 2 * (BLOCK_M * ROW_BYTES + 2 * BLOCK_N * ROW_BYTES + 2048) + (2 * 2 + 2) * 8 + 8 + 1024;
-constexpr int SPARSE_SHARED_PAIR = 4 * (BLOCK_M * ROW_BYTES + BLOCK_N * ROW_BYTES + 2048) + (2 * 4 + 2) * 8 + 8 + 1024;
+// 2:4 sparse kernels (gemm_sparse_tcgen05.cuh).  Their tiles are 224 columns wide: two accumulators of 224 columns and the
+// 16 metadata columns of the pipeline stages fit the 512 columns of tensor memory (2 x 256 + 16 would not), so that a
+// tile's epilogue overlaps the next tile's main loop.  Dynamic shared memory of the one-CTA (2 stages of 74 KiB) and
+// CTA-pair (4 stages of 46 KiB) entries, and the size of one metadata block (128 rows x 128 logical K).
+constexpr int SPARSE_BLOCK_N = 224;
+constexpr int SPARSE_SHARED_SINGLE = 2 * (BLOCK_M * ROW_BYTES + 2 * SPARSE_BLOCK_N * ROW_BYTES + 2048) + (2 * 2 + 4) * 8 + 8 + 1024;
+constexpr int SPARSE_SHARED_PAIR = 4 * (BLOCK_M * ROW_BYTES + SPARSE_BLOCK_N * ROW_BYTES + 2048) + (2 * 4 + 4) * 8 + 8 + 1024;
 constexpr int SPARSE_METADATA_BLOCK_BYTES = 2048;
 constexpr int SPARSE_BLOCK_K = 128;
 

@@ -11,9 +11,9 @@
 // One pipeline stage is 128 logical K: 128 bytes of compressed A per row, two 128-byte-swizzled tiles of B
 // (logical K 0..63 and 64..127) and one metadata block.  The MMA thread copies the block into tensor memory
 // (tcgen05.cp, 4 columns) and issues 4 tcgen05.mma.sp of 32 logical K each, one metadata column apiece.
-// Tensor memory: one 256-column accumulator plus 4 metadata columns per stage.  With a single accumulator
-// the epilogue of a tile is not overlapped with the next tile's main loop (about 2000 of 34000 cycles per
-// tile at K = 8192).
+// Tensor memory: two accumulators of 224 columns (tiles are 224 columns wide for that reason: the epilogue of a tile
+// overlaps the main loop of the next) plus 4 metadata columns per stage.  With one 256-column accumulator the exposed
+// epilogue and hand-over cost about 4 us per tile, 15 % at K = 8192 (measured by varying K).
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -34,18 +34,18 @@ __host__ __device__ inline int metadata_offset(int row, int k) {
 template <int CTA_GROUP, int STAGES>
 struct SparseLayout {
     static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;                   // 128 rows x 64 kept elements
-    static constexpr int B_ROWS = BLOCK_N / CTA_GROUP;
+    static constexpr int B_ROWS = SPARSE_BLOCK_N / CTA_GROUP;
     static constexpr int B_HALF_BYTES = B_ROWS * ROW_BYTES;               // one 64-deep half of the B tile
     static constexpr int STAGE_BYTES = A_BYTES + 2 * B_HALF_BYTES + METADATA_BLOCK_BYTES;
     static constexpr int BARRIER_OFFSET = ((STAGES * STAGE_BYTES + 1023) / 1024) * 1024;
-    static constexpr int NUM_BARRIERS = 2 * STAGES + 2;                   // full, empty, accumulator full / empty
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 4;                   // full, empty, two accumulators' full / empty
     static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
     static constexpr int DYNAMIC_BYTES = ABORT_OFFSET + 4 + 1024;
 };
 
-constexpr int SPARSE_STAGES_SINGLE = 2;   // 82 KiB per stage
-constexpr int SPARSE_STAGES_PAIR = 4;     // 50 KiB per stage and CTA
+constexpr int SPARSE_STAGES_SINGLE = 2;   // 74 KiB per stage
+constexpr int SPARSE_STAGES_PAIR = 4;     // 46 KiB per stage and CTA
 static_assert(SparseLayout<1, SPARSE_STAGES_SINGLE>::DYNAMIC_BYTES == SPARSE_SHARED_SINGLE, "host and kernel disagree on shared memory");
 static_assert(SparseLayout<2, SPARSE_STAGES_PAIR>::DYNAMIC_BYTES == SPARSE_SHARED_PAIR, "host and kernel disagree on shared memory");
 static_assert(METADATA_BLOCK_BYTES == SPARSE_METADATA_BLOCK_BYTES && SPARSE_STAGE_K == SPARSE_BLOCK_K, "host and kernel disagree on the metadata block");
@@ -54,9 +54,10 @@ static_assert(METADATA_BLOCK_BYTES == SPARSE_METADATA_BLOCK_BYTES && SPARSE_STAG
 template <int ELEMENT_FORMAT, int OUT, int CTA_GROUP, int STAGES>
 __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_e, const Params &p) {
     using L = SparseLayout<CTA_GROUP, STAGES>;
-    constexpr int BN = BLOCK_N;
+    constexpr int BN = SPARSE_BLOCK_N;
     constexpr uint32_t TMEM_COLUMNS = 512;
-    constexpr uint32_t METADATA_COLUMN = BN;      // metadata of stage s: columns BN + 4*s .. +3
+    constexpr uint32_t METADATA_COLUMN = 2 * BN;  // metadata of stage s: columns 2*BN + 4*s .. +3, after the two accumulators
+    static_assert(2 * BN + 4 * STAGES <= 512 && BN % 32 == 0, "two accumulators and the metadata must fit tensor memory");
     // sparse flag (bit 2) on top of the dense descriptor
     constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, BN) | (1u << 2);
     static_assert(L::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
@@ -72,8 +73,8 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
     auto stage_e = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES + 2 * L::B_HALF_BYTES; };
     auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
     auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
-    const uint32_t acc_full_bar = base + L::BARRIER_OFFSET + uint32_t(2 * STAGES) * 8;
-    const uint32_t acc_empty_bar = base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 1) * 8;
+    auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
+    auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 2 + a) * 8; };
 
     const int warp = threadIdx.x / 32;
     const uint32_t lane = ptx::lane_id();
@@ -90,8 +91,10 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
             ptx::mbarrier_init(full_bar(s), 1);
             ptx::mbarrier_init(empty_bar(s), 1);
         }
-        ptx::mbarrier_init(acc_full_bar, 1);
-        ptx::mbarrier_init(acc_empty_bar, EPILOGUE_WARPS * CTA_GROUP);
+        for (int a = 0; a < 2; a++) {
+            ptx::mbarrier_init(acc_full_bar(a), 1);
+            ptx::mbarrier_init(acc_empty_bar(a), EPILOGUE_WARPS * CTA_GROUP);
+        }
         ptx::fence_mbarrier_init();
         ptx::prefetch_tensor_map(map_a);
         ptx::prefetch_tensor_map(map_b);
@@ -160,13 +163,15 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
         if (lane == 0 && leader) {
             int stage = 0;
             uint32_t phase = 0, acc_phase = 0;
+            int acc = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
-                if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar, acc_phase ^ 1, abort_flag)) {
+                if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
                     report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
                     break;
                 }
                 ptx::tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                         report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
@@ -184,7 +189,7 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
                         // The instruction takes the metadata column pair (an even column address) and, in bits 0..1 of
                         // its descriptor, which column of the pair to use.
                         const uint32_t column = metadata_tmem + uint32_t(j);
-                        ptx::tcgen05_mma_sparse_f16<CTA_GROUP>(tmem_base, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc,
+                        ptx::tcgen05_mma_sparse_f16<CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc,
                                                                column & ~1u, IDESC | (column & 1u), uint32_t((kb | j) != 0));
                     }
                     if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
@@ -192,26 +197,27 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar);
-                else ptx::tcgen05_commit_pair(acc_full_bar, 0x3);
-                acc_phase ^= 1;
+                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(acc));
+                else ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (single accumulator)
+        // ------------------------------------------------------------------ epilogue
         const int quadrant = warp % 4;
         uint32_t acc_phase = 0;
+        int acc = 0;
         for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
-            const bool ready = ptx::mbarrier_wait(acc_full_bar, acc_phase, abort_flag);
+            const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) {
                 if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, -1);
                 break;
             }
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
-            const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16);
+            const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN;
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; chunk++) {
                 uint32_t values[32];
@@ -222,10 +228,10 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
             ptx::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar);
-                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar, 0));
+                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
             }
-            acc_phase ^= 1;
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
 
