@@ -203,4 +203,65 @@ void matmul(const Stream &stream, const DeviceBuffer<A> &a, const DeviceBuffer<A
     check(gpurs_matmul(stream.raw(), &desc, a.address(), b.address(), c.address()));
 }
 
+// The same product with operands and result in host memory (page-locked for the copies to overlap), staged through the
+// device buffers: the example's upload / upload / launch / download as one call that overlaps the three.  Does not
+// wait: synchronise `stream` before reading `host_c`.
+template <class A, class C>
+void matmul_host(const Stream &stream, const A *host_a, const A *host_b, C *host_c, DeviceBuffer<A> &a, DeviceBuffer<A> &b, DeviceBuffer<C> &c,
+                 std::array<size_t, 3> shape, const MatmulOptions &options = {}) {
+    gpurs_matmul_desc desc{};
+    desc.a_type = Element<A>::code;
+    desc.c_type = Element<C>::code;
+    desc.m = shape[0], desc.n = shape[1], desc.k = shape[2];
+    desc.lda = options.lda, desc.ldb = options.ldb, desc.ldc = options.ldc;
+    desc.algorithm = options.algorithm;
+    desc.precision = options.precision;
+    desc.scale_a = options.scale_a, desc.scale_b = options.scale_b;
+    desc.b_row_major = options.b_row_major ? 1 : 0;
+    desc.bias = options.bias, desc.row_scale = options.row_scale, desc.column_scale = options.column_scale, desc.alpha = options.alpha;
+    check(gpurs_matmul_host(stream.raw(), &desc, host_a, host_b, host_c, a.address(), b.address(), c.address()));
+}
+
+// output[r] = input[routes[r]] * weight[e]^T for offsets[e] <= r < offsets[e + 1]: the grouped (mixture-of-experts) product
+// of the reference's `experts` example (examples/ada/examples/grouped_matrix.rs:30-60).
+template <class A, class C>
+void matmul_grouped(const Stream &stream, const DeviceBuffer<A> &input, const DeviceBuffer<uint32_t> &routes, const DeviceBuffer<uint32_t> &offsets,
+                    const DeviceBuffer<A> &weight, DeviceBuffer<C> &output, size_t rows, size_t tokens, size_t n, size_t k, size_t experts) {
+    gpurs_grouped_desc desc{};
+    desc.a_type = Element<A>::code;
+    desc.c_type = Element<C>::code;
+    desc.rows = rows, desc.tokens = tokens, desc.n = n, desc.k = k, desc.experts = experts;
+    check(gpurs_matmul_grouped(stream.raw(), &desc, input.address(), routes.address(), offsets.address(), weight.address(), output.address()));
+}
+
+// A recorded sequence of the calls above (`Graph` / `GraphExec`, crates/gpurs/src/host/graph/capture.rs:99-149, exec.rs:15-72).
+class Graph {
+  public:
+    Graph(Graph &&other) noexcept : handle_(std::exchange(other.handle_, nullptr)) {}
+    Graph(const Graph &) = delete;
+    ~Graph() { gpurs_graph_free(handle_); }
+    // Enqueues one replay of the whole recording on `stream`; does not wait.
+    void launch(const Stream &stream) const { check(gpurs_graph_launch(handle_, stream.raw())); }
+
+  private:
+    template <class F> friend Graph capture(const Stream &stream, F &&record);
+    explicit Graph(gpurs_graph *handle) : handle_(handle) {}
+    gpurs_graph *handle_;
+};
+
+// `stream.capture(|capture| { ... })`: runs `record(stream)` with the stream recording instead of executing.
+template <class F>
+Graph capture(const Stream &stream, F &&record) {
+    check(gpurs_stream_capture_begin(stream.raw()));
+    gpurs_graph *handle = nullptr;
+    try {
+        record(stream);
+    } catch (...) {
+        if (gpurs_stream_capture_end(stream.raw(), &handle) == GPURS_OK) gpurs_graph_free(handle);
+        throw;
+    }
+    check(gpurs_stream_capture_end(stream.raw(), &handle));
+    return Graph(handle);
+}
+
 }  // namespace gpurs
