@@ -48,6 +48,8 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int accumulator_fo
 
 // Tile index -> (tile row, tile column): bands of `raster_rows` tile rows are walked column by column,
 // the same idea as the reference's Swizzle<8> raster (crates/gpurs/src/gpu/tensor/schedule/grid.rs:55-82).
+// Odd bands walk their columns backwards, so that the columns of B in L2 at the end of a band are the first
+// ones the next band asks for.
 __device__ __forceinline__ void tile_position(int tile, const Params &p, int &tile_m, int &tile_n) {
     int band_tiles = p.raster_rows * p.tiles_n;
     int band = tile / band_tiles;
@@ -55,7 +57,7 @@ __device__ __forceinline__ void tile_position(int tile, const Params &p, int &ti
     int rows = min(p.raster_rows, p.tiles_m - first_row);
     int local = tile - band * band_tiles;
     tile_m = first_row + local % rows;
-    tile_n = local / rows;
+    tile_n = (band & 1) ? p.tiles_n - 1 - local / rows : local / rows;
 }
 
 __device__ __forceinline__ void report_status(unsigned int *status, volatile uint32_t *abort_flag, uint32_t code, int tile, int k_block) {
