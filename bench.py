@@ -56,7 +56,7 @@ DEFAULT_WORKLOAD = "bf16_8192"
 
 # DRAM bytes moved by one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
 # an ncu capture, see profiles/); None until a capture of that workload has been taken.
-MEASURED_TRAFFIC = {"bf16_8192": 1_213_700_000}   # profiles/gemm_bf16_bf16_cg2_8192.md: 1.0859 GB read + 127.9 MB written
+MEASURED_TRAFFIC = {"bf16_8192": 1_156_000_000}   # profiles/gemm_bf16_bf16_cg2_8192.md: 1.0859 GB read + 127.9 MB written
 
 
 def bf16_bits(values: np.ndarray) -> np.ndarray:
@@ -138,6 +138,17 @@ def measured_peak_tflops() -> tuple[float, str]:
     if path.exists():
         return float(json.loads(path.read_text())["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
     return 1590.0, "fallback (earlier measurement on this pool)"
+
+
+def sustained_peak_tflops(kind: str):
+    """The seconds-long cuBLAS bf16 figure of MEASURED_PEAKS.json, scaled like the burst one (x2 for 8-bit, /2 for TF32)."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    if not path.exists():
+        return None
+    value = json.loads(path.read_text()).get("bf16_tflops_sustained")
+    if not value:
+        return None
+    return float(value) * (2.0 if kind in ("i8", "e4m3") else 0.5 if kind == "f32" else 1.0)
 
 
 def cpu_band(kind: str, n: int, k: int, rows: int, seed: int = 1):
@@ -389,6 +400,16 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
             dist.barrier()
             gathered.close()
         del c_block, borrowed
+    # Single launches with idle gaps, best of 10: the protocol of the burst figure in MEASURED_PEAKS.json (the timed region
+    # above is 100 back-to-back launches, which run into the power cap like that file's sustained figure).
+    isolated = []
+    for _ in range(10):
+        time.sleep(0.02)
+        first, _unused = stream.record_timed(), launch()
+        last = stream.record_timed()
+        stream.synchronize()
+        isolated.append(first.elapsed_ms(last))
+    burst_tflops = flops_per_step / (min(isolated) * 1e-3) / 1e12
     status = gpu.status()
 
     if rank == 0:
@@ -414,7 +435,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
                          "traffic": MEASURED_TRAFFIC.get(args.workload), "peak_source": peak_source,
                          "frac_of_nominal": per_gpu_tflops / NOMINAL_PEAK[kind], "nominal_peak": NOMINAL_PEAK[kind],
                          "algorithmic_flops_per_launch": flops_per_step,
-                         "algorithmic_bytes_per_launch": int(a_host.nbytes + b_host.nbytes + m * n * out_bytes)},
+                         "algorithmic_bytes_per_launch": int(a_host.nbytes + b_host.nbytes + m * n * out_bytes),
+                         "single_launch": {"achieved": burst_tflops, "ms": min(isolated), "frac": burst_tflops / peak,
+                                           "protocol": "best of 10 single launches 20 ms apart (the burst protocol of the peak)"},
+                         "frac_of_sustained_peak": (per_gpu_tflops / sustained_peak_tflops(kind)) if sustained_peak_tflops(kind) else None},
             "device_status": status,
         }
         if gather is not None:
