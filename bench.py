@@ -56,7 +56,7 @@ DEFAULT_WORKLOAD = "bf16_8192"
 
 # DRAM bytes moved by one launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from
 # an ncu capture, see profiles/); None until a capture of that workload has been taken.
-MEASURED_TRAFFIC = {"bf16_8192": 1_156_000_000}   # profiles/gemm_bf16_bf16_cg2_8192.md: 1.0859 GB read + 127.9 MB written
+MEASURED_TRAFFIC = {"bf16_8192": 1_156_000_000}   # profiles/gemm_bf16_bf16_cg2_8192.md, second capture: 1.024 GB read + 132 MB written
 
 
 def bf16_bits(values: np.ndarray) -> np.ndarray:
