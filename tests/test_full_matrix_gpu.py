@@ -73,3 +73,58 @@ def test_int8_8192_whole_matrix_is_exact(gpu, stream):
     rows = np.arange(0, size, 521)
     assert np.array_equal(theirs[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, size, size, rows).astype(np.int64))
     assert np.array_equal(ours, theirs)
+
+
+def test_block_scaled_fp8_whole_matrix(gpu, stream):
+    """C3, 4096 x 7168 x 7168 block-scaled E4M3 -> bf16: all 29 million outputs within 2e-2 of an fp32 CUDA-core product of the
+    dequantised operands (codes times their block scales, which is exact in fp32), itself within 1e-3 of the oracle's fp64
+    product on sampled rows (fp32 summation over K = 7168; measured 3e-4)."""
+    m, n, k = 4096, 7168, 7168
+    a_source, b_source = O.fill_normal_f32(m * k, 1), O.fill_normal_f32(n * k, 2)
+    a_codes, a_scales = O.quantize_e4m3(a_source, m, k, 1)
+    b_codes, b_scales = O.quantize_e4m3(b_source, n, k, 128)
+    del a_source, b_source
+    ours = O.bf16_to_f32(run_matmul(gpu, stream, "e4m3", "bf16", a_codes, b_codes, m, n, k, scale_a=gpu.upload(a_scales),
+                                    scale_b=gpu.upload(b_scales))).reshape(m, n)
+    k_blocks = k // 128
+    a = torch.from_numpy(a_codes.reshape(m, k).copy()).cuda().view(torch.float8_e4m3fn).float()
+    a = (a.view(m, k_blocks, 128) * torch.from_numpy(a_scales.reshape(m, k_blocks, 1)).cuda()).view(m, k)
+    b = torch.from_numpy(b_codes.reshape(n, k).copy()).cuda().view(torch.float8_e4m3fn).float()
+    b = (b.view(n // 128, 128, k_blocks, 128) * torch.from_numpy(b_scales.reshape(n // 128, 1, k_blocks, 1)).cuda()).view(n, k)
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        theirs = torch.matmul(a, b.T).cpu().numpy()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = previous
+    del a, b
+    rows = np.arange(0, m, 331)
+    expected = O.matmul_rows(O.FMT_E4M3, a_codes, b_codes, n, k, rows, a_scales, b_scales)
+    assert relative_error(theirs[rows].astype(np.float64), expected) <= 1e-3
+    error = np.abs(ours - theirs) / np.maximum(np.abs(theirs), 1.0)
+    assert float(error.max()) <= 2e-2
+    assert not np.isnan(ours).any()
+
+
+def test_sparse_shard_whole_matrix(gpu, stream):
+    """C5, one GPU's shard 2048 x 8192 (2:4) x 8192 -> bf16: all 16.8 million outputs within 1e-2 of the library's dense
+    product of the densified operand (the definition of the sparse product), which is within 1e-2 of the oracle on
+    sampled rows."""
+    m, n, k = 2048, 8192, 8192
+    dense = O.fill_sparse24_bf16(m, k, 3)
+    b_bits = O.fill_normal_16(O.FMT_BF16, n * k, 4)
+    values, metadata, violations = G.compress_24(stream, gpu.upload(dense, G.BF16), m, k)
+    c = gpu.zeros(G.BF16, m * n)
+    G.matmul(stream, values, gpu.upload(b_bits, G.BF16), c, [m, n, k], G.MatmulOptions(metadata=metadata))
+    stream.synchronize()
+    assert violations.download()[0] == 0
+    ours = O.bf16_to_f32(c.download()).reshape(m, n)
+    a = as_tensor(dense.view(np.int16), m, k, torch.bfloat16)
+    b = as_tensor(b_bits.view(np.int16), n, k, torch.bfloat16)
+    theirs = torch.matmul(a, b.T).float().cpu().numpy()
+    del a, b
+    rows = np.arange(0, m, 131)
+    expected = O.matmul_rows(O.FMT_BF16, dense, b_bits, n, k, rows)
+    assert relative_error(theirs[rows].astype(np.float64), expected) <= 1e-2
+    error = np.abs(ours - theirs) / np.maximum(np.abs(theirs), 1.0)
+    assert float(error.max()) <= 1e-2
