@@ -29,6 +29,7 @@ ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
 ALGO_WHOLE_TILES = 0x100   # flag: never split the last round's tiles along K
 ALGO_SPLIT_LAST_ROUND = 0x200   # flag: split it whenever it is not full
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
+SCALES_FP32_BLOCKS, SCALES_MX = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
 
 
@@ -47,6 +48,7 @@ class MatmulDesc(C.Structure):
         ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
         ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("batches", C.c_int32),
         ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_c", C.c_uint64), ("row_absmax", C.c_uint64),
+        ("scale_kind", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -105,6 +107,8 @@ SIGNATURES = {
     "gpurs_kernel_image": (_P, [C.POINTER(C.c_size_t)]),
     "gpurs_matmul": (C.c_int, [_P, C.POINTER(MatmulDesc), C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_quantize_e4m3": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint64]),
+    "gpurs_mx_scale_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64, C.c_int]),
+    "gpurs_quantize_mx_e4m3": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int, C.c_uint64, C.c_uint64]),
     "gpurs_metadata_bytes": (C.c_size_t, [C.c_uint64, C.c_uint64]),
     "gpurs_compress_24": (C.c_int, [_P, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_f32_static": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),

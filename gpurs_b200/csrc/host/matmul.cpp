@@ -215,6 +215,56 @@ namespace {
 
 using launcher::launch_gemm;
 
+// The FP8 product with the tensor core's own block scaling (kernels/gemm_mx_tcgen05.cuh): operand descriptors as for the
+// dense kernels (224-row boxes of B), plus the two tiled scale arrays as rows of 16 bytes.
+int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
+    gpurs_gpu *gpu = stream->gpu;
+    char name[96];
+    std::snprintf(name, sizeof name, "%s_cg1", g.stem);
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, name, uint32_t(gemm::MX_SHARED_BYTES), &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t k_blocks = (g.k + 127) / 128, tiles_m = (g.m + 127) / 128, tiles_n = (g.n + gemm::MX_BLOCK_N - 1) / gemm::MX_BLOCK_N;
+    alignas(64) CUtensorMap map_a, map_b, map_sa, map_sb;
+    const uint64_t dims_a[2] = {g.k, g.m}, dims_b[2] = {g.k, g.n}, stride_a[1] = {g.lda}, stride_b[1] = {g.ldb};
+    const uint32_t box_a[2] = {128, uint32_t(gemm::BLOCK_M)}, box_b[2] = {128, uint32_t(gemm::MX_BLOCK_N)};
+    result = gpurs_tensor_map_encode(gpu, &map_a, GPURS_E4M3, 2, g.a, dims_a, stride_a, box_a, 3, 3);
+    if (result != GPURS_OK) return result;
+    result = gpurs_tensor_map_encode(gpu, &map_b, GPURS_E4M3, 2, g.b, dims_b, stride_b, box_b, 3, 3);
+    if (result != GPURS_OK) return result;
+    const uint64_t dims_sa[2] = {16, tiles_m * k_blocks * 32}, dims_sb[2] = {16, tiles_n * k_blocks * 64}, stride_s[1] = {16};
+    const uint32_t box_sa[2] = {16, 32}, box_sb[2] = {16, 64};
+    result = gpurs_tensor_map_encode(gpu, &map_sa, GPURS_I8, 2, g.scale_a, dims_sa, stride_s, box_sa, 0, 3);
+    if (result != GPURS_OK) return result;
+    result = gpurs_tensor_map_encode(gpu, &map_sb, GPURS_I8, 2, g.scale_b, dims_sb, stride_s, box_sb, 0, 3);
+    if (result != GPURS_OK) return result;
+
+    gemm::Params params;
+    std::memset(&params, 0, sizeof params);
+    params.c = reinterpret_cast<void *>(g.c);
+    params.ldc = (long long)g.ldc;
+    params.m = int(g.m), params.n = int(g.n), params.k = int(g.k);
+    params.tiles_m = int(tiles_m), params.tiles_n = int(tiles_n);
+    params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16;
+    params.vector_stores = (g.c % 16 == 0 && (g.ldc * uint64_t(g.output_bytes)) % 16 == 0) ? 1 : 0;
+    params.status = reinterpret_cast<unsigned int *>(gpu->status);
+    params.bias = reinterpret_cast<const float *>(g.bias);
+    params.row_scale = reinterpret_cast<const float *>(g.row_scale);
+    params.column_scale = reinterpret_cast<const float *>(g.column_scale);
+    params.alpha = g.alpha;
+    params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
+    const uint64_t tiles = tiles_m * tiles_n;
+    if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
+    const uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::min(ctas, tiles));
+    config.block[0] = uint32_t(gemm::NUM_THREADS);
+    config.shared_bytes = uint32_t(gemm::MX_SHARED_BYTES);
+    void *arguments[5] = {&map_a, &map_b, &map_sa, &map_sb, &params};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
 // Host mirror of gemm::SkinnyParams (kernels/gemm_skinny_tcgen05.cuh).
 struct SkinnyParams {
     float *c;
@@ -379,6 +429,29 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         return fail(op, GPURS_E_INVALID_ARGUMENT, "both scale arrays or neither must be given");
     if (desc->scale_a && desc->a_type != GPURS_E4M3) return fail(op, GPURS_E_INVALID_ARGUMENT, "scales are for E4M3 operands only");
     if (desc->scale_a && (desc->scale_a % 4 || desc->scale_b % 4)) return fail(op, GPURS_E_INVALID_VIEW, "scale arrays must be 4-byte aligned");
+    if (desc->scale_kind != GPURS_SCALES_FP32_BLOCKS && desc->scale_kind != GPURS_SCALES_MX) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown scale kind");
+    if (desc->scale_kind == GPURS_SCALES_MX) {
+        // Power-of-two scales per 32 elements, applied by the tensor core: its own kernel, dispatched here.
+        if (!desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "both scale arrays or neither must be given");
+        if (desc->c_type != GPURS_BF16 && desc->c_type != GPURS_F32)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
+        if (sparse || b_row_major || batches > 1 || gather || desc->row_absmax || (desc->algorithm & 0xff) > GPURS_ALGO_SINGLE_CTA)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the MX-scaled product is a single dense n x k product on one-CTA tiles");
+        if (k % 128) return fail(op, GPURS_E_INVALID_VIEW, "the depth of an MX-scaled product must be a multiple of 128");
+        if (desc->scale_a % 16 || desc->scale_b % 16) return fail(op, GPURS_E_INVALID_VIEW, "MX scale arrays must be 16-byte aligned");
+        if (desc->bias % 4 || desc->row_scale % 4 || desc->column_scale % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
+        if (desc->alpha != desc->alpha) return fail(op, GPURS_E_INVALID_ARGUMENT, "alpha is not a number");
+        Gemm mx;
+        mx.stem = desc->c_type == GPURS_BF16 ? "gpurs_gemm_e4m3_mx_bf16" : "gpurs_gemm_e4m3_mx_f32";
+        mx.element_type = desc->a_type, mx.element_bytes = 1, mx.output_bytes = choice.output_bytes, mx.output_type = desc->c_type;
+        mx.a = a, mx.b = b, mx.c = c;
+        mx.lda = lda, mx.ldb = ldb, mx.ldc = ldc;
+        mx.m = m, mx.n = n, mx.k = k;
+        mx.cta_group = 1, mx.raster_rows = desc->raster_rows, mx.max_ctas = desc->max_ctas;
+        mx.scale_a = desc->scale_a, mx.scale_b = desc->scale_b;
+        mx.bias = desc->bias, mx.row_scale = desc->row_scale, mx.column_scale = desc->column_scale, mx.alpha = desc->alpha;
+        return launch_mx(stream, mx);
+    }
 
     int group = desc->algorithm & 0xff;
     if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES | GPURS_ALGO_SPLIT_LAST_ROUND)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
@@ -551,6 +624,7 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
     if (desc->metadata) return fail(op, GPURS_E_INVALID_ARGUMENT, "a 2:4-sparse operand is prepared on the device: use gpurs_matmul");
     if (desc->batches > 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "the host-buffer product takes a single product");
+    if (desc->scale_kind != GPURS_SCALES_FP32_BLOCKS) return fail(op, GPURS_E_INVALID_ARGUMENT, "the host-buffer product takes fp32 block scales only");
     const uint64_t m = desc->m, n = desc->n, k = desc->k;
     if (m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
         return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
@@ -731,6 +805,46 @@ extern "C" int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t
     long long source_pitch = (long long)pitch;
     int row_count = int(rows), depth = int(k);
     void *arguments[6] = {&source_pointer, &source_pitch, &code_pointer, &scale_pointer, &row_count, &depth};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
+extern "C" size_t gpurs_mx_scale_bytes(uint64_t rows, uint64_t k, int right_operand) {
+    const uint64_t k_blocks = (k + 127) / 128;
+    return right_operand ? size_t(((rows + gemm::MX_BLOCK_N - 1) / gemm::MX_BLOCK_N) * k_blocks * 1024) : size_t(((rows + 127) / 128) * k_blocks * 512);
+}
+
+extern "C" int gpurs_quantize_mx_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, int right_operand,
+                                      gpurs_device_ptr codes, gpurs_device_ptr scales) {
+    const char *const op = "gpurs_quantize_mx_e4m3";
+    if (!stream) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream");
+    if (right_operand != 0 && right_operand != 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "right_operand must be 0 or 1");
+    if (rows > 0x7fffffffull || k > 0x7fffffffull) return fail(op, GPURS_E_SIZE_OVERFLOW, "a matrix dimension exceeds 2^31 - 1");
+    if (rows == 0 || k == 0) return GPURS_OK;
+    const uint64_t pitch = ld ? ld : k;
+    if (pitch < k) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+    if (!source || !codes || !scales) return fail(op, GPURS_E_INVALID_ARGUMENT, "null argument");
+    if (k % 4 || source % 16 || (pitch * 4) % 16 || codes % 4 || scales % 16)
+        return fail(op, GPURS_E_INVALID_VIEW, "k must be a multiple of 4, the source and the scales 16-byte aligned, the codes 4-byte aligned");
+    const uint64_t source_bytes = ((rows - 1) * pitch + k) * 4, scale_bytes = gpurs_mx_scale_bytes(rows, k, right_operand);
+    if (overlap(codes, rows * k, source, source_bytes) || overlap(scales, scale_bytes, source, source_bytes) || overlap(scales, scale_bytes, codes, rows * k))
+        return fail(op, GPURS_E_ALIASING, "an output overlaps the input or the other output");
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_quantize_mx_e4m3", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    // entries of the tiled array that no element maps to (rows past the matrix, the unused quarter of B's second block): scale 1
+    GPURS_TRY(gpu->api, cuMemsetD8Async(scales, 127, scale_bytes, stream->handle));
+    const uint64_t spans = rows * ((k + 127) / 128);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>((spans + 7) / 8, uint64_t(gpu->multiprocessors) * 8)));
+    config.block[0] = 256;
+    const void *source_pointer = reinterpret_cast<const void *>(source);
+    void *code_pointer = reinterpret_cast<void *>(codes), *scale_pointer = reinterpret_cast<void *>(scales);
+    long long source_pitch = (long long)pitch;
+    int row_count = int(rows), depth = int(k), right = right_operand;
+    void *arguments[7] = {&source_pointer, &source_pitch, &code_pointer, &scale_pointer, &row_count, &depth, &right};
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
 

@@ -1,0 +1,13 @@
+// Entry points of the FP8 GEMM with the tensor core's own (MX, power-of-two) block scaling (see gemm_mx_tcgen05.cuh).
+#include "gemm_mx_tcgen05.cuh"
+
+#define GPURS_MX_KERNEL(NAME, OUT)                                                                                   \
+    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                               \
+    NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                       \
+         const __grid_constant__ CUtensorMap map_sa, const __grid_constant__ CUtensorMap map_sb,                     \
+         const __grid_constant__ gemm::Params params) {                                                              \
+        gemm::gemm_mx_body<OUT, gemm::MX_STAGES>(&map_a, &map_b, &map_sa, &map_sb, params);                          \
+    }
+
+GPURS_MX_KERNEL(gpurs_gemm_e4m3_mx_bf16_cg1, gemm::OUT_BF16)
+GPURS_MX_KERNEL(gpurs_gemm_e4m3_mx_f32_cg1, gemm::OUT_F32)

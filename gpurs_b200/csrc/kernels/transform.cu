@@ -167,3 +167,43 @@ gpurs_quantize_e4m3_tiles(const float *source, long long pitch, uint8_t *codes, 
     GPURS_AFTER_PREVIOUS_KERNEL();
     quantize_e4m3_body<128>(source, pitch, codes, scales, rows, k);
 }
+
+
+#include "gemm_mx_tcgen05.cuh"
+
+// MX quantiser: fp32 -> E4M3 codes with one power-of-two scale (UE8M0 byte = exponent + 127) per 32 elements of a row,
+// the scale being the smallest power of two that brings the group's largest magnitude to 448 or below (1 for an all-zero
+// group); dividing by a power of two is exact, so code = E4M3(x * 2^-e), round to nearest even with saturation like the
+// reference's host conversion (crates/gpurs/src/gpu/float8.rs:20-52).  Scales are written in the tiled order of
+// gemm::mx_scale_index for the left or the right operand.  One warp per 128 elements of a row (8 lanes per group).
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_quantize_mx_e4m3(const float *__restrict__ source, long long pitch, uint8_t *__restrict__ codes, uint8_t *__restrict__ scales, int rows, int k,
+                       int right_operand) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    const int lane = threadIdx.x % 32;
+    const int k_blocks = (k + 127) / 128;
+    const long long spans = (long long)rows * k_blocks;
+    for (long long span = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32; span < spans; span += (long long)gridDim.x * (blockDim.x / 32)) {
+        const long long row = span / k_blocks;
+        const int column = int(span - row * k_blocks) * 128 + lane * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (column < k) x = *reinterpret_cast<const float4 *>(source + row * pitch + column);   // k is a multiple of 4
+        float absmax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+#pragma unroll
+        for (int offset = 4; offset > 0; offset >>= 1) absmax = fmaxf(absmax, __shfl_xor_sync(0xffffffffu, absmax, offset));
+        // absmax = f * 2^x with 1 <= f < 2; 448 = 1.75 * 2^8: e = x - 8 if f <= 1.75, else x - 7
+        int exponent = 0;
+        if (absmax > 0.0f && absmax <= 3.0e38f) {
+            int x2;
+            const float fraction = frexpf(absmax, &x2) * 2.0f;      // frexpf gives [0.5, 1)
+            exponent = (x2 - 1) - (fraction <= 1.75f ? 8 : 7);
+            exponent = max(-127, min(127, exponent));
+        }
+        if (column < k) {
+            const __nv_fp8x2_storage_t low = __nv_cvt_float2_to_fp8x2(make_float2(scalbnf(x.x, -exponent), scalbnf(x.y, -exponent)), __NV_SATFINITE, __NV_E4M3);
+            const __nv_fp8x2_storage_t high = __nv_cvt_float2_to_fp8x2(make_float2(scalbnf(x.z, -exponent), scalbnf(x.w, -exponent)), __NV_SATFINITE, __NV_E4M3);
+            *reinterpret_cast<uint32_t *>(codes + row * (long long)k + column) = uint32_t(low) | (uint32_t(high) << 16);
+            if (lane % 8 == 0) scales[gemm::mx_scale_index(right_operand != 0, row, column, k_blocks)] = uint8_t(exponent + 127);
+        }
+    }
+}

@@ -335,6 +335,7 @@ class MatmulOptions:
     stride_b: int = 0
     stride_c: int = 0
     row_absmax: DeviceBuffer | None = None     # fp32 [m], zeroed by the caller: max |C[row, :]| is folded in
+    scale_kind: int = _ffi.SCALES_FP32_BLOCKS  # SCALES_MX: scale_a / scale_b are tiled UE8M0 bytes from quantize_mx_e4m3
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
     extra: dict = field(default_factory=dict)
 
@@ -371,6 +372,7 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.batches = options.batches
     desc.stride_a, desc.stride_b, desc.stride_c = options.stride_a, options.stride_b, options.stride_c
     desc.row_absmax = options.row_absmax.pointer if options.row_absmax else 0
+    desc.scale_kind = options.scale_kind
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 
@@ -476,6 +478,17 @@ def quantize_e4m3(stream: Stream, source: DeviceBuffer, rows: int, k: int, block
     codes = gpu.allocate(E4M3, rows * k)
     scales = gpu.allocate(F32, -(-rows // block_rows) * -(-k // 128))
     _check(gpu._lib.gpurs_quantize_e4m3(stream._handle, rows, k, source.pointer, ld, block_rows, codes.pointer, scales.pointer))
+    return codes, scales
+
+
+def quantize_mx_e4m3(stream: Stream, source: DeviceBuffer, rows: int, k: int, right_operand: bool, ld: int = 0):
+    """MX quantisation of a rows x k fp32 matrix on the device: returns (codes, scales) with one power-of-two scale
+    (UE8M0 byte) per 32 elements of a row, in the tiled order the MX-scaled product reads for its left
+    (right_operand = False) or right operand.  Pass them to `matmul` with `scale_kind=SCALES_MX`."""
+    gpu = stream.gpu
+    codes = gpu.allocate(E4M3, rows * k)
+    scales = gpu.allocate(I8, gpu._lib.gpurs_mx_scale_bytes(rows, k, 1 if right_operand else 0))
+    _check(gpu._lib.gpurs_quantize_mx_e4m3(stream._handle, rows, k, source.pointer, ld, 1 if right_operand else 0, codes.pointer, scales.pointer))
     return codes, scales
 
 

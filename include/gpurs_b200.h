@@ -193,6 +193,14 @@ enum {
     GPURS_ALGO_SPLIT_LAST_ROUND = 0x200
 };
 
+/* What the scale arrays of an E4M3 product hold. */
+enum {
+    GPURS_SCALES_FP32_BLOCKS = 0,    /* fp32, one per 1 x 128 block of A and per 128 x 128 block of B (promoted every K-block in registers) */
+    GPURS_SCALES_MX = 1              /* power-of-two (UE8M0) bytes, one per 32 elements of K of every row of A and of B, in the tiled order
+                                        gpurs_quantize_mx_e4m3 writes: applied by the tensor core itself (kind::mxf8f6f4.block_scale),
+                                        k a multiple of 128, n x k right operand, one-CTA tiles */
+};
+
 /* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */
 enum {
     GPURS_PRECISION_DEFAULT = 0, /* fp32 operands: three TF32 passes over a hi/lo split, about 2^-21 relative */
@@ -244,6 +252,8 @@ typedef struct gpurs_matmul_desc {
      * before the output rounding.  The caller zeroes the array first; it may be folded into by several products.  What a
      * per-row quantiser of C needs without reading C again.  Dense tile kernels, float outputs, single products. */
     gpurs_device_ptr row_absmax;
+    int32_t scale_kind;              /* what scale_a / scale_b hold: GPURS_SCALES_* */
+    int32_t reserved;                /* 0 */
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
@@ -278,6 +288,17 @@ int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *desc, const
  * layout gpurs_matmul takes for GPURS_E4M3 with scales. */
 int gpurs_quantize_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, uint32_t block_rows,
                         gpurs_device_ptr codes, gpurs_device_ptr scales);
+
+/* MX quantiser (no counterpart in the reference): fp32 rows x k (pitch `ld`, 0 = k; k a multiple of 4) -> E4M3 codes
+ * (rows x k bytes) and one power-of-two scale per 32 elements of a row: the smallest power of two that brings the group's
+ * largest magnitude to 448 or below (1 for an all-zero group), stored as its biased exponent (UE8M0).  `scales` receives
+ * gpurs_mx_scale_bytes(rows, k, right_operand) bytes in the order the MX-scaled product reads them: 512-byte blocks of 128
+ * rows x 128 K, inside a block the scale of row r and group g at byte (r % 32) * 16 + (r / 32) * 4 + g; the left operand's
+ * blocks ordered [row / 128][k / 128], the right operand's by the product's 224-row tiles, [row / 224][k / 128][2] (rows
+ * 0..127 and 128..223 of the tile).  Entries no element maps to are set to 127 (scale 1). */
+size_t gpurs_mx_scale_bytes(uint64_t rows, uint64_t k, int right_operand);
+int gpurs_quantize_mx_e4m3(gpurs_stream *stream, uint64_t rows, uint64_t k, gpurs_device_ptr source, uint64_t ld, int right_operand,
+                           gpurs_device_ptr codes, gpurs_device_ptr scales);
 
 /* ---- 2:4 structured sparsity (no counterpart in the reference, which has no sparse path) ---------- */
 

@@ -125,6 +125,53 @@ def quantize_e4m3(source: np.ndarray, rows: int, depth: int, block_rows: int):
     return codes, scales
 
 
+MX_TILE_ROWS = 224     # rows of the right operand per tile of the MX-scaled product
+
+
+def quantize_mx_e4m3(source: np.ndarray, rows: int, depth: int):
+    """MX quantisation (numpy restatement of the definition the library's header gives; the reference has no block
+    quantiser, its E4M3 conversion is crates/gpurs/src/gpu/float8.rs:20-52): per 32 elements of a row the smallest
+    power of two 2^e with absmax / 2^e <= 448 (e = 0 for an all-zero group), codes = E4M3(x / 2^e).  Returns (codes
+    uint8 [rows * depth], exponents int [rows, depth / 32])."""
+    x = np.asarray(source, np.float32).reshape(rows, depth // 32, 32)
+    absmax = np.abs(x).max(axis=2).astype(np.float64)
+    with np.errstate(divide="ignore"):
+        exponents = np.where(absmax > 0, np.ceil(np.log2(absmax / 448.0)), 0.0).astype(np.int64)
+    # log2 in floating point can be off by one ulp at exact powers of two: settle by the definition itself
+    exponents = np.where((absmax > 0) & (absmax / np.exp2(exponents - 1.0) <= 448.0), exponents - 1, exponents)
+    exponents = np.where((absmax > 0) & (absmax / np.exp2(exponents.astype(np.float64)) > 448.0), exponents + 1, exponents)
+    exponents = np.clip(exponents, -127, 127)
+    scaled = (x.astype(np.float64) / np.exp2(exponents.astype(np.float64))[:, :, None]).astype(np.float32)   # exact: a power of two
+    return e4m3_from_f32(scaled.reshape(-1)), exponents
+
+
+def mx_scale_index(right_operand: bool, row, k, k_blocks: int):
+    """Byte index of the scale of element (row, k) in the tiled scale array of the left or right operand."""
+    row, k = np.asarray(row, np.int64), np.asarray(k, np.int64)
+    inside_block = lambda r: (r % 32) * 16 + ((r // 32) % 4) * 4 + (k // 32) % 4
+    if not right_operand:
+        return ((row // 128) * k_blocks + k // 128) * 512 + inside_block(row % 128)
+    inside = row % MX_TILE_ROWS
+    return (((row // MX_TILE_ROWS) * k_blocks + k // 128) * 2 + inside // 128) * 512 + inside_block(inside % 128)
+
+
+def mx_tile_scales(exponents: np.ndarray, right_operand: bool) -> np.ndarray:
+    """The exponents [rows, depth / 32] as the tiled array of UE8M0 bytes (unused entries 127)."""
+    rows, groups = exponents.shape
+    k_blocks = -(-groups // 4)
+    size = (-(-rows // MX_TILE_ROWS) * k_blocks * 1024) if right_operand else (-(-rows // 128) * k_blocks * 512)
+    tiled = np.full(size, 127, np.uint8)
+    r, g = np.meshgrid(np.arange(rows), np.arange(groups), indexing="ij")
+    tiled[mx_scale_index(right_operand, r, g * 32, k_blocks)] = (exponents + 127).astype(np.uint8)
+    return tiled
+
+
+def mx_dequantize(codes: np.ndarray, exponents: np.ndarray, rows: int, depth: int) -> np.ndarray:
+    """codes * 2^e as fp64 [rows, depth]."""
+    values = e4m3_to_f32(codes).astype(np.float64).reshape(rows, depth // 32, 32)
+    return (values * np.exp2(exponents.astype(np.float64))[:, :, None]).reshape(rows, depth)
+
+
 def compress_24(dense: np.ndarray, rows: int, depth: int):
     dense = np.ascontiguousarray(dense, np.uint16)
     values = np.empty(rows * depth // 2, np.uint16)
