@@ -219,20 +219,23 @@ using launcher::launch_gemm;
 // dense kernels (224-row boxes of B), plus the two tiled scale arrays as rows of 16 bytes.
 int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     gpurs_gpu *gpu = stream->gpu;
+    const int cta_group = g.cta_group;
+    const uint32_t shared_bytes = uint32_t(cta_group == 2 ? gemm::MX_SHARED_PAIR : gemm::MX_SHARED_SINGLE);
     char name[96];
-    std::snprintf(name, sizeof name, "%s_cg1", g.stem);
+    std::snprintf(name, sizeof name, "%s_cg%d", g.stem, cta_group);
     gpurs_kernel *kernel = nullptr;
-    int result = runtime::builtin_kernel(gpu, name, uint32_t(gemm::MX_SHARED_BYTES), &kernel);
+    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
-    const uint64_t k_blocks = (g.k + 127) / 128, tiles_m = (g.m + 127) / 128, tiles_n = (g.n + gemm::MX_BLOCK_N - 1) / gemm::MX_BLOCK_N;
+    const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
+    const uint64_t k_blocks = (g.k + 127) / 128, tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + gemm::MX_BLOCK_N - 1) / gemm::MX_BLOCK_N;
     alignas(64) CUtensorMap map_a, map_b, map_sa, map_sb;
     const uint64_t dims_a[2] = {g.k, g.m}, dims_b[2] = {g.k, g.n}, stride_a[1] = {g.lda}, stride_b[1] = {g.ldb};
-    const uint32_t box_a[2] = {128, uint32_t(gemm::BLOCK_M)}, box_b[2] = {128, uint32_t(gemm::MX_BLOCK_N)};
+    const uint32_t box_a[2] = {128, uint32_t(gemm::BLOCK_M)}, box_b[2] = {128, uint32_t(gemm::MX_BLOCK_N / cta_group)};
     result = gpurs_tensor_map_encode(gpu, &map_a, GPURS_E4M3, 2, g.a, dims_a, stride_a, box_a, 3, 3);
     if (result != GPURS_OK) return result;
     result = gpurs_tensor_map_encode(gpu, &map_b, GPURS_E4M3, 2, g.b, dims_b, stride_b, box_b, 3, 3);
     if (result != GPURS_OK) return result;
-    const uint64_t dims_sa[2] = {16, tiles_m * k_blocks * 32}, dims_sb[2] = {16, tiles_n * k_blocks * 64}, stride_s[1] = {16};
+    const uint64_t dims_sa[2] = {16, ((g.m + 127) / 128) * k_blocks * 32}, dims_sb[2] = {16, tiles_n * k_blocks * 64}, stride_s[1] = {16};
     const uint32_t box_sa[2] = {16, 32}, box_sb[2] = {16, 64};
     result = gpurs_tensor_map_encode(gpu, &map_sa, GPURS_I8, 2, g.scale_a, dims_sa, stride_s, box_sa, 0, 3);
     if (result != GPURS_OK) return result;
@@ -245,7 +248,7 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     params.ldc = (long long)g.ldc;
     params.m = int(g.m), params.n = int(g.n), params.k = int(g.k);
     params.tiles_m = int(tiles_m), params.tiles_n = int(tiles_n);
-    params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16;
+    params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 16 / cta_group;
     params.vector_stores = (g.c % 16 == 0 && (g.ldc * uint64_t(g.output_bytes)) % 16 == 0) ? 1 : 0;
     params.status = reinterpret_cast<unsigned int *>(gpu->status);
     params.bias = reinterpret_cast<const float *>(g.bias);
@@ -258,9 +261,12 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     const uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     gpurs_launch_config config;
     std::memset(&config, 0, sizeof config);
-    config.grid[0] = uint32_t(std::min(ctas, tiles));
+    const uint64_t clusters = std::min(std::max<uint64_t>(1, ctas / cta_group), tiles);
+    config.grid[0] = uint32_t(clusters * cta_group);
     config.block[0] = uint32_t(gemm::NUM_THREADS);
-    config.shared_bytes = uint32_t(gemm::MX_SHARED_BYTES);
+    config.shared_bytes = shared_bytes;
+    config.cluster[0] = uint32_t(cta_group);
+    config.cluster[1] = config.cluster[2] = 1;
     void *arguments[5] = {&map_a, &map_b, &map_sa, &map_sb, &params};
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
@@ -435,8 +441,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         if (!desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "both scale arrays or neither must be given");
         if (desc->c_type != GPURS_BF16 && desc->c_type != GPURS_F32)
             return fail(op, GPURS_E_INVALID_ARGUMENT, "unsupported combination of operand and output types");
-        if (sparse || b_row_major || batches > 1 || gather || desc->row_absmax || (desc->algorithm & 0xff) > GPURS_ALGO_SINGLE_CTA)
-            return fail(op, GPURS_E_INVALID_ARGUMENT, "the MX-scaled product is a single dense n x k product on one-CTA tiles");
+        if (sparse || b_row_major || batches > 1 || gather || desc->row_absmax || (desc->algorithm & 0xff) > GPURS_ALGO_CTA_PAIR)
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the MX-scaled product is a single dense n x k product on the tile kernels");
         if (k % 128) return fail(op, GPURS_E_INVALID_VIEW, "the depth of an MX-scaled product must be a multiple of 128");
         if (desc->scale_a % 16 || desc->scale_b % 16) return fail(op, GPURS_E_INVALID_VIEW, "MX scale arrays must be 16-byte aligned");
         if (desc->bias % 4 || desc->row_scale % 4 || desc->column_scale % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
@@ -447,7 +453,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         mx.a = a, mx.b = b, mx.c = c;
         mx.lda = lda, mx.ldb = ldb, mx.ldc = ldc;
         mx.m = m, mx.n = n, mx.k = k;
-        mx.cta_group = 1, mx.raster_rows = desc->raster_rows, mx.max_ctas = desc->max_ctas;
+        const int wanted = desc->algorithm & 0xff;
+        mx.cta_group = wanted == GPURS_ALGO_CTA_PAIR || (wanted == GPURS_ALGO_AUTO && m > 128) ? 2 : 1;
+        mx.raster_rows = desc->raster_rows, mx.max_ctas = desc->max_ctas;
         mx.scale_a = desc->scale_a, mx.scale_b = desc->scale_b;
         mx.bias = desc->bias, mx.row_scale = desc->row_scale, mx.column_scale = desc->column_scale, mx.alpha = desc->alpha;
         return launch_mx(stream, mx);

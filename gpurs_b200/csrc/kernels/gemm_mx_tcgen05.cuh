@@ -19,8 +19,11 @@
 // distinct power of two, the factor of every output row and K group solved for).  Instruction j of a stage (32 of its 128
 // K) selects byte j of the columns through the scale ids of its descriptor.
 //
-// Tiles are 128 x 224: two accumulators of 224 columns plus 12 scale columns per stage (4 for A's 128 rows, 8 for B's 224
-// columns in two blocks) fit the 512 columns of tensor memory for 4 stages.
+// Tiles are 224 columns wide (128 rows for one CTA, 256 for a CTA pair): two accumulators of 224 columns plus 12 scale
+// columns per stage (4 for the CTA's 128 rows of A, 8 for B's 224 columns in two blocks) fit the 512 columns of tensor
+// memory for 4 (5) stages.  In a pair each CTA loads the scale block of its own rows of A and BOTH blocks of B (its
+// tensor core multiplies its 128 rows by all 224 columns), and the leader's `tcgen05.cp.cta_group::2` copies each CTA's
+// shared-memory blocks into that CTA's own tensor memory.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -42,10 +45,11 @@ __host__ __device__ inline long long mx_scale_index(bool right_operand, long lon
     return ((tile * k_blocks + k_block) * 2 + inside / 128) * MX_SCALE_BLOCK_BYTES + mx_scale_offset(inside % 128, k);
 }
 
-template <int STAGES>
+template <int CTA_GROUP, int STAGES>
 struct MxLayout {
     static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
-    static constexpr int B_BYTES = MX_BLOCK_N * ROW_BYTES;
+    static constexpr int B_ROWS = MX_BLOCK_N / CTA_GROUP;
+    static constexpr int B_BYTES = B_ROWS * ROW_BYTES;
     static constexpr int SCALE_BYTES = 3 * MX_SCALE_BLOCK_BYTES + 512;           // A's block, B's two blocks, padding to 1024
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SCALE_BYTES;
     static constexpr int BARRIER_OFFSET = ((STAGES * STAGE_BYTES + 1023) / 1024) * 1024;
@@ -54,32 +58,41 @@ struct MxLayout {
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
     static constexpr int DYNAMIC_BYTES = ABORT_OFFSET + 4 + 1024;
 };
-static_assert(MxLayout<MX_STAGES>::DYNAMIC_BYTES == MX_SHARED_BYTES, "host and kernel disagree on shared memory");
+static_assert(MxLayout<1, MX_STAGES_SINGLE>::DYNAMIC_BYTES == MX_SHARED_SINGLE, "host and kernel disagree on shared memory");
+static_assert(MxLayout<2, MX_STAGES_PAIR>::DYNAMIC_BYTES == MX_SHARED_PAIR, "host and kernel disagree on shared memory");
 
+template <int CTA_GROUP>
 __device__ __forceinline__ void tcgen05_mma_mx(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t scale_a_tmem,
                                                uint32_t scale_b_tmem, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate) : "memory");
+    if constexpr (CTA_GROUP == 1)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+                     "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+                     ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(scale_a_tmem), "r"(scale_b_tmem), "r"(accumulate) : "memory");
 }
 
 // 32 rows of 16 bytes from shared memory to 4 columns of tensor memory, the same in all four lane quadrants.
+template <int CTA_GROUP>
 __device__ __forceinline__ void tcgen05_copy_32x128b_warpx4(uint32_t tmem_address, uint64_t smem_descriptor) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_address), "l"(smem_descriptor) : "memory");
+    if constexpr (CTA_GROUP == 1) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_address), "l"(smem_descriptor) : "memory");
+    else asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_address), "l"(smem_descriptor) : "memory");
 }
 
 // map_sa / map_sb describe the tiled scales as rows of 16 bytes: box 16 x 32 (one block of A's), 16 x 64 (B's two blocks).
-template <int OUT, int STAGES>
+template <int OUT, int CTA_GROUP, int STAGES>
 __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_sa, const CUtensorMap *map_sb,
                                              const Params &p) {
-    using L = MxLayout<STAGES>;
+    using L = MxLayout<CTA_GROUP, STAGES>;
     constexpr int BN = MX_BLOCK_N;
     constexpr uint32_t TMEM_COLUMNS = 512;
     constexpr uint32_t SCALE_COLUMN = 2 * BN;         // stage s: A's scales at 2*BN + 12*s .. +3, B's at +4 .. +11
     static_assert(2 * BN + 12 * STAGES <= 512 && BN % 32 == 0 && BN > 128 && BN <= 256, "accumulators and scales must fit tensor memory");
     // Block-scaled instruction descriptor: operand formats E4M3 (0) at bits 7 and 10, N >> 3 at bit 17, scale format UE8M0
     // at bit 23, M >> 4 at bit 24; the scale ids (which byte of the scale columns) go to bits 4..5 (B) and 29..30 (A).
-    constexpr uint32_t IDESC = (uint32_t(BN >> 3) << 17) | (1u << 23) | (uint32_t(BLOCK_M >> 4) << 24);
+    constexpr uint32_t IDESC = (uint32_t(BN >> 3) << 17) | (1u << 23) | (uint32_t((BLOCK_M * CTA_GROUP) >> 4) << 24);
     static_assert(L::STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
 
     extern __shared__ uint8_t raw_shared[];
@@ -98,6 +111,10 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
 
     const int warp = threadIdx.x / 32;
     const uint32_t lane = ptx::lane_id();
+    const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int cluster_count = gridDim.x / CTA_GROUP;
     const int tile_count = p.tiles_m * p.tiles_n;
     const int k_blocks = (p.k + ROW_BYTES - 1) / ROW_BYTES;           // 128 one-byte elements per stage
 
@@ -109,7 +126,7 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         }
         for (int a = 0; a < 2; a++) {
             ptx::mbarrier_init(acc_full_bar(a), 1);
-            ptx::mbarrier_init(acc_empty_bar(a), EPILOGUE_WARPS);
+            ptx::mbarrier_init(acc_empty_bar(a), EPILOGUE_WARPS * CTA_GROUP);
         }
         ptx::fence_mbarrier_init();
         ptx::prefetch_tensor_map(map_a);
@@ -118,11 +135,15 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         ptx::prefetch_tensor_map(map_sb);
     }
     if (warp == 1) {
-        ptx::tmem_alloc<1>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
-        ptx::tmem_relinquish<1>();
+        ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+        ptx::tmem_relinquish<CTA_GROUP>();
     }
     ptx::tcgen05_fence_before();
     __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     ptx::tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Everything above touched no global memory and may have overlapped the previous kernel of the stream.
@@ -135,21 +156,32 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tile_count && ok; tile += gridDim.x) {
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
                 int tile_m, tile_n;
                 tile_position(tile, p, tile_m, tile_n);
-                const int row_a = tile_m * BLOCK_M, row_b = tile_n * BN;
+                const int row_block = tile_m * CTA_GROUP + int(cta_rank);          // 128-row block of A this CTA owns
+                const int row_a = row_block * BLOCK_M, row_b = tile_n * BN + int(cta_rank) * L::B_ROWS;
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
                         ok = false;
                         break;
                     }
-                    ptx::mbarrier_arrive_expect_tx(full_bar(stage), L::A_BYTES + L::B_BYTES + 3 * MX_SCALE_BLOCK_BYTES);
-                    ptx::tma_load_2d(stage_a(stage), map_a, kb * ROW_BYTES, row_a, full_bar(stage));
-                    ptx::tma_load_2d(stage_b(stage), map_b, kb * ROW_BYTES, row_b, full_bar(stage));
-                    ptx::tma_load_2d(stage_scales(stage, 0), map_sa, 0, (tile_m * k_blocks + kb) * 32, full_bar(stage));
-                    ptx::tma_load_2d(stage_scales(stage, 1), map_sb, 0, (tile_n * k_blocks + kb) * 64, full_bar(stage));
+                    constexpr uint32_t BYTES = L::A_BYTES + L::B_BYTES + 3 * MX_SCALE_BLOCK_BYTES;
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::mbarrier_arrive_expect_tx(full_bar(stage), BYTES);
+                        ptx::tma_load_2d(stage_a(stage), map_a, kb * ROW_BYTES, row_a, full_bar(stage));
+                        ptx::tma_load_2d(stage_b(stage), map_b, kb * ROW_BYTES, row_b, full_bar(stage));
+                        ptx::tma_load_2d(stage_scales(stage, 0), map_sa, 0, (row_block * k_blocks + kb) * 32, full_bar(stage));
+                        ptx::tma_load_2d(stage_scales(stage, 1), map_sb, 0, (tile_n * k_blocks + kb) * 64, full_bar(stage));
+                    } else {
+                        if (leader) ptx::mbarrier_arrive_expect_tx(full_bar(stage), 2 * BYTES);
+                        const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
+                        ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * ROW_BYTES, row_a, leader_bar);
+                        ptx::tma_load_2d_pair(stage_b(stage), map_b, kb * ROW_BYTES, row_b, leader_bar);
+                        ptx::tma_load_2d_pair(stage_scales(stage, 0), map_sa, 0, (row_block * k_blocks + kb) * 32, leader_bar);
+                        ptx::tma_load_2d_pair(stage_scales(stage, 1), map_sb, 0, (tile_n * k_blocks + kb) * 64, leader_bar);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -160,12 +192,12 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tile_count && ok; tile += gridDim.x) {
-                if (!ptx::mbarrier_wait(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
+            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+                if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
                     report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
                     break;
                 }
@@ -179,20 +211,22 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
                     }
                     ptx::tcgen05_fence_after();
                     const uint32_t scale_a_tmem = tmem_base + SCALE_COLUMN + uint32_t(stage) * 12, scale_b_tmem = scale_a_tmem + 4;
-                    tcgen05_copy_32x128b_warpx4(scale_a_tmem, ptx::smem_descriptor_rows16(stage_scales(stage, 0)));
-                    tcgen05_copy_32x128b_warpx4(scale_b_tmem, ptx::smem_descriptor_rows16(stage_scales(stage, 1)));
-                    tcgen05_copy_32x128b_warpx4(scale_b_tmem + 4, ptx::smem_descriptor_rows16(stage_scales(stage, 2)));
+                    tcgen05_copy_32x128b_warpx4<CTA_GROUP>(scale_a_tmem, ptx::smem_descriptor_rows16(stage_scales(stage, 0)));
+                    tcgen05_copy_32x128b_warpx4<CTA_GROUP>(scale_b_tmem, ptx::smem_descriptor_rows16(stage_scales(stage, 1)));
+                    tcgen05_copy_32x128b_warpx4<CTA_GROUP>(scale_b_tmem + 4, ptx::smem_descriptor_rows16(stage_scales(stage, 2)));
                     const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
                     const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
 #pragma unroll
                     for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
-                        tcgen05_mma_mx(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
+                        tcgen05_mma_mx<CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
                                        IDESC | (uint32_t(j) << 29) | (uint32_t(j) << 4), scale_a_tmem, scale_b_tmem, uint32_t((kb | j) != 0));
-                    ptx::tcgen05_commit(empty_bar(stage));
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                ptx::tcgen05_commit(acc_full_bar(acc));
+                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(acc));
+                else ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -201,7 +235,7 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         const int quadrant = warp % 4;
         uint32_t acc_phase = 0;
         int acc = 0;
-        for (int tile = blockIdx.x; tile < tile_count; tile += gridDim.x) {
+        for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
             const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
@@ -210,7 +244,7 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
                 break;
             }
             ptx::tcgen05_fence_after();
-            const int row = tile_m * BLOCK_M + quadrant * 32 + int(lane);
+            const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN;
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; chunk++) {
@@ -221,7 +255,10 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
             }
             ptx::tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbarrier_arrive(acc_empty_bar(acc));
+            if (lane == 0) {
+                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+            }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
@@ -234,10 +271,16 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         const unsigned long long start = ptx::global_timer();
         while (ptx::global_timer() - start < 2000000ull) __nanosleep(1000);
     }
-    __syncthreads();
+    __syncwarp();
+    if constexpr (CTA_GROUP == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    } else {
+        __syncthreads();
+    }
     if (warp == 1) {
         ptx::tcgen05_fence_after();
-        ptx::tmem_dealloc<1>(tmem_base, TMEM_COLUMNS);
+        ptx::tmem_dealloc<CTA_GROUP>(tmem_base, TMEM_COLUMNS);
     }
 }
 

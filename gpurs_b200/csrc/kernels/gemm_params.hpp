@@ -99,11 +99,13 @@ constexpr int SPARSE_BLOCK_N = 224;
 constexpr int SPARSE_SHARED_SINGLE = 2 * (BLOCK_M * ROW_BYTES + 2 * SPARSE_BLOCK_N * ROW_BYTES + 2048) + (2 * 2 + 4) * 8 + 8 + 1024;
 constexpr int SPARSE_SHARED_PAIR = 4 * (BLOCK_M * ROW_BYTES + SPARSE_BLOCK_N * ROW_BYTES + 2048) + (2 * 4 + 4) * 8 + 8 + 1024;
 constexpr int SPARSE_METADATA_BLOCK_BYTES = 2048;
-
-// MX (hardware block-scaled FP8) kernels (gemm_mx_tcgen05.cuh): 128 x 224 tiles, 4 stages of A (16 KiB) + B (28 KiB) + 2 KiB of scales.
-constexpr int MX_BLOCK_N = 224;
-constexpr int MX_STAGES = 4;
-constexpr int MX_SHARED_BYTES = MX_STAGES * (BLOCK_M * ROW_BYTES + MX_BLOCK_N * ROW_BYTES + 2048) + (2 * MX_STAGES + 4) * 8 + 8 + 1024;
 constexpr int SPARSE_BLOCK_K = 128;
+
+// MX (hardware block-scaled FP8) kernels (gemm_mx_tcgen05.cuh): 224-column tiles; per stage A (16 KiB), B (28 KiB, or 14 KiB per
+// CTA of a pair) and 2 KiB of scales; 12 columns of tensor memory per stage hold the scales, which bounds the depth.
+constexpr int MX_BLOCK_N = 224;
+constexpr int MX_STAGES_SINGLE = 4, MX_STAGES_PAIR = 5;
+constexpr int MX_SHARED_SINGLE = MX_STAGES_SINGLE * (BLOCK_M * ROW_BYTES + MX_BLOCK_N * ROW_BYTES + 2048) + (2 * MX_STAGES_SINGLE + 4) * 8 + 8 + 1024;
+constexpr int MX_SHARED_PAIR = MX_STAGES_PAIR * (BLOCK_M * ROW_BYTES + MX_BLOCK_N / 2 * ROW_BYTES + 2048) + (2 * MX_STAGES_PAIR + 4) * 8 + 8 + 1024;
 
 }  // namespace gemm

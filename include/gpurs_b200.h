@@ -198,7 +198,7 @@ enum {
     GPURS_SCALES_FP32_BLOCKS = 0,    /* fp32, one per 1 x 128 block of A and per 128 x 128 block of B (promoted every K-block in registers) */
     GPURS_SCALES_MX = 1              /* power-of-two (UE8M0) bytes, one per 32 elements of K of every row of A and of B, in the tiled order
                                         gpurs_quantize_mx_e4m3 writes: applied by the tensor core itself (kind::mxf8f6f4.block_scale),
-                                        k a multiple of 128, n x k right operand, one-CTA tiles */
+                                        k a multiple of 128, n x k right operand */
 };
 
 /* How fp32 operands are multiplied.  The tensor cores take TF32 (10-bit mantissa) inputs. */

@@ -48,16 +48,17 @@ def test_quantiser_edge_values(gpu, stream):
     assert np.array_equal(codes.download(), expected_codes)
 
 
+@pytest.mark.parametrize("algorithm", [G.ALGO_SINGLE_CTA, G.ALGO_CTA_PAIR])
 @pytest.mark.parametrize("out,tolerance", [("f32", 1e-5), ("bf16", 1e-2)])
 @pytest.mark.parametrize("m,n,k", [(128, 224, 128), (128, 128, 256), (200, 300, 384), (384, 672, 1024), (129, 449, 2048), (1024, 1000, 512)])
-def test_product_matches_the_dequantised_fp64_product(gpu, stream, m, n, k, out, tolerance):
+def test_product_matches_the_dequantised_fp64_product(gpu, stream, m, n, k, out, tolerance, algorithm):
     """Ragged rows and columns, several tiles in both directions, tiles whose second scale block is partly or wholly
     outside the matrix."""
     a, sa, a_codes, a_exp = quantized(gpu, stream, m, k, False, seed=11)
     b, sb, b_codes, b_exp = quantized(gpu, stream, n, k, True, seed=12)
     c = gpu.allocate(G.F32 if out == "f32" else G.BF16, m * n)
     gpu._lib.gpurs_fill_u8(stream._handle, c.pointer, 0x7F, c.nbytes)
-    G.matmul(stream, a, b, c, [m, n, k], G.MatmulOptions(scale_a=sa, scale_b=sb, scale_kind=G.SCALES_MX))
+    G.matmul(stream, a, b, c, [m, n, k], G.MatmulOptions(scale_a=sa, scale_b=sb, scale_kind=G.SCALES_MX, algorithm=algorithm))
     stream.synchronize()
     got = decode_output(c.download(), out).reshape(m, n)
     expected = O.mx_dequantize(a_codes, a_exp, m, k) @ O.mx_dequantize(b_codes, b_exp, n, k).T
@@ -103,7 +104,7 @@ def test_what_the_mx_product_rejects(gpu, stream):
 
     assert code(scale_a=sa, scale_b=sb) == 0
     assert code() == _ffi.E_INVALID_ARGUMENT                                    # no scales
-    assert code(scale_a=sa, scale_b=sb, algorithm=G.ALGO_CTA_PAIR) == _ffi.E_INVALID_ARGUMENT
+    assert code(scale_a=sa, scale_b=sb, algorithm=G.ALGO_SKINNY) == _ffi.E_INVALID_ARGUMENT
     assert code(scale_a=sa, scale_b=sb, b_row_major=True) == _ffi.E_INVALID_ARGUMENT
     assert code(shape=(m, n, 96), scale_a=sa, scale_b=sb) == _ffi.E_INVALID_VIEW  # depth not a multiple of 128
     assert code(scale_a=sa, scale_b=sb, batches=2) in (_ffi.E_INVALID_ARGUMENT, _ffi.E_LENGTH_MISMATCH)
