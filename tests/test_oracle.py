@@ -177,3 +177,33 @@ def test_sparse24_generator_and_compression_round_trip():
     bad = dense.copy()
     bad[:4] = 0x3f80
     assert O.compress_24(bad, rows, depth)[2] == 1
+
+
+def test_mx_quantiser_restatement_follows_its_definition():
+    """The numpy restatement of the MX quantiser (test infrastructure for the MX-scaled product): per 32 elements the
+    smallest power of two that brings the largest magnitude to 448 or below, codes = E4M3(x / 2^e), and the tiled scale
+    layouts put every (row, group) at a distinct byte."""
+    rows, depth = 96, 256
+    rng = np.random.default_rng(5)
+    source = (rng.normal(0, 1, (rows, depth // 32, 32)) * np.exp2(rng.integers(-20, 20, (rows, depth // 32, 1)))).astype(np.float32)
+    source[0, 0] = 0.0                          # all-zero group
+    source[1, 0] = 448.0                        # exactly at the boundary: scale 1
+    source[2, 0, :] = 0.0
+    source[2, 0, 3] = 449.0                     # just above: scale 2
+    codes, exponents = O.quantize_mx_e4m3(source.reshape(-1), rows, depth)
+    assert exponents[0, 0] == 0 and exponents[1, 0] == 0 and exponents[2, 0] == 1
+    absmax = np.abs(source).max(axis=2).astype(np.float64)
+    nonzero = absmax > 0
+    assert (absmax[nonzero] / np.exp2(exponents[nonzero].astype(np.float64)) <= 448.0).all()
+    assert (absmax[nonzero] / np.exp2(exponents[nonzero] - 1.0) > 448.0).all()           # and no smaller power would do
+    back = O.mx_dequantize(codes, exponents, rows, depth).reshape(rows, depth // 32, 32)
+    # E4M3 keeps 3 mantissa bits: relative error at most 2^-4 for values in the normal range of the scaled group
+    scaled = np.abs(source.astype(np.float64)) / np.exp2(exponents.astype(np.float64))[:, :, None]
+    normal = scaled >= 2.0 ** -6
+    assert (np.abs(back - source)[normal] <= np.abs(source.astype(np.float64))[normal] * 2.0 ** -4).all()
+    for right in (False, True):
+        tiled = O.mx_tile_scales(exponents, right)
+        r, g = np.meshgrid(np.arange(rows), np.arange(depth // 32), indexing="ij")
+        index = O.mx_scale_index(right, r, g * 32, depth // 128)
+        assert len(np.unique(index)) == index.size and index.max() < tiled.size
+        assert np.array_equal(tiled[index], (exponents + 127).astype(np.uint8))
