@@ -40,6 +40,8 @@ struct PushTargets {
     alignas(64) CUtensorMap maps[gemm::MAX_PUSH_TARGETS];
     int count;
     int row_offset;
+    int first;
+    int reserved;
 };
 
 // Half-open byte ranges [begin, end) overlap?
@@ -184,6 +186,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         }
         targets.count = int(g.gather->world);
         targets.row_offset = int(g.gather->row_offset);
+        targets.first = int((g.gather->rank + 1) % g.gather->world);
         void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
         return runtime::launch(kernel, stream, &config, push_arguments, true);
     }

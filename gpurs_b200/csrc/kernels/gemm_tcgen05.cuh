@@ -37,6 +37,8 @@ struct PushTargets {
     CUtensorMap maps[MAX_PUSH_TARGETS];
     int count;
     int row_offset;
+    int first;       // the copy a box goes to first (the rank after this one): the ranks do not all start on the same GPU
+    int reserved;
 };
 
 // Instruction descriptor: accumulator format (1 = f32, 2 = s32) at bit 4, A and B element formats at
@@ -517,7 +519,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         if (lane == 0) {
                             if constexpr (PUSH) {
                                 // one staged box, one store per GPU of the box (remote ones travel over NVLink)
-                                for (int t = 0; t < targets->count; t++) ptx::tma_store_2d(&targets->maps[t], column, targets->row_offset + warp_row, buffer);
+                                for (int t = 0; t < targets->count; t++) {
+                                    const int target = targets->first + t < targets->count ? targets->first + t : targets->first + t - targets->count;
+                                    ptx::tma_store_2d(&targets->maps[target], column, targets->row_offset + warp_row, buffer);
+                                }
                             } else if constexpr (BATCHED) {
                                 ptx::tma_store_3d(map_c, column, warp_row, batch, buffer);
                             } else {
