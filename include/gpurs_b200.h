@@ -116,7 +116,7 @@ int gpurs_host_free(gpurs_gpu *gpu, void *pointer);
  * `GraphExec::launch` of the reference (crates/gpurs/src/host/graph/capture.rs:110-149,272-282; graph/exec.rs:48-72).
  * The recording keeps the addresses and shapes it was made with; the caller keeps those buffers alive and unchanged in
  * place while the graph exists.  One capture at a time per gpu handle.  Products that borrow the handle's scratch (fp32
- * operands at full precision, split-K) must have run once with the same shapes before they are captured, because the
+ * operands at full precision, split-K, a last round of tiles split along K) must have run once with the same shapes before they are captured, because the
  * scratch cannot grow inside a capture (GPURS_E_INVALID_ARGUMENT otherwise); a replay takes its turn on the scratch like
  * any other call.  Calls that wait for the device (download, status_read, stream_synchronize) are not capturable. */
 typedef struct gpurs_graph gpurs_graph;
