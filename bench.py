@@ -377,7 +377,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
         gather = {"ms_per_step": gather_ms, "value": world * flops_per_step / (gather_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                   "bytes_received_per_gpu": int((world - 1) * shard_bytes), "collective": "ncclAllGather, in place, after the GEMM on the same stream"}
         # The same result from ONE kernel per GPU: the epilogue stores every box of C into all GPUs' copies over NVLink.
-        dense_tiles = not any(word in args.workload for word in ("sparse24", "grouped", "skinny", "e4m3_scaled"))
+        dense_tiles = not any(word in args.workload for word in ("grouped", "skinny", "e4m3_scaled", "_mx_"))     # 2:4 sparse bf16 has a push kernel too
         if dense_tiles and (kind, out) in (("bf16", "bf16"), ("i8", "i32"), ("f16", "f32"), ("e4m3", "bf16")):
             def exchange(handle):
                 handles = [None] * world

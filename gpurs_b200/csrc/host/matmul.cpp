@@ -69,7 +69,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const bool stream_k = split_tiles > 0;
     std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? "%s_sk_cg%d" : "%s_cg%d", g.stem, cta_group);
     const bool sparse = g.metadata != 0;
-    const uint32_t shared_bytes = sparse ? uint32_t(cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
+    const uint32_t shared_bytes = sparse ? uint32_t(g.gather ? gemm::SPARSE_SHARED_PAIR_PUSH : cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
                                   : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
                                                    : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
     gpurs_kernel *kernel = nullptr;
@@ -188,7 +188,8 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         targets.row_offset = int(g.gather->row_offset);
         targets.first = int((g.gather->rank + 1) % g.gather->world);
         void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
-        return runtime::launch(kernel, stream, &config, push_arguments, true);
+        void *sparse_push_arguments[5] = {&map_a, &map_b, &map_e, &targets, &params};
+        return runtime::launch(kernel, stream, &config, sparse ? sparse_push_arguments : push_arguments, true);
     }
     if (stream_k) {
         // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch
@@ -493,8 +494,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         // The push epilogue exists for the CTA-pair tile kernels of these type pairs, and it stores whole boxes of 32 rows.
         const bool typed = (desc->a_type == GPURS_BF16 && desc->c_type == GPURS_BF16) || (desc->a_type == GPURS_F16 && desc->c_type == GPURS_F32) ||
                            (desc->a_type == GPURS_I8 && desc->c_type == GPURS_I32) || (desc->a_type == GPURS_E4M3 && desc->c_type == GPURS_BF16);
-        if (!typed || sparse || promoted)
-            return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product supports dense bf16->bf16, f16->f32, i8->i32 and unscaled e4m3->bf16");
+        if (!typed || promoted || (sparse && desc->a_type != GPURS_BF16))
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product supports bf16->bf16 (dense or 2:4 sparse), f16->f32, i8->i32 and unscaled e4m3->bf16");
         if (group != GPURS_ALGO_AUTO && group != GPURS_ALGO_CTA_PAIR)
             return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product runs on the CTA-pair kernels only");
         group = GPURS_ALGO_CTA_PAIR;
@@ -610,7 +611,7 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
     }
     // No copy of the result may lie over an operand (the rank's own copy is checked again with exact extents below).
     const uint64_t eb = desc->a_type == GPURS_F32 ? 4 : (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) ? 2 : 1;
-    const uint64_t a_bytes = m * (desc->lda ? desc->lda : desc->k) * eb;
+    const uint64_t a_bytes = m * (desc->lda ? desc->lda : (desc->metadata ? desc->k / 2 : desc->k)) * eb;
     const uint64_t b_bytes = (desc->b_row_major == 1 ? desc->k * (desc->ldb ? desc->ldb : n) : n * (desc->ldb ? desc->ldb : desc->k)) * eb;
     for (uint32_t t = 0; t < gather->world; t++)
         if (overlap(gather->full[t], gather->total_rows * pitch * ob, a, a_bytes) || overlap(gather->full[t], gather->total_rows * pitch * ob, b, b_bytes))

@@ -42,17 +42,27 @@ struct SparseLayout {
     static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
     static constexpr int DYNAMIC_BYTES = ABORT_OFFSET + 4 + 1024;
+    // the push entries stage their output boxes behind everything else: two 4 KiB buffers per epilogue warp
+    static constexpr int STAGING_OFFSET = ((ABORT_OFFSET + 4 + 1023) / 1024) * 1024;
+    static constexpr int PUSH_DYNAMIC_BYTES = STAGING_OFFSET + EPILOGUE_WARPS * 2 * 32 * ROW_BYTES + 1024;
 };
 
 constexpr int SPARSE_STAGES_SINGLE = 2;   // 74 KiB per stage
 constexpr int SPARSE_STAGES_PAIR = 4;     // 46 KiB per stage and CTA
 static_assert(SparseLayout<1, SPARSE_STAGES_SINGLE>::DYNAMIC_BYTES == SPARSE_SHARED_SINGLE, "host and kernel disagree on shared memory");
 static_assert(SparseLayout<2, SPARSE_STAGES_PAIR>::DYNAMIC_BYTES == SPARSE_SHARED_PAIR, "host and kernel disagree on shared memory");
+static_assert(SparseLayout<2, SPARSE_STAGES_PAIR>::PUSH_DYNAMIC_BYTES == SPARSE_SHARED_PAIR_PUSH, "host and kernel disagree on shared memory");
 static_assert(METADATA_BLOCK_BYTES == SPARSE_METADATA_BLOCK_BYTES && SPARSE_STAGE_K == SPARSE_BLOCK_K, "host and kernel disagree on the metadata block");
 
 // ELEMENT_FORMAT: 0 = f16, 1 = bf16.  map_e describes the metadata as rows of 16 bytes (box 16 x 128).
-template <int ELEMENT_FORMAT, int OUT, int CTA_GROUP, int STAGES>
-__device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_e, const Params &p) {
+// PUSH (bf16 output): every finished box of C is stored to all GPUs' copies of the gathered matrix (PushTargets) by TMA
+// stores from swizzled shared staging, as the dense push kernels do.  A 224-column tile is three boxes of 64 columns and a
+// fourth that starts at column 160: it writes columns 160..191 a second time, with the same values, rather than needing
+// a narrower kind of box for the last 32 columns.
+template <int ELEMENT_FORMAT, int OUT, int CTA_GROUP, int STAGES, bool PUSH = false>
+__device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_e, const Params &p,
+                                                 const PushTargets *targets = nullptr) {
+    static_assert(!PUSH || OUT == OUT_BF16, "the push epilogue of the sparse kernels writes bf16");
     using L = SparseLayout<CTA_GROUP, STAGES>;
     constexpr int BN = SPARSE_BLOCK_N;
     constexpr uint32_t TMEM_COLUMNS = 512;
@@ -207,6 +217,7 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
         const int quadrant = warp % 4;
         uint32_t acc_phase = 0;
         int acc = 0;
+        [[maybe_unused]] int stores = 0;     // push epilogue: TMA stores issued by this warp, picks the staging buffer
         for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
@@ -218,12 +229,52 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN;
+            if constexpr (PUSH) {
+                const int warp_row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32;
+                const uint32_t staging = base + L::STAGING_OFFSET;
 #pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; chunk++) {
-                uint32_t values[32];
-                ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
-                ptx::tmem_load_wait();
-                store_chunk<OUT>(p, values, row, tile_n * BN + chunk * 32);
+                for (int box = 0; box < (BN + 63) / 64; box++) {
+                    const int first = min(box * 64, BN - 64);            // 0, 64, 128, 160
+                    const int column = tile_n * BN + first;
+                    uint32_t low[32], high[32], packed[32];
+                    ptx::tmem_load_32x32(lane_base + uint32_t(first), low);
+                    ptx::tmem_load_32x32(lane_base + uint32_t(first + 32), high);
+                    ptx::tmem_load_wait();
+                    apply_epilogue<OUT>(p, low, row, column);
+                    apply_epilogue<OUT>(p, high, row, column + 32);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
+                        packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
+                    }
+                    if (warp_row < p.m && column < p.n) {
+                        const uint32_t buffer = staging + uint32_t(((warp - 2) * 2 + (stores & 1)) * 32 * ROW_BYTES);
+                        stores++;
+                        if (lane == 0) ptx::tma_store_wait_read<1>();
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
+                            ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), packed[4 * j], packed[4 * j + 1],
+                                                 packed[4 * j + 2], packed[4 * j + 3]);
+                        ptx::fence_async_shared();
+                        __syncwarp();
+                        if (lane == 0) {
+                            for (int t = 0; t < targets->count; t++) {
+                                const int target = targets->first + t < targets->count ? targets->first + t : targets->first + t - targets->count;
+                                ptx::tma_store_2d(&targets->maps[target], column, targets->row_offset + warp_row, buffer);
+                            }
+                            ptx::tma_store_commit();
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN / 32; chunk++) {
+                    uint32_t values[32];
+                    ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
+                    ptx::tmem_load_wait();
+                    store_chunk<OUT>(p, values, row, tile_n * BN + chunk * 32);
+                }
             }
             ptx::tcgen05_fence_before();
             __syncwarp();
@@ -232,6 +283,9 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
                 else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+        if constexpr (PUSH) {
+            if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
         }
     }
 

@@ -454,6 +454,7 @@ def matmul_allgather(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, gathered:
     desc.row_scale = options.row_scale.pointer if options.row_scale else 0
     desc.column_scale = options.column_scale.pointer if options.column_scale else 0
     desc.alpha = options.alpha
+    desc.metadata = options.metadata.pointer if options.metadata else 0     # 2:4-sparse A (bf16 -> bf16)
     gather = _ffi.GatherDesc()
     gather.world, gather.rank, gather.row_offset, gather.total_rows, gather.ld_full = gathered.world, gathered.rank, row_offset, gathered.total_rows, 0
     for peer, pointer in enumerate(gathered.pointers):

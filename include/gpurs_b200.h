@@ -355,7 +355,7 @@ int gpurs_matmul_grouped(gpurs_stream *stream, const gpurs_grouped_desc *desc, g
  *   full[t]  the gathered matrix (total_rows x n, pitch ld_full) on GPU t as an address valid in THIS process: the
  *            rank's own allocation for t == rank, gpurs_ipc_open of the owner's handle otherwise (peers of one box).
  * `desc` describes the local product as for gpurs_matmul (m = rows of this block; ldc 0 or ld_full; c_len ignored).
- * Supported: dense bf16->bf16, f16->f32, i8->i32, unscaled e4m3->bf16; bases and pitches of the gathered matrices
+ * Supported: dense bf16->bf16, f16->f32, i8->i32, unscaled e4m3->bf16, and 2:4-sparse bf16->bf16 (desc.metadata set); bases and pitches of the gathered matrices
  * multiples of 16 bytes; every block but the last a multiple of 32 rows. */
 typedef struct gpurs_gather_desc {
     uint32_t world;              /* GPUs that receive the result, 1..8 */

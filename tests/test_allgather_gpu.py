@@ -153,3 +153,35 @@ def test_two_processes_exchange_blocks_through_ipc(gpu, stream):
     for rank, payload, status in outcomes:
         assert status == 0, payload
         assert np.array_equal(np.frombuffer(payload, np.uint16), whole), f"rank {rank}"
+
+
+@pytest.mark.parametrize("m,n,k,world", [(512, 448, 256, 2), (1024, 1000, 512, 4), (768, 224, 128, 3)])
+def test_sparse_product_pushes_its_blocks_too(gpu, stream, m, n, k, world):
+    """The 2:4-sparse bf16 kernel has the same push epilogue (its 224-column tiles end in a half box): every copy equals the
+    single-GPU sparse product bit for bit."""
+    dense = O.fill_sparse24_bf16(m, k, 7)
+    b_bits = O.fill_normal_16(O.FMT_BF16, n * k, 8)
+    b = gpu.upload(b_bits, G.BF16)
+    values, metadata, _ = G.compress_24(stream, gpu.upload(dense, G.BF16), m, k)
+    whole = gpu.zeros(G.BF16, m * n)
+    G.matmul(stream, values, b, whole, [m, n, k], G.MatmulOptions(metadata=metadata, algorithm=G.ALGO_CTA_PAIR))
+    stream.synchronize()
+    expected = whole.download()
+    copies = [gpu.allocate(G.BF16, m * n) for _ in range(world)]
+    for copy in copies:
+        gpu._lib.gpurs_fill_u8(stream._handle, copy.pointer, 0x7F, copy.nbytes)
+    for rank, (first, rows) in enumerate(shard_table(m, world)):
+        if rows == 0:
+            continue
+        shard_values, shard_metadata, _ = G.compress_24(stream, gpu.upload(dense[first * k:(first + rows) * k], G.BF16), rows, k)
+        desc = _ffi.MatmulDesc()
+        desc.a_type, desc.c_type, desc.m, desc.n, desc.k, desc.metadata = G.BF16, G.BF16, rows, n, k, shard_metadata.pointer
+        gather = _ffi.GatherDesc()
+        gather.world, gather.rank, gather.row_offset, gather.total_rows = world, rank, first, m
+        for peer, copy in enumerate(copies):
+            gather.full[peer] = copy.pointer
+        code = gpu._lib.gpurs_matmul_allgather(stream._handle, C.byref(desc), C.byref(gather), shard_values.pointer, b.pointer)
+        assert code == 0
+        stream.synchronize()
+    for copy in copies:
+        assert np.array_equal(copy.download(), expected)
