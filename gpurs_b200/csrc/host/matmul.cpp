@@ -44,6 +44,16 @@ struct PushTargets {
     int reserved;
 };
 
+// Host mirror of gemm::SparsePushTargets (kernels/gemm_sparse_tcgen05.cuh).
+struct SparsePushTargets {
+    alignas(64) CUtensorMap maps[gemm::MAX_PUSH_TARGETS];
+    alignas(64) CUtensorMap half_maps[gemm::MAX_PUSH_TARGETS];
+    int count;
+    int row_offset;
+    int first;
+    int reserved;
+};
+
 // Half-open byte ranges [begin, end) overlap?
 bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { return a < b + b_bytes && b < a + a_bytes; }
 
@@ -173,6 +183,25 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, batched ? 3 : 2, g.c, dims_c, stride_c, box_c, 3, 3);
         if (result != GPURS_OK) return result;
     }
+    if (g.gather && sparse) {
+        // as below, with a second, unswizzled descriptor per GPU for the 32-column box that ends a 224-column tile
+        SparsePushTargets targets;
+        std::memset(&targets, 0, sizeof targets);
+        const uint64_t pitch = g.gather->ld_full ? g.gather->ld_full : g.n;
+        const uint64_t dims_c[2] = {g.n, g.gather->total_rows}, stride_c[1] = {pitch * ob};
+        const uint32_t box_c[2] = {64, 32}, half_box_c[2] = {32, 32};
+        for (uint32_t t = 0; t < g.gather->world; t++) {
+            result = gpurs_tensor_map_encode(gpu, &targets.maps[t], g.output_type, 2, g.gather->full[t], dims_c, stride_c, box_c, 3, 3);
+            if (result != GPURS_OK) return result;
+            result = gpurs_tensor_map_encode(gpu, &targets.half_maps[t], g.output_type, 2, g.gather->full[t], dims_c, stride_c, half_box_c, 0, 3);
+            if (result != GPURS_OK) return result;
+        }
+        targets.count = int(g.gather->world);
+        targets.row_offset = int(g.gather->row_offset);
+        targets.first = int((g.gather->rank + 1) % g.gather->world);
+        void *push_arguments[5] = {&map_a, &map_b, &map_e, &targets, &params};
+        return runtime::launch(kernel, stream, &config, push_arguments, true);
+    }
     if (g.gather) {
         // One descriptor of the whole gathered matrix per GPU; the kernel stores each box of its block to all of them.
         PushTargets targets;
@@ -188,8 +217,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         targets.row_offset = int(g.gather->row_offset);
         targets.first = int((g.gather->rank + 1) % g.gather->world);
         void *push_arguments[4] = {&map_a, &map_b, &targets, &params};
-        void *sparse_push_arguments[5] = {&map_a, &map_b, &map_e, &targets, &params};
-        return runtime::launch(kernel, stream, &config, sparse ? sparse_push_arguments : push_arguments, true);
+        return runtime::launch(kernel, stream, &config, push_arguments, true);
     }
     if (stream_k) {
         // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch

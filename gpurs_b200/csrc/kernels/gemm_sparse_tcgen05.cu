@@ -15,11 +15,11 @@ GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_bf16_f32_cg2, 1, gemm::OUT_F32, 2, gemm::S
 GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_f16_f32_cg1, 0, gemm::OUT_F32, 1, gemm::SPARSE_STAGES_SINGLE)
 GPURS_SPARSE_KERNEL(gpurs_gemm_sparse_f16_f32_cg2, 0, gemm::OUT_F32, 2, gemm::SPARSE_STAGES_PAIR)
 
-// Push entry (see gemm::PushTargets): the M-sharded sparse product whose epilogue stores every box of C into all
+// Push entry (see gemm::SparsePushTargets): the M-sharded sparse product whose epilogue stores every box of C into all
 // GPUs' copies of the gathered matrix.
 extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 gpurs_gemm_sparse_bf16_bf16_push_cg2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                     const __grid_constant__ CUtensorMap map_e, const __grid_constant__ gemm::PushTargets targets,
+                                     const __grid_constant__ CUtensorMap map_e, const __grid_constant__ gemm::SparsePushTargets targets,
                                      const __grid_constant__ gemm::Params params) {
     gemm::gemm_sparse_body<1, gemm::OUT_BF16, 2, gemm::SPARSE_STAGES_PAIR, true>(&map_a, &map_b, &map_e, params, &targets);
 }

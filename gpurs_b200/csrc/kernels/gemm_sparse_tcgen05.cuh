@@ -47,6 +47,17 @@ struct SparseLayout {
     static constexpr int PUSH_DYNAMIC_BYTES = STAGING_OFFSET + EPILOGUE_WARPS * 2 * 32 * ROW_BYTES + 1024;
 };
 
+// Destinations of the push epilogue of the sparse kernels (bf16 output): as gemm::PushTargets, with a second descriptor per
+// GPU whose boxes are 32 columns wide and unswizzled, for the last 32 of a tile's 224 columns.
+struct SparsePushTargets {
+    CUtensorMap maps[MAX_PUSH_TARGETS];        // boxes of 32 rows x 64 columns, 128-byte swizzle
+    CUtensorMap half_maps[MAX_PUSH_TARGETS];   // boxes of 32 rows x 32 columns, rows of 64 bytes back to back
+    int count;
+    int row_offset;
+    int first;
+    int reserved;
+};
+
 constexpr int SPARSE_STAGES_SINGLE = 2;   // 74 KiB per stage
 constexpr int SPARSE_STAGES_PAIR = 4;     // 46 KiB per stage and CTA
 static_assert(SparseLayout<1, SPARSE_STAGES_SINGLE>::DYNAMIC_BYTES == SPARSE_SHARED_SINGLE, "host and kernel disagree on shared memory");
@@ -56,12 +67,12 @@ static_assert(METADATA_BLOCK_BYTES == SPARSE_METADATA_BLOCK_BYTES && SPARSE_STAG
 
 // ELEMENT_FORMAT: 0 = f16, 1 = bf16.  map_e describes the metadata as rows of 16 bytes (box 16 x 128).
 // PUSH (bf16 output): every finished box of C is stored to all GPUs' copies of the gathered matrix (PushTargets) by TMA
-// stores from swizzled shared staging, as the dense push kernels do.  A 224-column tile is three boxes of 64 columns and a
-// fourth that starts at column 160: it writes columns 160..191 a second time, with the same values, rather than needing
-// a narrower kind of box for the last 32 columns.
+// stores from shared staging, as the dense push kernels do.  A 224-column tile is three boxes of 64 columns (128-byte
+// swizzled staging) and one of 32 (staged as plain 64-byte rows, its own descriptors): writing columns 160..191 twice with a
+// fourth full box instead was measured at 8 GPUs and cost the 14 % more bytes it sends.
 template <int ELEMENT_FORMAT, int OUT, int CTA_GROUP, int STAGES, bool PUSH = false>
 __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_e, const Params &p,
-                                                 const PushTargets *targets = nullptr) {
+                                                 const SparsePushTargets *targets = nullptr) {
     static_assert(!PUSH || OUT == OUT_BF16, "the push epilogue of the sparse kernels writes bf16");
     using L = SparseLayout<CTA_GROUP, STAGES>;
     constexpr int BN = SPARSE_BLOCK_N;
@@ -234,34 +245,40 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
                 const uint32_t staging = base + L::STAGING_OFFSET;
 #pragma unroll 1
                 for (int box = 0; box < (BN + 63) / 64; box++) {
-                    const int first = min(box * 64, BN - 64);            // 0, 64, 128, 160
-                    const int column = tile_n * BN + first;
+                    const int column = tile_n * BN + box * 64;
+                    const bool half = box * 64 + 64 > BN;            // the tile's last 32 columns
                     uint32_t low[32], high[32], packed[32];
-                    ptx::tmem_load_32x32(lane_base + uint32_t(first), low);
-                    ptx::tmem_load_32x32(lane_base + uint32_t(first + 32), high);
+                    ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
+                    if (!half) ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
                     ptx::tmem_load_wait();
                     apply_epilogue<OUT>(p, low, row, column);
-                    apply_epilogue<OUT>(p, high, row, column + 32);
+                    if (!half) apply_epilogue<OUT>(p, high, row, column + 32);
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
-                        packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
+                        packed[16 + i] = half ? 0u : pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
                     }
                     if (warp_row < p.m && column < p.n) {
                         const uint32_t buffer = staging + uint32_t(((warp - 2) * 2 + (stores & 1)) * 32 * ROW_BYTES);
                         stores++;
                         if (lane == 0) ptx::tma_store_wait_read<1>();
                         __syncwarp();
+                        if (half) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
-                            ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), packed[4 * j], packed[4 * j + 1],
-                                                 packed[4 * j + 2], packed[4 * j + 3]);
+                            for (int j = 0; j < 4; j++)                      // rows of 64 bytes back to back, no swizzle
+                                ptx::store_shared_v4(buffer + lane * 64u + uint32_t(j * 16), packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j++)                      // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
+                                ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), packed[4 * j], packed[4 * j + 1],
+                                                     packed[4 * j + 2], packed[4 * j + 3]);
+                        }
                         ptx::fence_async_shared();
                         __syncwarp();
                         if (lane == 0) {
                             for (int t = 0; t < targets->count; t++) {
                                 const int target = targets->first + t < targets->count ? targets->first + t : targets->first + t - targets->count;
-                                ptx::tma_store_2d(&targets->maps[target], column, targets->row_offset + warp_row, buffer);
+                                ptx::tma_store_2d(half ? &targets->half_maps[target] : &targets->maps[target], column, targets->row_offset + warp_row, buffer);
                             }
                             ptx::tma_store_commit();
                         }
