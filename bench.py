@@ -299,6 +299,15 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
     ms_per_step = milliseconds / args.steps
     per_gpu_tflops = flops_per_step / (ms_per_step * 1e-3) / 1e12
     value = per_gpu_tflops * world
+    # Four more repetitions of the same K steps (this rank's own times), reported beside `value`, which stays the first.
+    repetitions = [ms_per_step]
+    for _ in range(4):
+        first = stream.record_timed()
+        for _ in range(args.steps):
+            launch()
+        last = stream.record_timed()
+        stream.synchronize()
+        repetitions.append(first.elapsed_ms(last) / args.steps)
 
     # ---- end to end through the public API with host buffers ------------------------------------
     e2e_steps = max(1, min(args.steps, 8))
@@ -439,6 +448,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
                     "call": "gpurs_matmul_host: pinned host buffers, copies and product overlapped by blocks of rows" if host_call
                             else "copy_to_device x2, product, copy_to_host on one stream"},
             "gpu_launches": int(launches),
+            "repetitions": {"ms_per_step": [round(x, 6) for x in repetitions], "best": min(repetitions), "median": sorted(repetitions)[len(repetitions) // 2],
+                            "note": "five times K back-to-back steps on rank 0; `value` and `ms_per_step` are the first (max over ranks)"},
             "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu_tflops / peak,
                          "traffic": MEASURED_TRAFFIC.get(args.workload), "peak_source": peak_source,
                          "frac_of_nominal": per_gpu_tflops / NOMINAL_PEAK[kind], "nominal_peak": NOMINAL_PEAK[kind],
