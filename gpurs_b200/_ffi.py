@@ -23,6 +23,8 @@ E_INCOMPATIBLE_DEVICE = 100008
 E_INVALID_ARGUMENT = 100009
 E_DEVICE_TIMEOUT = 100010
 E_DRIVER_UNAVAILABLE = 100011
+E_COLLECTIVE = 100012
+COMM_ID_BYTES = 128
 
 F16, F32, BF16, I8, I32, E4M3 = 6, 7, 9, 100, 101, 102
 ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
@@ -48,7 +50,9 @@ class MatmulDesc(C.Structure):
         ("l2_policy", C.c_int32), ("b_row_major", C.c_int32), ("bias", C.c_uint64),
         ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("batches", C.c_int32),
         ("stride_a", C.c_uint64), ("stride_b", C.c_uint64), ("stride_c", C.c_uint64), ("row_absmax", C.c_uint64),
-        ("scale_kind", C.c_int32), ("reserved", C.c_int32),
+        ("scale_kind", C.c_int32), ("accumulate", C.c_int32),
+        ("row_bias", C.c_uint64), ("residual", C.c_uint64), ("ldr", C.c_uint64), ("beta", C.c_float), ("reserved", C.c_int32),
+        ("row_sum", C.c_uint64), ("launch", C.POINTER(LaunchConfigStruct)),
     ]
 
 
@@ -88,6 +92,7 @@ SIGNATURES = {
     "gpurs_copy_to_device": (C.c_int, [_P, C.c_uint64, _P, C.c_size_t]),
     "gpurs_copy_to_host": (C.c_int, [_P, _P, C.c_uint64, C.c_size_t]),
     "gpurs_fill_u8": (C.c_int, [_P, C.c_uint64, C.c_uint8, C.c_size_t]),
+    "gpurs_memory_info": (C.c_int, [_P, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "gpurs_host_alloc": (C.c_int, [_P, C.c_size_t, _PP]),
     "gpurs_host_free": (C.c_int, [_P, _P]),
     "gpurs_stream_capture_begin": (C.c_int, [_P]),
@@ -115,6 +120,10 @@ SIGNATURES = {
     "gpurs_matmul_grouped": (C.c_int, [_P, C.POINTER(GroupedDesc), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_host": (C.c_int, [_P, C.POINTER(MatmulDesc), _P, _P, _P, C.c_uint64, C.c_uint64, C.c_uint64]),
     "gpurs_matmul_allgather": (C.c_int, [_P, C.POINTER(MatmulDesc), C.POINTER(GatherDesc), C.c_uint64, C.c_uint64]),
+    "gpurs_comm_unique_id": (C.c_int, [C.POINTER(C.c_uint8)]),
+    "gpurs_comm_init": (C.c_int, [_P, C.POINTER(C.c_uint8), C.c_uint32, C.c_uint32, _PP]),
+    "gpurs_comm_allgather": (C.c_int, [_P, _P, C.c_uint64, C.c_uint64]),
+    "gpurs_comm_free": (None, [_P]),
     "gpurs_self_test_timeout": (C.c_int, [_P]),
     "gpurs_status_read": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "gpurs_launch_count": (C.c_uint64, [_P]),

@@ -37,6 +37,7 @@ namespace driver {
     X(cuEventDestroy)             \
     X(cuMemAlloc)                 \
     X(cuMemFree)                  \
+    X(cuMemGetInfo)               \
     X(cuMemcpyHtoDAsync)          \
     X(cuMemcpyDtoHAsync)          \
     X(cuMemsetD8Async)            \

@@ -19,6 +19,13 @@ struct Gemm {
     gpurs_device_ptr row_scale = 0, column_scale = 0;   // optional fp32 [m] and [n]
     float alpha = 0.0f;                          // 0 = none
     gpurs_device_ptr row_absmax = 0;             // optional fp32 [m], atomic max of |C[row, :]|
+    gpurs_device_ptr row_bias = 0;               // optional fp32 [m]
+    gpurs_device_ptr residual = 0;               // optional m x n matrix of C's type, pitch ldr, added as beta * residual
+    uint64_t ldr = 0;
+    float beta = 1.0f;
+    gpurs_device_ptr row_sum = 0;                // optional fp32 [m], atomic add of the row's sum
+    bool accumulate = false;                     // fp32 output: atomic adds into C instead of stores
+    const gpurs_launch_config *launch = nullptr; // the caller's explicit geometry, already checked for plausibility
     uint64_t batches = 1, stride_a = 0, stride_b = 0, stride_c = 0;   // batched entries: matrices and the elements between them
     bool whole_tiles = false;                    // never split the last round's tiles along K
     bool force_split = false;                    // split it whenever it is not full, whether or not that pays

@@ -54,6 +54,32 @@ struct SparsePushTargets {
     int reserved;
 };
 
+// The caller's explicit geometry against the kernel that was chosen: block and shared memory must fit it, the grid is a
+// whole number of clusters.  Returns the number of CTAs to launch at most (0 = the caller has no say).
+int explicit_ctas(const char *op, const gpurs_launch_config *launch, int cta_group, uint32_t threads, uint32_t shared_bytes, uint64_t &ctas) {
+    ctas = 0;
+    if (!launch) return GPURS_OK;
+    const uint64_t grid = uint64_t(launch->grid[0] ? launch->grid[0] : 1) * (launch->grid[1] ? launch->grid[1] : 1) * (launch->grid[2] ? launch->grid[2] : 1);
+    if (launch->grid[0] == 0) return fail(op, GPURS_E_INVALID_VIEW, "empty launch geometry");
+    if (grid % uint64_t(cta_group) || grid > 0x7fffffffull) return fail(op, GPURS_E_INVALID_VIEW, "the grid must be a whole number of clusters");
+    if (launch->block[0] != 0 && (launch->block[0] != threads || launch->block[1] > 1 || launch->block[2] > 1))
+        return fail(op, GPURS_E_INVALID_VIEW, "the block size differs from the kernel's thread count");
+    if (launch->shared_bytes != 0 && launch->shared_bytes < shared_bytes)
+        return fail(op, GPURS_E_INVALID_VIEW, "less shared memory than the kernel needs");
+    if (launch->shared_bytes > 232448) return fail(op, GPURS_E_INVALID_VIEW, "more shared memory than a CTA may have");
+    if (launch->cluster[0] > 1 && int(launch->cluster[0]) != cta_group) return fail(op, GPURS_E_INVALID_VIEW, "the cluster size differs from the tile algorithm's");
+    if (launch->cluster[1] > 1 || launch->cluster[2] > 1) return fail(op, GPURS_E_INVALID_VIEW, "clusters are one-dimensional");
+    ctas = grid;
+    return GPURS_OK;
+}
+
+// Dynamic shared memory of the tile kernel a Gemm selects.
+uint32_t shared_for(const launcher::Gemm &g) {
+    if (g.metadata != 0) return uint32_t(g.gather ? gemm::SPARSE_SHARED_PAIR_PUSH : g.cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE);
+    return g.cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
+                            : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
+}
+
 // Half-open byte ranges [begin, end) overlap?
 bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { return a < b + b_bytes && b < a + a_bytes; }
 
@@ -70,18 +96,27 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     // Stream-K: decided here from the tile count and the grid, by the same arithmetic the kernel uses to find its work.
     const uint64_t tile_rows_ = uint64_t(gemm::BLOCK_M) * cta_group;
     const uint64_t all_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
-    const uint64_t wanted_ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    uint64_t explicit_grid = 0;
+    {
+        const int checked = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(g.threads), shared_for(g), explicit_grid);
+        if (checked != GPURS_OK) return checked;
+    }
+    const uint64_t wanted_ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     const uint64_t grid_clusters = std::min(std::max<uint64_t>(1, wanted_ctas / cta_group), std::max<uint64_t>(all_tiles, 1));
     const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
     const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull;
     const int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
     gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
     const bool stream_k = split_tiles > 0;
-    std::snprintf(name, sizeof name, g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? "%s_sk_cg%d" : "%s_cg%d", g.stem, cta_group);
+    // The dense tile kernels come without and with the output algebra compiled in ("_ep"): a plain product runs the lean entry.
+    const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
+                         g.row_sum || g.accumulate;
+    const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+                       : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
+    std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
-    const uint32_t shared_bytes = sparse ? uint32_t(g.gather ? gemm::SPARSE_SHARED_PAIR_PUSH : cta_group == 2 ? gemm::SPARSE_SHARED_PAIR : gemm::SPARSE_SHARED_SINGLE)
-                                  : cta_group == 2 ? gemm::SharedLayout<gemm::BLOCK_N, 2, gemm::STAGES_PAIR>::DYNAMIC_BYTES
-                                                   : gemm::SharedLayout<gemm::BLOCK_N, 1, gemm::STAGES_SINGLE>::DYNAMIC_BYTES;
+    const uint32_t shared_bytes = std::max(shared_for(g), g.launch ? g.launch->shared_bytes : 0u);
     gpurs_kernel *kernel = nullptr;
     int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
@@ -157,10 +192,16 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.alpha = g.alpha;
     params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
     params.row_absmax = reinterpret_cast<float *>(g.row_absmax);
+    params.row_bias = reinterpret_cast<const float *>(g.row_bias);
+    params.residual = reinterpret_cast<const void *>(g.residual);
+    params.ldr = (long long)g.ldr;
+    params.beta = g.beta;
+    params.row_sum = reinterpret_cast<float *>(g.row_sum);
+    params.accumulate = g.accumulate ? 1 : 0;
 
     const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n) * g.batches;
     if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
-    uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    uint64_t ctas = wanted_ctas;
     uint64_t clusters = std::max<uint64_t>(1, ctas / cta_group);
     clusters = std::min(clusters, tiles);
     gpurs_launch_config config;
@@ -227,7 +268,10 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         result = runtime::workspace_acquire(stream, partial_bytes, &partials);
         if (result != GPURS_OK) return result;
         result = runtime::turns_acquire(stream, std::max<size_t>(size_t(schedule.split_tiles) * 4 * cta_group * sizeof(uint32_t), 4096), &counters);
-        if (result != GPURS_OK) return result;
+        if (result != GPURS_OK) {
+            runtime::workspace_release(stream);     // nothing was enqueued: the next borrower need not wait for this one
+            return result;
+        }
         params.partials = reinterpret_cast<void *>(partials);
         params.split_counters = reinterpret_cast<unsigned int *>(counters);
         params.max_contributors = most;
@@ -288,9 +332,17 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     params.column_scale = reinterpret_cast<const float *>(g.column_scale);
     params.alpha = g.alpha;
     params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
+    params.row_bias = reinterpret_cast<const float *>(g.row_bias);
+    params.residual = reinterpret_cast<const void *>(g.residual);
+    params.ldr = (long long)g.ldr;
+    params.beta = g.beta;
+    params.accumulate = g.accumulate ? 1 : 0;
     const uint64_t tiles = tiles_m * tiles_n;
     if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
-    const uint64_t ctas = g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    uint64_t explicit_grid = 0;
+    result = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(gemm::NUM_THREADS), shared_bytes, explicit_grid);
+    if (result != GPURS_OK) return result;
+    const uint64_t ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     gpurs_launch_config config;
     std::memset(&config, 0, sizeof config);
     const uint64_t clusters = std::min(std::max<uint64_t>(1, ctas / cta_group), tiles);
@@ -353,7 +405,10 @@ int launch_skinny(gpurs_stream *stream, const launcher::Gemm &g) {
         result = runtime::turns_acquire(stream, size_t(gemm::SKINNY_MAX_TILES) * 4 * sizeof(unsigned int), &turns);
         if (result != GPURS_OK) return result;
         result = runtime::workspace_acquire(stream, size_t(params.tiles) * splits * tokens * gemm::BLOCK_M * sizeof(float), &partials);
-        if (result != GPURS_OK) return result;
+        if (result != GPURS_OK) {
+            runtime::turns_release(stream);
+            return result;
+        }
     }
     params.turns = reinterpret_cast<unsigned int *>(turns);
     params.partials = reinterpret_cast<float *>(partials);
@@ -389,6 +444,25 @@ int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gp
     long long source_pitch = (long long)pitch;
     int row_count = int(rows), depth = int(k);
     void *arguments[6] = {&source_pointer, &source_pitch, &destination_pointer, &row_count, &depth, &order};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
+// The same split for a right operand stored k x n: written transposed, as the n x 3k array the product reads K-major.
+int split_tf32_transposed(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t n, uint64_t k) {
+    gpurs_gpu *gpu = stream->gpu;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_split_tf32_transposed", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t tiles = ((n + 31) / 32) * ((k + 31) / 32);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(tiles, uint64_t(gpu->multiprocessors) * 8)));
+    config.block[0] = 256;
+    const void *source_pointer = reinterpret_cast<const void *>(source);
+    void *destination_pointer = reinterpret_cast<void *>(destination);
+    long long source_pitch = (long long)pitch;
+    int columns = int(n), depth = int(k);
+    void *arguments[5] = {&source_pointer, &source_pitch, &destination_pointer, &columns, &depth};
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
@@ -490,6 +564,18 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         mx.raster_rows = desc->raster_rows, mx.max_ctas = desc->max_ctas;
         mx.scale_a = desc->scale_a, mx.scale_b = desc->scale_b;
         mx.bias = desc->bias, mx.row_scale = desc->row_scale, mx.column_scale = desc->column_scale, mx.alpha = desc->alpha;
+        if (desc->row_sum) return fail(op, GPURS_E_INVALID_ARGUMENT, "the row reduction is for single dense products with float outputs on the tile kernels");
+        if (desc->accumulate != 0 && (desc->accumulate != 1 || desc->c_type != GPURS_F32)) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulating into the output needs an fp32 output");
+        if (desc->row_bias % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
+        const uint64_t mx_ldr = desc->ldr ? desc->ldr : n;
+        if (desc->residual) {
+            if (mx_ldr < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+            if (desc->residual % ob) return fail(op, GPURS_E_INVALID_VIEW, "the residual is not aligned to its element size");
+            if (!(desc->residual == c && mx_ldr == ldc) && overlap(desc->residual, ((m - 1) * mx_ldr + n) * ob, c, c_extent * ob))
+                return fail(op, GPURS_E_ALIASING, "the residual overlaps the output without being the output");
+        }
+        mx.row_bias = desc->row_bias, mx.residual = desc->residual, mx.ldr = mx_ldr, mx.beta = desc->beta == 0.0f ? 1.0f : desc->beta;
+        mx.accumulate = desc->accumulate == 1, mx.launch = desc->launch;
         return launch_mx(stream, mx);
     }
 
@@ -503,11 +589,15 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
                                  desc->c_type == GPURS_F32 && !sparse && !desc->scale_a && !b_row_major && (n + 127) / 128 <= uint64_t(gemm::SKINNY_MAX_TILES) &&
-                                 c % 4 == 0 && batches == 1 && !desc->row_absmax && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f);
+                                 c % 4 == 0 && batches == 1 && !desc->row_absmax && !desc->row_scale && !desc->column_scale && (desc->alpha == 0.0f || desc->alpha == 1.0f) &&
+                                 !desc->row_bias && !desc->residual && !desc->row_sum && !desc->accumulate;
     // N-major reading of 32-bit elements needs a different shared-memory swizzle (32-byte atoms) that these kernels
     // do not set up; measured: the plain 128-byte swizzle yields zeros for TF32.
-    if (b_row_major && (sparse || promoted || desc->a_type == GPURS_F32))
-        return fail(op, GPURS_E_INVALID_ARGUMENT, "a k x n right operand is supported by the dense 16-bit and 8-bit tile kernels only");
+    // fp32 operands at full precision are copied (split) before the product anyway: the copy of a k x n right operand is
+    // written transposed, and the product reads it K-major like any other.
+    const bool transposing_split = b_row_major && desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT && !sparse && !desc->scale_a;
+    if (b_row_major && !transposing_split && (sparse || promoted || desc->a_type == GPURS_F32))
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "a k x n right operand is supported by the dense 16-bit and 8-bit tile kernels and by full-precision fp32 products");
     if (group == GPURS_ALGO_SKINNY && !skinny_possible)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm needs m <= 64, 16-bit dense operands and fp32 output");
     if (batches > 1) {
@@ -528,7 +618,10 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
             return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product runs on the CTA-pair kernels only");
         group = GPURS_ALGO_CTA_PAIR;
     }
-    if (group == GPURS_ALGO_AUTO && skinny_possible) group = GPURS_ALGO_SKINNY;
+    // An explicit geometry speaks for the tile kernels: its cluster size picks between them when the caller left that open.
+    if (group == GPURS_ALGO_AUTO && desc->launch && (desc->launch->cluster[0] == 1 || desc->launch->cluster[0] == 2) && !promoted)
+        group = desc->launch->cluster[0] == 2 ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
+    if (group == GPURS_ALGO_AUTO && skinny_possible && !desc->launch) group = GPURS_ALGO_SKINNY;
     if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR && group != GPURS_ALGO_SKINNY)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
@@ -547,6 +640,37 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     }
     if (desc->precision != GPURS_PRECISION_DEFAULT && desc->precision != GPURS_PRECISION_TF32)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown precision");
+    if (desc->accumulate != 0 && desc->accumulate != 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulate must be 0 or 1");
+    if (desc->reserved != 0) return fail(op, GPURS_E_INVALID_ARGUMENT, "reserved fields must be 0");
+    const uint64_t ldr = desc->ldr ? desc->ldr : n;
+    if (desc->row_bias || desc->residual || desc->row_sum || desc->accumulate) {
+        if (desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "the output algebra is for floating-point outputs");
+        if (group == GPURS_ALGO_SKINNY) return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm takes a bias only");
+        if (desc->row_bias % 4 || desc->row_sum % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
+    }
+    if (desc->residual) {
+        if (batches > 1 || gather) return fail(op, GPURS_E_INVALID_ARGUMENT, "a residual is for single products");
+        if (ldr < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+        if (desc->residual % ob) return fail(op, GPURS_E_INVALID_VIEW, "the residual is not aligned to its element size");
+        if (desc->beta != desc->beta) return fail(op, GPURS_E_INVALID_ARGUMENT, "beta is not a number");
+        // C itself (updated in place, element by element) or memory that does not touch C
+        const bool in_place = desc->residual == c && ldr == ldc;
+        if (!in_place && overlap(desc->residual, ((m - 1) * ldr + n) * ob, c, c_extent * ob))
+            return fail(op, GPURS_E_ALIASING, "the residual overlaps the output without being the output");
+    }
+    if (desc->row_sum) {
+        if (sparse || promoted || batches > 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "the row reduction is for single dense products with float outputs on the tile kernels");
+        if (overlap(desc->row_sum, m * sizeof(float), c, c_extent * ob)) return fail(op, GPURS_E_ALIASING, "the row reduction overlaps the output");
+    }
+    if (desc->accumulate) {
+        if (desc->c_type != GPURS_F32) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulating into the output needs an fp32 output");
+        if (batches > 1 || gather) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulating into the output is for single products");
+        if (c % 4) return fail(op, GPURS_E_INVALID_VIEW, "the output is not aligned to its element size");
+    }
+    if (desc->launch) {
+        if (group == GPURS_ALGO_SKINNY) return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm sizes its own grid");
+        if (gather) return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product sizes its own grid");
+    }
     Gemm gemm;
     gemm.stem = choice.stem;
     gemm.element_type = desc->a_type;
@@ -562,6 +686,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.bias = desc->bias;
     gemm.row_scale = desc->row_scale, gemm.column_scale = desc->column_scale, gemm.alpha = desc->alpha;
     gemm.row_absmax = desc->row_absmax;
+    gemm.row_bias = desc->row_bias, gemm.residual = desc->residual, gemm.ldr = ldr, gemm.beta = desc->beta == 0.0f ? 1.0f : desc->beta;
+    gemm.row_sum = desc->row_sum, gemm.accumulate = desc->accumulate == 1, gemm.launch = desc->launch;
     gemm.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0;
     gemm.force_split = (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND) != 0;
     gemm.b_row_major = b_row_major;
@@ -588,12 +714,23 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         // fp32 operands at fp32-like accuracy: split both operands into TF32 hi and lo parts in scratch
         // memory, laid out so that ONE K-major product over 3K sums hi*hi + hi*lo + lo*hi.
         if (k % 4) return fail(op, GPURS_E_INVALID_VIEW, "operand bases and row pitches must be multiples of 16 bytes");
+        // the split operands are 3k deep, and the kernels index the depth with 32-bit integers
+        if (k > 0x7fffffffull / 3) return fail(op, GPURS_E_SIZE_OVERFLOW, "the depth of a full-precision fp32 product exceeds (2^31 - 1) / 3");
         const uint64_t a_split = m * 3 * k * sizeof(float), b_split = n * 3 * k * sizeof(float);
+        {
+            // the geometry is checked before the split kernels are enqueued: a rejected call launches nothing
+            gemm.threads = gemm::SCALED_THREADS;
+            uint64_t unused = 0;
+            result = explicit_ctas(op, desc->launch, gemm.cta_group, uint32_t(gemm.threads), shared_for(gemm), unused);
+            if (result != GPURS_OK) return result;
+        }
         CUdeviceptr scratch = 0;
         result = runtime::workspace_acquire(stream, a_split + b_split, &scratch);
         if (result != GPURS_OK) return result;
         result = split_tf32(stream, a, lda, scratch, m, k, 0);
-        if (result == GPURS_OK) result = split_tf32(stream, b, ldb, scratch + a_split, n, k, 1);
+        if (result == GPURS_OK) result = b_row_major ? split_tf32_transposed(stream, b, ldb, scratch + a_split, n, k)
+                                                     : split_tf32(stream, b, ldb, scratch + a_split, n, k, 1);
+        gemm.b_row_major = false;     // the split copy is n x 3k whatever B was
         gemm.a = scratch, gemm.b = scratch + a_split;
         gemm.lda = gemm.ldb = 3 * k;
         gemm.k = 3 * k;
@@ -724,14 +861,16 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         return api->cuMemcpy2DAsync(&copy, on);
     };
     auto driver_failed = [&](CUresult code) { return runtime::fail_driver(api, "gpurs_matmul_host copy", code); };
+    // From here on no exit may skip join(): a failure is remembered in `result` and the loops stop.
+    auto checked = [&](CUresult code, const char *what) { return code == CUDA_SUCCESS ? int(GPURS_OK) : runtime::fail_driver(api, what, code); };
     const uint8_t *bytes_a = static_cast<const uint8_t *>(host_a), *bytes_b = static_cast<const uint8_t *>(host_b);
     uint8_t *bytes_c = static_cast<uint8_t *>(host_c);
     if (k) {
         const CUresult code = by_columns ? copy_rows(true, a, host_a, m, k * eb, lda * eb, gpu->copy_in)
                                          : copy_rows(true, b, host_b, b_rows, b_columns * eb, ldb * eb, gpu->copy_in);
-        if (code) return driver_failed(code);
-        GPURS_TRY(api, cuEventRecord(whole_arrived, gpu->copy_in));
-        GPURS_TRY(api, cuStreamWaitEvent(stream->handle, whole_arrived, 0));
+        if (code) result = driver_failed(code);
+        if (result == GPURS_OK) result = checked(api->cuEventRecord(whole_arrived, gpu->copy_in), "cuEventRecord");
+        if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(stream->handle, whole_arrived, 0), "cuStreamWaitEvent");
     }
     gpurs_matmul_desc local = *desc;
     local.a_len = local.b_len = local.c_len = 0;
@@ -746,9 +885,10 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         if (k) {
             const CUresult code = by_columns ? copy_rows(true, b + operand_offset, bytes_b + operand_offset, count, k * eb, ldb * eb, gpu->copy_in)
                                              : copy_rows(true, a + operand_offset, bytes_a + operand_offset, count, k * eb, lda * eb, gpu->copy_in);
-            if (code) return driver_failed(code);
-            GPURS_TRY(api, cuEventRecord(arrived, gpu->copy_in));
-            GPURS_TRY(api, cuStreamWaitEvent(stream->handle, arrived, 0));
+            if (code) result = driver_failed(code);
+            if (result == GPURS_OK) result = checked(api->cuEventRecord(arrived, gpu->copy_in), "cuEventRecord");
+            if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(stream->handle, arrived, 0), "cuStreamWaitEvent");
+            if (result != GPURS_OK) break;
         }
         if (by_columns) {
             // columns [first, first + count) of C: the per-column vectors and B's scale rows move along
@@ -764,11 +904,12 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
             result = matmul_checked(op, stream, &local, a + operand_offset, b, c + c_offset, nullptr);
         }
         if (result != GPURS_OK) break;
-        GPURS_TRY(api, cuEventRecord(c_ready, stream->handle));
-        GPURS_TRY(api, cuStreamWaitEvent(gpu->copy_out, c_ready, 0));
+        result = checked(api->cuEventRecord(c_ready, stream->handle), "cuEventRecord");
+        if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(gpu->copy_out, c_ready, 0), "cuStreamWaitEvent");
+        if (result != GPURS_OK) break;
         const CUresult code = by_columns ? copy_rows(false, c + c_offset, bytes_c + c_offset, m, count * ob, ldc * ob, gpu->copy_out)
                                          : copy_rows(false, c + c_offset, bytes_c + c_offset, count, n * ob, ldc * ob, gpu->copy_out);
-        if (code) return driver_failed(code);
+        if (code) result = driver_failed(code);
     }
     const int joined = join();
     return result != GPURS_OK ? result : joined;

@@ -16,8 +16,11 @@
 //     calls on one stream are ordered by the stream and are safe;
 //   * nothing in the array has to start at zero: the split kernel writes every element the GEMM reads,
 //     rows past the end of a tile come from the TMA unit's out-of-range fill, not from the array;
-//   * the first call on each device looks the array's device address up and loads the kernels; make that
-//     first call before starting any stream capture.
+//   * every call asks the CUDA runtime for the array's device address (a host-side lookup that allocates
+//     nothing once the library image is loaded on the device) and hands that one address to both kernels,
+//     so a handle that was closed and reopened, or a context that was torn down and rebuilt in between,
+//     can never leave a stale address behind.  The first call on each device also loads the kernels; make
+//     that first call before starting any stream capture.
 #include "gemm_launch.hpp"
 
 #include <cuda_runtime.h>
@@ -34,16 +37,17 @@ static __device__ __align__(256) float static_scratch[GPURS_STATIC_SCRATCH_BYTES
 // Same split as the regular path's kernel: x -> hi = tf32(x), lo = tf32(x - hi), written as three K-wide
 // segments per row, [hi | hi | lo] for the left operand and [hi | lo | hi] for the right one, so that one
 // K-major product over 3K gives hi*hi + hi*lo + lo*hi.  Both operands are handled by one launch and the
-// destination is the static array, named directly: rows of A first, rows of B from `b_offset` floats on.
+// destination is the static array at the address the host resolved for this call (`scratch`, the same pointer the
+// product's TMA descriptors are built from): rows of A first, rows of B from `b_offset` floats on.
 __global__ void __launch_bounds__(256)
-split_tf32_static(const float *__restrict__ a, const float *__restrict__ b, int m, int n, int k, long long b_offset) {
+split_tf32_static(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ scratch, int m, int n, int k, long long b_offset) {
     const long long quads_per_row = k / 4;
     const long long total = (long long)(m + n) * quads_per_row;
     for (long long index = blockIdx.x * (long long)blockDim.x + threadIdx.x; index < total; index += (long long)gridDim.x * blockDim.x) {
         const long long row = index / quads_per_row, quad = index - row * quads_per_row;
         const bool left = row < m;
         const float *source = left ? a + row * (long long)k : b + (row - m) * (long long)k;
-        float *out = left ? static_scratch + row * 3ll * k : static_scratch + b_offset + (row - m) * 3ll * k;
+        float *out = left ? scratch + row * 3ll * k : scratch + b_offset + (row - m) * 3ll * k;
         const float4 x = *reinterpret_cast<const float4 *>(source + quad * 4);
         const float in[4] = {x.x, x.y, x.z, x.w};
         float hi[4], lo[4];
@@ -62,9 +66,6 @@ split_tf32_static(const float *__restrict__ a, const float *__restrict__ b, int 
         *reinterpret_cast<float4 *>(out + 2ll * k) = left ? low : high;
     }
 }
-
-constexpr int MAX_DEVICES = 64;
-float *scratch_address[MAX_DEVICES];   // device address of static_scratch, per device ordinal; set once
 
 int fail_runtime(const char *operation, cudaError_t code) {
     return runtime::fail(operation, int(code), cudaGetErrorString(code));
@@ -87,32 +88,29 @@ extern "C" int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_
     if (a % 16 || b % 16 || c % 4) return runtime::fail(op, GPURS_E_INVALID_VIEW, "operands must be 16-byte aligned, the output 4-byte aligned");
     // Split copies: m x 3k floats, then (256-byte aligned) n x 3k floats.
     const uint64_t a_split = (m * 3 * k * 4 + 255) & ~uint64_t(255), b_split = n * 3 * k * 4;
-    if (a_split + b_split > uint64_t(GPURS_STATIC_SCRATCH_BYTES)) {
+    // each term is below 2^64 for dimensions below 2^31 (3k included); their sum need not be: compare without adding
+    if (a_split > uint64_t(GPURS_STATIC_SCRATCH_BYTES) || b_split > uint64_t(GPURS_STATIC_SCRATCH_BYTES) - a_split) {
         static thread_local char message[160];
         std::snprintf(message, sizeof message, "the split operands need %llu bytes but the static scratch holds %llu: use gpurs_matmul",
-                      (unsigned long long)(a_split + b_split), (unsigned long long)GPURS_STATIC_SCRATCH_BYTES);
+                      (unsigned long long)(a_split + std::min<uint64_t>(b_split, ~uint64_t(0) - a_split)), (unsigned long long)GPURS_STATIC_SCRATCH_BYTES);
         return runtime::fail(op, GPURS_E_SIZE_OVERFLOW, message);
     }
     const uint64_t a_bytes = m * k * 4, b_bytes = n * k * 4, c_bytes = m * n * 4;
     if (overlap(c, c_bytes, a, a_bytes) || overlap(c, c_bytes, b, b_bytes))
         return runtime::fail(op, GPURS_E_ALIASING, "the output overlaps an operand");
-    if (gpu->device < 0 || gpu->device >= MAX_DEVICES) return runtime::fail(op, GPURS_E_INVALID_ARGUMENT, "device ordinal out of range");
 
     runtime::Enter enter(gpu);   // the gpu's (primary) context is current from here on, for both APIs
-    if (!scratch_address[gpu->device]) {
-        // Once per device, with that device current: ask the runtime where the array lives on it.
-        float *address = nullptr;
-        const cudaError_t found = cudaGetSymbolAddress(reinterpret_cast<void **>(&address), static_scratch);
-        if (found != cudaSuccess) return fail_runtime("cudaGetSymbolAddress", found);
-        if (!address) return runtime::fail(op, GPURS_E_INVALID_ARGUMENT, "the static scratch has no device address");
-        scratch_address[gpu->device] = address;
-    }
-    float *const scratch = scratch_address[gpu->device];
+    // With that device current: ask the runtime where the array lives in this context.  Asked on every call, never
+    // cached: the answer belongs to the context that is current now.
+    float *scratch = nullptr;
+    const cudaError_t found = cudaGetSymbolAddress(reinterpret_cast<void **>(&scratch), static_scratch);
+    if (found != cudaSuccess) return fail_runtime("cudaGetSymbolAddress", found);
+    if (!scratch) return runtime::fail(op, GPURS_E_INVALID_ARGUMENT, "the static scratch has no device address");
 
     const uint64_t quads = (m + n) * (k / 4);
     const unsigned blocks = unsigned(std::max<uint64_t>(1, std::min<uint64_t>((quads + 255) / 256, uint64_t(gpu->multiprocessors) * 8)));
     split_tf32_static<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream->handle)>>>(
-        reinterpret_cast<const float *>(a), reinterpret_cast<const float *>(b), int(m), int(n), int(k), (long long)(a_split / 4));
+        reinterpret_cast<const float *>(a), reinterpret_cast<const float *>(b), scratch, int(m), int(n), int(k), (long long)(a_split / 4));
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) return fail_runtime("split_tf32_static", launched);
     gpu->launches++;

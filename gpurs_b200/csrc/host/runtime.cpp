@@ -102,6 +102,15 @@ int launch(gpurs_kernel *kernel, gpurs_stream *stream, const gpurs_launch_config
     return GPURS_OK;
 }
 
+// Lets go of one graph's hold on a block; a block the handle has already replaced is freed with its last holder.
+void block_unborrow(gpurs_gpu *gpu, gpurs_gpu::Block *block) {
+    if (!block) return;
+    if (--block->graphs == 0 && !block->current) {
+        gpu->api->cuMemFree(block->pointer);
+        delete block;
+    }
+}
+
 static int scratch_acquire(gpurs_stream *stream, gpurs_gpu::Scratch &scratch, size_t bytes, bool zeroed, CUdeviceptr *out) {
     gpurs_gpu *gpu = stream->gpu;
     const driver::Api *api = gpu->api;
@@ -109,31 +118,44 @@ static int scratch_acquire(gpurs_stream *stream, gpurs_gpu::Scratch &scratch, si
     // block must not move under it.  The graph remembers that it borrows the block and orders itself at every replay.
     CUstreamCaptureStatus capture = CU_STREAM_CAPTURE_STATUS_NONE;
     GPURS_TRY(api, cuStreamIsCapturing(stream->handle, &capture));
+    const size_t held = scratch.block ? scratch.block->bytes : 0;
     if (capture == CU_STREAM_CAPTURE_STATUS_ACTIVE) {
-        if (scratch.bytes < bytes)
+        if (held < bytes)
             return fail("capture", GPURS_E_INVALID_ARGUMENT, "scratch memory cannot grow during a capture: run the same product once before capturing it");
         scratch.captured = true;
-        *out = scratch.pointer;
+        *out = scratch.block->pointer;
         return GPURS_OK;
     }
-    if (scratch.bytes < bytes) {
-        // Nobody may still be using the old block when it is replaced.
+    if (held < bytes) {
+        // Nobody may still be using the old block when it is replaced.  A block whose address a live graph holds is not
+        // freed here: it stays allocated, for that graph's replays alone, until the graph is freed.
         GPURS_TRY(api, cuCtxSynchronize());
-        if (scratch.pointer) GPURS_TRY(api, cuMemFree(scratch.pointer));
-        scratch.pointer = 0;
-        scratch.bytes = 0;
         const size_t rounded = (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);
-        GPURS_TRY(api, cuMemAlloc(&scratch.pointer, rounded));
-        scratch.bytes = rounded;
+        gpurs_gpu::Block *fresh = new (std::nothrow) gpurs_gpu::Block{};
+        if (!fresh) return fail("scratch", GPURS_E_SIZE_OVERFLOW, "out of host memory");
+        const CUresult allocated = api->cuMemAlloc(&fresh->pointer, rounded);
+        if (allocated != CUDA_SUCCESS) {
+            delete fresh;
+            return fail_driver(api, "cuMemAlloc", allocated);
+        }
+        fresh->bytes = rounded;
+        if (gpurs_gpu::Block *old = scratch.block) {
+            old->current = false;
+            if (old->graphs == 0) {
+                api->cuMemFree(old->pointer);
+                delete old;
+            }
+        }
+        scratch.block = fresh;
         scratch.used = false;
         if (zeroed) {
-            GPURS_TRY(api, cuMemsetD8Async(scratch.pointer, 0, rounded, gpu->transfer));
+            GPURS_TRY(api, cuMemsetD8Async(fresh->pointer, 0, rounded, gpu->transfer));
             GPURS_TRY(api, cuStreamSynchronize(gpu->transfer));
         }
     }
     if (!scratch.event) GPURS_TRY(api, cuEventCreate(&scratch.event, CU_EVENT_DISABLE_TIMING));
     if (scratch.used) GPURS_TRY(api, cuStreamWaitEvent(stream->handle, scratch.event, 0));
-    *out = scratch.pointer;
+    *out = scratch.block->pointer;
     return GPURS_OK;
 }
 
@@ -239,7 +261,14 @@ void gpurs_gpu_free(gpurs_gpu *gpu) {
         }
         gpu->api->cuMemFree(gpu->status);
         for (gpurs_gpu::Scratch *scratch : {&gpu->workspace, &gpu->turns}) {
-            if (scratch->pointer) gpu->api->cuMemFree(scratch->pointer);
+            // a block that a graph still holds is left to that graph (graphs are to be freed before their gpu)
+            if (gpurs_gpu::Block *block = scratch->block) {
+                block->current = false;
+                if (block->graphs == 0) {
+                    gpu->api->cuMemFree(block->pointer);
+                    delete block;
+                }
+            }
             if (scratch->event) gpu->api->cuEventDestroy(scratch->event);
         }
         gpu->api->cuStreamDestroy(gpu->transfer);
@@ -342,8 +371,14 @@ int gpurs_stream_capture_end(gpurs_stream *stream, gpurs_graph **out) {
         gpu->api->cuGraphDestroy(graph);
         return runtime::fail_driver(gpu->api, "cuGraphInstantiate", code);
     }
-    gpurs_graph *result = new (std::nothrow) gpurs_graph{gpu, graph, executable, nodes, gpu->workspace.captured, gpu->turns.captured};
+    gpurs_graph *result = new (std::nothrow) gpurs_graph{gpu, graph, executable, nodes, gpu->workspace.captured ? gpu->workspace.block : nullptr,
+                                                         gpu->turns.captured ? gpu->turns.block : nullptr};
     gpu->workspace.captured = gpu->turns.captured = false;
+    if (result) {
+        // the recording holds these addresses: the blocks must outlive it, wherever the handle's scratch moves meanwhile
+        if (result->workspace_block) result->workspace_block->graphs++;
+        if (result->turns_block) result->turns_block->graphs++;
+    }
     if (!result) {
         gpu->api->cuGraphExecDestroy(executable);
         gpu->api->cuGraphDestroy(graph);
@@ -359,12 +394,13 @@ int gpurs_graph_launch(gpurs_graph *graph, gpurs_stream *stream) {
     gpurs_gpu *gpu = graph->gpu;
     Enter enter(gpu);
     // A graph that borrows the handle's scratch takes its turn like any other borrower.
-    gpurs_gpu::Scratch *borrowed[2] = {graph->uses_workspace ? &gpu->workspace : nullptr, graph->uses_turns ? &gpu->turns : nullptr};
+    gpurs_gpu::Scratch *borrowed[2] = {graph->workspace_block ? &gpu->workspace : nullptr, graph->turns_block ? &gpu->turns : nullptr};
     for (gpurs_gpu::Scratch *scratch : borrowed)
         if (scratch && scratch->used) GPURS_TRY(gpu->api, cuStreamWaitEvent(stream->handle, scratch->event, 0));
     GPURS_TRY(gpu->api, cuGraphLaunch(graph->executable, stream->handle));
     for (gpurs_gpu::Scratch *scratch : borrowed)
         if (scratch) {
+            if (!scratch->event) GPURS_TRY(gpu->api, cuEventCreate(&scratch->event, CU_EVENT_DISABLE_TIMING));
             GPURS_TRY(gpu->api, cuEventRecord(scratch->event, stream->handle));
             scratch->used = true;
         }
@@ -377,6 +413,11 @@ void gpurs_graph_free(gpurs_graph *graph) {
     Enter enter(graph->gpu);
     graph->gpu->api->cuGraphExecDestroy(graph->executable);
     graph->gpu->api->cuGraphDestroy(graph->graph);
+    // Replays still in flight may be using the blocks: wait for them before a replaced block is freed.
+    if ((graph->workspace_block && !graph->workspace_block->current) || (graph->turns_block && !graph->turns_block->current))
+        graph->gpu->api->cuCtxSynchronize();
+    runtime::block_unborrow(graph->gpu, graph->workspace_block);
+    runtime::block_unborrow(graph->gpu, graph->turns_block);
     delete graph;
 }
 
@@ -512,6 +553,16 @@ int gpurs_fill_u8(gpurs_stream *stream, gpurs_device_ptr destination, uint8_t va
     if (bytes == 0) return GPURS_OK;
     Enter enter(stream->gpu);
     GPURS_TRY(stream->gpu->api, cuMemsetD8Async(destination, value, bytes, stream->handle));
+    return GPURS_OK;
+}
+
+int gpurs_memory_info(gpurs_gpu *gpu, size_t *free_bytes, size_t *total_bytes) {
+    if (!gpu) return fail("gpurs_memory_info", GPURS_E_INVALID_ARGUMENT, "null gpu");
+    Enter enter(gpu);
+    size_t free_now = 0, total = 0;
+    GPURS_TRY(gpu->api, cuMemGetInfo(&free_now, &total));
+    if (free_bytes) *free_bytes = free_now;
+    if (total_bytes) *total_bytes = total;
     return GPURS_OK;
 }
 

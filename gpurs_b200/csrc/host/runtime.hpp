@@ -30,11 +30,18 @@ struct gpurs_gpu {
     gpurs_module *builtin = nullptr;   // the embedded sm_100a image, loaded on first use
     std::map<std::string, gpurs_kernel *> kernels;
     uint64_t launches = 0;
-    // Scratch owned by the handle.  Each block has one user at a time: `event` marks the end of the previous
-    // user's work and the next user's stream waits on it.
-    struct Scratch {
+    // One allocation of scratch memory.  A recorded graph keeps the address it was recorded with, so a block stays
+    // allocated while any live graph borrows it (`graphs`), even after the handle has moved on to a larger block.
+    struct Block {
         CUdeviceptr pointer = 0;
         size_t bytes = 0;
+        int graphs = 0;          // live gpurs_graph objects whose recording holds this block's address
+        bool current = true;     // false once the handle has replaced it: freed when the last graph lets go
+    };
+    // Scratch owned by the handle.  Each scratch has one user at a time: `event` marks the end of the previous
+    // user's work and the next user's stream waits on it.
+    struct Scratch {
+        Block *block = nullptr;
         CUevent event = nullptr;
         bool used = false;
         bool captured = false;   // borrowed by work recorded into the capture now in progress
@@ -59,7 +66,8 @@ struct gpurs_graph {
     CUgraph graph;
     CUgraphExec executable;
     size_t nodes;                // operations recorded: what one replay adds to the launch count
-    bool uses_workspace, uses_turns;
+    // The scratch blocks whose addresses the recording holds (null = none): kept allocated until the graph is freed.
+    gpurs_gpu::Block *workspace_block, *turns_block;
 };
 
 struct gpurs_event {

@@ -50,8 +50,17 @@ struct Params {
     unsigned int *split_counters;
     int max_contributors;
     int split_tiles;            // tiles of the last round that are split (the host's decision, gemm_schedule.hpp)
+    // More epilogue algebra on float outputs, after the bias and before the output rounding (each optional):
+    //     value + row_bias[row] + beta * residual[row, column]
+    const float *row_bias;      // fp32 [M] or null: one value added to every element of the row
+    const void *residual;       // matrix of C's element type with row pitch ldr (elements), or null; it may be C itself
+    long long ldr;
+    float beta;                 // factor of the residual
+    int accumulate;             // fp32 output only: 1 = add the result to what C holds (atomic adds) instead of storing it
+    float *row_sum;             // fp32 [M] or null: the sum of each output row's values (after the algebra, before the output
+                                // rounding) is added in with atomic adds, one per row and tile; the caller zeroes it first
 };
-static_assert(sizeof(Params) == 152, "the parameter block is part of the kernel image's interface");
+static_assert(sizeof(Params) == 192, "the parameter block is part of the kernel image's interface");
 
 constexpr int MAX_PUSH_TARGETS = 8;   // GPUs of one box
 

@@ -83,11 +83,21 @@ __device__ __forceinline__ void tmem_load_columns(uint32_t address, uint32_t (&v
     else ptx::tmem_load_32x64(address, values);
 }
 
+// One element of the residual matrix (stored in C's element type) as fp32.  Plain loads: the residual may be C itself,
+// which this kernel writes (every element is read by the thread that later writes it, before it writes it).
+template <int OUT>
+__device__ __forceinline__ float residual_element(const Params &p, int row, int column) {
+    const size_t index = size_t(row) * size_t(p.ldr) + size_t(column);
+    if constexpr (OUT == OUT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.residual)[index]);
+    else if constexpr (OUT == OUT_F16) return __half2float(reinterpret_cast<const __half *>(p.residual)[index]);
+    else return reinterpret_cast<const float *>(p.residual)[index];
+}
+
 // The epilogue algebra on 32 accumulator columns of one output row, starting at `column`:
-// value * (alpha * row_scale[row]) * column_scale[column] + bias[column], each part optional (float outputs only),
-// every step rounded to fp32 on its own (no fused multiply-add), so that a host can reproduce the result exactly.
-// The reference offers the same steps on its accumulator tiles: scale, scale_rows, scale_columns, add_columns
-// (crates/gpurs/src/gpu/tensor/warp/accumulators.rs:86-110).
+// value * (alpha * row_scale[row]) * column_scale[column] + bias[column] + row_bias[row] + beta * residual[row, column],
+// each part optional (float outputs only), every step rounded to fp32 on its own (no fused multiply-add), so that a host
+// can reproduce the result exactly.  The reference offers the same steps on its accumulator tiles: scale, scale_rows,
+// scale_columns, add_columns, add_rows and add of another tile (crates/gpurs/src/gpu/tensor/warp/accumulators.rs:82-110).
 template <int OUT>
 __device__ __forceinline__ void apply_epilogue(const Params &p, uint32_t (&acc)[32], int row, int column) {
     if constexpr (OUT != OUT_I32) {
@@ -107,7 +117,26 @@ __device__ __forceinline__ void apply_epilogue(const Params &p, uint32_t (&acc)[
             for (int i = 0; i < 32; i++)
                 if (column + i < p.n) acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), __ldg(p.bias + column + i)));
         }
+        if (p.row_bias != nullptr) {
+            const float addend = __ldg(p.row_bias + min(row, p.m - 1));
+#pragma unroll
+            for (int i = 0; i < 32; i++) acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), addend));
+        }
+        if (p.residual != nullptr && row < p.m) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (column + i < p.n)
+                    acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), __fmul_rn(p.beta, residual_element<OUT>(p, row, column + i))));
+        }
     }
+}
+
+// running + the values of this chunk's columns that exist, added in column order (`reduce_rows` with + as the operation).
+__device__ __forceinline__ float fold_sum(const Params &p, const uint32_t (&acc)[32], int column, float running) {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+        if (column + i < p.n) running = __fadd_rn(running, __uint_as_float(acc[i]));
+    return running;
 }
 
 // Two fp32 accumulators rounded to nearest even and packed into one word of bf16 or f16.
@@ -131,7 +160,7 @@ __device__ __forceinline__ float fold_absmax(const Params &p, const uint32_t (&a
     return running;
 }
 
-template <int OUT, bool APPLY = true>
+template <int OUT, bool APPLY = true, bool ATOMIC = true>
 __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&source)[32], int row, int column, long long element_offset = 0) {
     if (row >= p.m || column >= p.n) return;
     const bool whole = column + 32 <= p.n && p.vector_stores;
@@ -141,6 +170,16 @@ __device__ __forceinline__ void store_chunk(const Params &p, const uint32_t (&so
     if constexpr (APPLY) apply_epilogue<OUT>(p, acc, row, column);
     if constexpr (OUT == OUT_F32 || OUT == OUT_I32) {
         uint32_t *out = reinterpret_cast<uint32_t *>(p.c) + element_offset + size_t(row) * p.ldc + column;
+        if constexpr (OUT == OUT_F32 && ATOMIC) {
+            if (p.accumulate != 0) {
+                // `accumulate` of the reference's f32 output matrix (crates/gpurs/src/gpu/tensor/output/reduction.rs:157-202):
+                // one atomic add per element, so that any number of products may add into the same C at once
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (column + i < p.n) atomicAdd(reinterpret_cast<float *>(out) + i, __uint_as_float(acc[i]));
+                return;
+            }
+        }
         if (whole) {
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -236,8 +275,10 @@ struct WorkWalker {
 // PUSH: the epilogue stores every box to all GPUs' copies (PushTargets).  BATCHED: the operands and the output are batches
 // of matrices described by rank-3 tensor maps (z = batch); tiles are numbered batch by batch.
 // STREAMK: the tiles of the last, partial round are split along K over all CTA groups (gemm_schedule.hpp).
+// ALGEBRA: the epilogue applies the optional output algebra and row reductions of Params.  The entries without it are
+// the ones a plain product runs: their epilogue is load, round, stage, store, and nothing else is compiled in.
 template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, int BLOCK_N, int CTA_GROUP, int STAGES, bool PUSH = false, bool BATCHED = false,
-          bool STREAMK = false>
+          bool STREAMK = false, bool ALGEBRA = true>
 __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p,
                                           const PushTargets *targets = nullptr) {
     using L = SharedLayout<BLOCK_N, CTA_GROUP, STAGES>;
@@ -455,8 +496,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BLOCK_N;
-            const bool reduce = OUT != OUT_I32 && p.row_absmax != nullptr;
-            float row_max = 0.0f;
+            const bool reduce = ALGEBRA && OUT != OUT_I32 && p.row_absmax != nullptr;
+            const bool summing = ALGEBRA && OUT != OUT_I32 && p.row_sum != nullptr;
+            float row_max = 0.0f, row_total = 0.0f;
             const bool shared_tile = STREAMK && item.split_tile >= 0;
             // A tile of the split round holds only this group's K-blocks: its 32-bit sums go to scratch as they are.
             constexpr int TILE_ROWS = BLOCK_M * CTA_GROUP;
@@ -489,16 +531,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     if constexpr (COLUMNS_PER_BOX == 32) {
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
                         ptx::tmem_load_wait();
-                        apply_epilogue<OUT>(p, packed, row, column);
+                        if constexpr (ALGEBRA) apply_epilogue<OUT>(p, packed, row, column);
                         if (reduce) row_max = fold_absmax(p, packed, column, row_max);
+                        if (summing) row_total = fold_sum(p, packed, column, row_total);
                     } else {
                         uint32_t low[32], high[32];
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
                         ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
                         ptx::tmem_load_wait();
-                        apply_epilogue<OUT>(p, low, row, column);
-                        apply_epilogue<OUT>(p, high, row, column + 32);
+                        if constexpr (ALGEBRA) {
+                            apply_epilogue<OUT>(p, low, row, column);
+                            apply_epilogue<OUT>(p, high, row, column + 32);
+                        }
                         if (reduce) row_max = fold_absmax(p, high, column + 32, fold_absmax(p, low, column, row_max));
+                        if (summing) row_total = fold_sum(p, high, column + 32, fold_sum(p, low, column, row_total));
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
@@ -525,6 +571,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                                 }
                             } else if constexpr (BATCHED) {
                                 ptx::tma_store_3d(map_c, column, warp_row, batch, buffer);
+                            } else if (ALGEBRA && OUT == OUT_F32 && p.accumulate != 0) {
+                                // the staged box is added to C by the TMA unit (element-wise atomic f32 adds)
+                                ptx::tma_reduce_add_2d(map_c, column, warp_row, buffer);
                             } else {
                                 ptx::tma_store_2d(map_c, column, warp_row, buffer);
                             }
@@ -538,13 +587,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                     uint32_t values[32];
                     ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
                     ptx::tmem_load_wait();
-                    apply_epilogue<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
+                    if constexpr (ALGEBRA) apply_epilogue<OUT>(p, values, row, tile_n * BLOCK_N + chunk * 32);
                     if (reduce) row_max = fold_absmax(p, values, tile_n * BLOCK_N + chunk * 32, row_max);
-                    store_chunk<OUT, false>(p, values, row, tile_n * BLOCK_N + chunk * 32, BATCHED ? batch * p.batch_stride_c : 0ll);
+                    if (summing) row_total = fold_sum(p, values, tile_n * BLOCK_N + chunk * 32, row_total);
+                    store_chunk<OUT, false, ALGEBRA>(p, values, row, tile_n * BLOCK_N + chunk * 32, BATCHED ? batch * p.batch_stride_c : 0ll);
                 }
             }
             // non-negative floats order like their bit patterns, so an unsigned atomic max folds the tile's part in
             if (reduce && row < p.m) atomicMax(reinterpret_cast<unsigned int *>(p.row_absmax) + row, __float_as_uint(row_max));
+            if (summing && row < p.m && !shared_tile) atomicAdd(p.row_sum + row, row_total);
             ptx::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -597,11 +648,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                                     }
                             }
                             const int column = tile_n * BLOCK_N + chunk * 32;
-                            apply_epilogue<OUT>(p, sum, row, column);
+                            if constexpr (ALGEBRA) apply_epilogue<OUT>(p, sum, row, column);
                             if (reduce) row_max = fold_absmax(p, sum, column, row_max);
-                            store_chunk<OUT, false>(p, sum, row, column);
+                            if (summing) row_total = fold_sum(p, sum, column, row_total);
+                            store_chunk<OUT, false, ALGEBRA>(p, sum, row, column);
                         }
                         if (reduce && row < p.m) atomicMax(reinterpret_cast<unsigned int *>(p.row_absmax) + row, __float_as_uint(row_max));
+                        if (summing && row < p.m) atomicAdd(p.row_sum + row, row_total);
                     }
                 }
             }

@@ -394,6 +394,14 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int32_t x, 
                  : "memory");
 }
 
+// The same box added element-wise into the tensor (fp32 tensors: atomic adds performed by the TMA unit).  Like the store
+// it must not start at a negative coordinate.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, int32_t x, int32_t y, uint32_t src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 // Waits until at most PENDING of this thread's store groups still read their shared-memory source.

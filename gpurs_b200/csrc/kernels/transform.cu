@@ -41,6 +41,41 @@ gpurs_split_tf32(const float *__restrict__ source, long long source_pitch, float
     }
 }
 
+// The same split for a right operand stored K x N (row-major B of C = A * B): tiles of 32 x 32 elements go through shared
+// memory, so that the reads run along N and the writes along K, and the destination is the N x 3K array [hi | lo | hi] the
+// product reads K-major.  Block = 32 x 8 threads, one tile per block and grid-stride step.
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_split_tf32_transposed(const float *__restrict__ source, long long source_pitch, float *__restrict__ destination, int n, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    __shared__ float tile[32][33];
+    const int tiles_n = (n + 31) / 32, tiles_k = (k + 31) / 32;
+    const int x = threadIdx.x % 32, y = threadIdx.x / 32;
+    for (long long t = blockIdx.x; t < (long long)tiles_n * tiles_k; t += gridDim.x) {
+        const int tile_k = int(t / tiles_n), tile_n = int(t - (long long)tile_k * tiles_n);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int kk = tile_k * 32 + y + 8 * i, nn = tile_n * 32 + x;
+            tile[y + 8 * i][x] = (kk < k && nn < n) ? source[kk * source_pitch + nn] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int nn = tile_n * 32 + y + 8 * i, kk = tile_k * 32 + x;
+            if (nn < n && kk < k) {
+                const float value = tile[x][y + 8 * i];
+                uint32_t bits;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(value));
+                const float hi = __uint_as_float(bits);
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(value - hi));
+                const float lo = __uint_as_float(bits);
+                float *out = destination + nn * 3ll * k + kk;
+                out[0] = hi, out[k] = lo, out[2ll * k] = hi;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 #include "gemm_sparse_tcgen05.cuh"
 
 // 2:4 compression of a 16-bit matrix (no counterpart in the reference, which has no sparse path).  One

@@ -337,6 +337,13 @@ class MatmulOptions:
     row_absmax: DeviceBuffer | None = None     # fp32 [m], zeroed by the caller: max |C[row, :]| is folded in
     scale_kind: int = _ffi.SCALES_FP32_BLOCKS  # SCALES_MX: scale_a / scale_b are tiled UE8M0 bytes from quantize_mx_e4m3
     metadata: DeviceBuffer | None = None   # 2:4-sparse A: `a` holds the kept values, see compress_24
+    row_bias: DeviceBuffer | None = None       # fp32 [m], added to every element of its row (after the bias)
+    residual: DeviceBuffer | None = None       # m x n matrix of C's element type, added as beta * residual (may be C itself)
+    ldr: int = 0                               # its row pitch in elements; 0 = n
+    beta: float = 0.0                          # 0 = 1
+    row_sum: DeviceBuffer | None = None        # fp32 [m], zeroed by the caller: the sum of each row of the result is added in
+    accumulate: bool = False                   # fp32 output: add the product to what C holds (atomic adds)
+    launch: LaunchConfig | None = None         # explicit geometry (`stream.launch(LaunchConfig)` in the reference)
     extra: dict = field(default_factory=dict)
 
 
@@ -373,6 +380,14 @@ def matmul(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, c: DeviceBuffer, sh
     desc.stride_a, desc.stride_b, desc.stride_c = options.stride_a, options.stride_b, options.stride_c
     desc.row_absmax = options.row_absmax.pointer if options.row_absmax else 0
     desc.scale_kind = options.scale_kind
+    desc.row_bias = options.row_bias.pointer if options.row_bias else 0
+    desc.residual = options.residual.pointer if options.residual else 0
+    desc.ldr, desc.beta = options.ldr, options.beta
+    desc.row_sum = options.row_sum.pointer if options.row_sum else 0
+    desc.accumulate = 1 if options.accumulate else 0
+    launch = options.launch._struct() if options.launch else None     # kept alive until the call returns
+    if launch is not None:
+        desc.launch = C.pointer(launch)
     _check(stream.gpu._lib.gpurs_matmul(stream._handle, C.byref(desc), a.pointer, b.pointer, c.pointer))
 
 
@@ -431,6 +446,38 @@ class GatheredMatrix:
             if peer != self.rank and pointer and self.gpu._handle:
                 self.gpu._lib.gpurs_ipc_close(self.gpu._handle, pointer)
         self.pointers = []
+
+
+def comm_unique_id() -> bytes:
+    """A fresh 128-byte communicator id (made on one rank, handed to all ranks by any means the host has)."""
+    raw = (C.c_uint8 * _ffi.COMM_ID_BYTES)()
+    _check(_ffi.load().gpurs_comm_unique_id(raw))
+    return bytes(raw)
+
+
+class Communicator:
+    """One rank's end of an NCCL communicator over the GPUs of the box, for the all-gather of C that may follow an
+    M-sharded product.  `exchange(id: bytes | None) -> bytes` takes rank 0's id and returns it on every rank (a broadcast
+    of any process group will do).  No counterpart in the reference, which drives one GPU."""
+
+    def __init__(self, gpu: "Gpu", rank: int, world: int, exchange):
+        self.gpu, self.rank, self.world = gpu, rank, world
+        unique = exchange(comm_unique_id() if rank == 0 else None)
+        if not isinstance(unique, (bytes, bytearray)) or len(unique) != _ffi.COMM_ID_BYTES:
+            raise ValueError("exchange must return the 128-byte id of rank 0 on every rank")
+        self._handle = C.c_void_p()
+        _check(gpu._lib.gpurs_comm_init(gpu._handle, (C.c_uint8 * _ffi.COMM_ID_BYTES).from_buffer_copy(bytes(unique)), world, rank, C.byref(self._handle)))
+
+    def allgather(self, stream: Stream, full: DeviceBuffer, block_bytes: int) -> None:
+        """In place on `full` (world * block_bytes bytes, this rank's block already at position `rank`); does not wait."""
+        if full.nbytes < self.world * block_bytes:
+            raise GpursErrorLocal(_ffi.E_LENGTH_MISMATCH, "the gathered buffer is smaller than world * block_bytes")
+        _check(self.gpu._lib.gpurs_comm_allgather(self._handle, stream._handle, full.pointer, block_bytes))
+
+    def close(self) -> None:
+        if self._handle and self.gpu._handle:
+            self.gpu._lib.gpurs_comm_free(self._handle)
+        self._handle = None
 
 
 def matmul_allgather(stream: Stream, a: DeviceBuffer, b: DeviceBuffer, gathered: GatheredMatrix, shape, row_offset: int,

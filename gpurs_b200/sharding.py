@@ -36,3 +36,26 @@ def shard_table(m: int, world: int, align: int = TILE_ROWS) -> list[tuple[int, i
 def equal_shards(m: int, world: int, align: int = TILE_ROWS) -> bool:
     """True when every rank holds the same number of rows (what an in-place all-gather needs)."""
     return len({rows for _, rows in shard_table(m, world, align)}) == 1
+
+
+def broadcast_from_rank0(dist):
+    """An `exchange` for `Communicator` and friends built on a torch.distributed process group of any backend: returns
+    a function that hands rank 0's bytes to every rank."""
+
+    def exchange(payload):
+        box = [payload if dist.get_rank() == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    return exchange
+
+
+def allgather_objects(dist):
+    """An `exchange` for `GatheredMatrix`: every rank's bytes, in rank order, on every rank."""
+
+    def exchange(payload):
+        everyone = [None] * dist.get_world_size()
+        dist.all_gather_object(everyone, payload)
+        return everyone
+
+    return exchange

@@ -49,7 +49,8 @@ enum {
     GPURS_E_INVALID_ARGUMENT = 100009,   /* null handle / unknown enum value */
     GPURS_E_DEVICE_TIMEOUT = 100010,     /* a bounded device-side wait gave up (no reference counterpart:
                                             the reference's waits are unbounded) */
-    GPURS_E_DRIVER_UNAVAILABLE = 100011  /* libcuda could not be loaded */
+    GPURS_E_DRIVER_UNAVAILABLE = 100011, /* libcuda could not be loaded */
+    GPURS_E_COLLECTIVE = 100012          /* libnccl could not be loaded, or an NCCL call failed (its text is in gpurs_last_error) */
 };
 
 /* Element types.  The values of the first three match the TMA data-type codes the reference uses
@@ -105,6 +106,9 @@ int gpurs_download(gpurs_gpu *gpu, gpurs_device_ptr source, void *host, size_t b
 int gpurs_copy_to_device(gpurs_stream *stream, gpurs_device_ptr destination, const void *host, size_t bytes);
 int gpurs_copy_to_host(gpurs_stream *stream, void *host, gpurs_device_ptr source, size_t bytes);
 int gpurs_fill_u8(gpurs_stream *stream, gpurs_device_ptr destination, uint8_t value, size_t bytes);
+/* Free and total device memory in bytes as the driver reports them now (`cuMemGetInfo`; the reference exposes the
+ * same pair through `Gpu::memory_info`, crates/driver/src/memory.rs).  Does not wait for the device. */
+int gpurs_memory_info(gpurs_gpu *gpu, size_t *free_bytes, size_t *total_bytes);
 /* Page-locked host memory (`PinnedBuffer`, crates/gpurs/src/host/memory/pinned.rs). */
 int gpurs_host_alloc(gpurs_gpu *gpu, size_t bytes, void **out);
 int gpurs_host_free(gpurs_gpu *gpu, void *pointer);
@@ -253,7 +257,32 @@ typedef struct gpurs_matmul_desc {
      * per-row quantiser of C needs without reading C again.  Dense tile kernels, float outputs, single products. */
     gpurs_device_ptr row_absmax;
     int32_t scale_kind;              /* what scale_a / scale_b hold: GPURS_SCALES_* */
+    /* 1: the product is ADDED to what C holds instead of replacing it, with atomic adds, so that several products (for
+     * instance the parts of a depth split across launches or streams) may add into one C at once: `accumulate` of the
+     * reference's f32 output matrix (`red.global.add.f32`, crates/gpurs/src/gpu/tensor/output/reduction.rs:157-202).  fp32
+     * output only; single products on the tile kernels.  The order of the additions, and so the last bits, is not fixed. */
+    int32_t accumulate;
+    /* The rest of the accumulator-tile algebra of the reference (`add_rows`, and `add` of another tile,
+     * crates/gpurs/src/gpu/tensor/warp/accumulators.rs:82-105), applied after the bias, each step rounded on its own:
+     *     C = acc * alpha * row_scale[row] * column_scale[column] + bias[column] + row_bias[row] + beta * residual[row, column] */
+    gpurs_device_ptr row_bias;       /* optional fp32 [m]: one value added to every element of its row */
+    gpurs_device_ptr residual;       /* optional m x n matrix of C's element type: a skip connection, or beta * C_in when it is C
+                                        itself (then ldr must equal ldc); otherwise it must not overlap C.  Single products. */
+    uint64_t ldr;                    /* its row pitch in elements; 0 = n */
+    float beta;                      /* factor of the residual; 0 is read as 1 */
     int32_t reserved;                /* 0 */
+    /* `reduce_rows` with + (warp/accumulators.rs:112-128): fp32 [m], zeroed by the caller; the sum of each row of the
+     * result (after the algebra, before the output rounding) is added in with one atomic add per row and tile, so the
+     * last bits depend on the order the tiles finish in.  Dense tile kernels, float outputs, single products. */
+    gpurs_device_ptr row_sum;
+    /* An explicit launch geometry, as `stream.launch(LaunchConfig)` gives a launcher in the reference
+     * (crates/gpurs/src/host/stream.rs:28-52,142-148), or NULL to let the library pick.  The kernels are persistent, so the
+     * grid says how many CTAs walk the tiles: grid[0] * grid[1] * grid[2] CTAs (a multiple of the cluster size, at most one
+     * per multiprocessor is useful).  cluster[0] 1 or 2 picks one-CTA or CTA-pair tiles when `algorithm` is AUTO and must
+     * agree with it otherwise (0 = no say).  block[0], if not 0, must be the thread count of the kernel that will run, and
+     * shared_bytes, if not 0, at least what it needs: a mismatch is GPURS_E_INVALID_VIEW and nothing is launched.
+     * Tile kernels only (the split-K decode kernel sizes its own grid). */
+    const gpurs_launch_config *launch;
 } gpurs_matmul_desc;
 
 /* The launcher behind `matmul(&stream, &a, &b, &mut c, ...)`.  It validates like the reference's
@@ -323,8 +352,9 @@ int gpurs_compress_24(gpurs_stream *stream, int element_type, uint64_t m, uint64
  * allocation or a free implies.  The scratch for the split operands is a fixed array inside the library
  * image instead of an allocation, so (m + n) * 3 * k * 4 bytes (the A part rounded up to 256) must fit
  * GPURS_STATIC_SCRATCH_BYTES, else GPURS_E_SIZE_OVERFLOW.  All calls on a device share that array: calls
- * ordered by one stream are safe, calls that may overlap on the GPU race.  The first call on a device
- * resolves the array's address and loads the kernels; make it before starting any stream capture. */
+ * ordered by one stream are safe, calls that may overlap on the GPU race.  Every call looks the array's
+ * device address up afresh (a host-side lookup, nothing is allocated), so closing and reopening a handle
+ * is safe; the first call on a device also loads the kernels: make it before starting any stream capture. */
 int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_t n, uint64_t k, gpurs_device_ptr a,
                             gpurs_device_ptr b, gpurs_device_ptr c);
 
@@ -368,6 +398,25 @@ typedef struct gpurs_gather_desc {
 
 int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_desc *desc, const gpurs_gather_desc *gather,
                            gpurs_device_ptr a, gpurs_device_ptr b);
+
+/* ---- the optional all-gather of C as a plain collective ------------------------------------------------ */
+
+/* No counterpart in the reference (one device, no collective: crates/gpurs/src/lib.rs:7-9).  After an M-sharded product
+ * every GPU of the box holds its block of rows of C; these three calls make every GPU hold all of C with one NCCL
+ * all-gather over NVLink, the baseline that gpurs_matmul_allgather (above) fuses into the product.  One communicator per
+ * GPU and process (or thread).  How the 128-byte id travels from the rank that made it to the others is the host's
+ * business (a file, a socket, any process group): gpurs_comm_unique_id on one rank, the same bytes to gpurs_comm_init on
+ * all `world` ranks, which meet inside that call.
+ * gpurs_comm_allgather is in place and stream-ordered: `full` is this rank's buffer of world * block_bytes bytes whose
+ * block [rank * block_bytes, (rank + 1) * block_bytes) already holds this rank's rows (the product was written there);
+ * when the call has completed on `stream`, block r holds rank r's rows.  Every rank must make the call, with the same
+ * block_bytes.  Free the communicator on every rank after the last collective has completed. */
+#define GPURS_COMM_ID_BYTES 128
+typedef struct gpurs_comm gpurs_comm;
+int gpurs_comm_unique_id(uint8_t id[GPURS_COMM_ID_BYTES]);
+int gpurs_comm_init(gpurs_gpu *gpu, const uint8_t id[GPURS_COMM_ID_BYTES], uint32_t world, uint32_t rank, gpurs_comm **out);
+int gpurs_comm_allgather(gpurs_comm *comm, gpurs_stream *stream, gpurs_device_ptr full, uint64_t block_bytes);
+void gpurs_comm_free(gpurs_comm *comm);
 
 /* Reads and clears the device status word: [0] code (0 = none), [1] block, [2] tile, [3] K-block of the
  * first bounded wait that gave up.  Synchronises the device. */

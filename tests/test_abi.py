@@ -38,14 +38,16 @@ def test_struct_layouts_match_a_c_compiler(tmp_path):
     source = tmp_path / "layout.c"
     source.write_text(
         '#include "gpurs_b200.h"\n#include <stdio.h>\n#include <stddef.h>\n'
-        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(gpurs_matmul_desc), offsetof(gpurs_matmul_desc, m),"
+        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(gpurs_matmul_desc), offsetof(gpurs_matmul_desc, m),"
         " offsetof(gpurs_matmul_desc, lda), offsetof(gpurs_matmul_desc, algorithm), offsetof(gpurs_matmul_desc, scale_a),"
-        " sizeof(gpurs_launch_config), offsetof(gpurs_launch_config, cluster));return 0;}\n")
+        " sizeof(gpurs_launch_config), offsetof(gpurs_launch_config, cluster), offsetof(gpurs_matmul_desc, accumulate),"
+        " offsetof(gpurs_matmul_desc, beta), offsetof(gpurs_matmul_desc, row_sum), offsetof(gpurs_matmul_desc, launch));return 0;}\n")
     binary = tmp_path / "layout"
     subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(source), "-o", str(binary)], check=True)
     sizes = [int(x) for x in subprocess.run([str(binary)], capture_output=True, text=True, check=True).stdout.split()]
     D, L = _ffi.MatmulDesc, _ffi.LaunchConfigStruct
-    assert sizes == [C.sizeof(D), D.m.offset, D.lda.offset, D.algorithm.offset, D.scale_a.offset, C.sizeof(L), L.cluster.offset]
+    assert sizes == [C.sizeof(D), D.m.offset, D.lda.offset, D.algorithm.offset, D.scale_a.offset, C.sizeof(L), L.cluster.offset,
+                     D.accumulate.offset, D.beta.offset, D.row_sum.offset, D.launch.offset]
 
 
 def test_kernel_image_is_embedded():

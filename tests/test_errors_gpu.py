@@ -34,6 +34,11 @@ def test_rejections_happen_before_any_launch(gpu, stream):
     assert code_of(lambda: G.matmul(stream, a, b, c, [128, 256, 64], G.MatmulOptions(algorithm=9))) == _ffi.E_INVALID_ARGUMENT
     alias = gpu.import_allocation(a.pointer, 128 * 16, G.F32)  # the output lies over A
     assert code_of(lambda: G.matmul(stream, a, b, alias, [16, 128, 64], G.MatmulOptions(lda=64))) == _ffi.E_ALIASING
+    # fp32 operands at full precision are multiplied over a depth of 3k, which the kernels index with 32 bits: refused
+    # before the split kernels are enqueued (slice lengths left unchecked, so the depth check is what answers)
+    deep = _ffi.MatmulDesc()
+    deep.a_type, deep.c_type, deep.m, deep.n, deep.k = G.F32, G.F32, 1, 1, (0x7FFFFFFF // 3 // 4 + 1) * 4
+    assert gpu._lib.gpurs_matmul(stream._handle, C.byref(deep), 1 << 40, 2 << 40, 3 << 40) == _ffi.E_SIZE_OVERFLOW
     assert gpu.launches == before
     error = pytest.raises(G.GpursError, lambda: G.matmul(stream, a, b, alias, [16, 128, 64])).value
     assert error.operation == "gpurs_matmul" and "overlaps" in error.description
@@ -75,12 +80,17 @@ def test_tensor_map_encode_checks(gpu):
 
 
 class _Params(C.Structure):
-    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp (128 bytes)
+    # gemm::Params of gpurs_b200/csrc/kernels/gemm_params.hpp (192 bytes)
     _fields_ = [("c", C.c_uint64), ("ldc", C.c_longlong), ("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("tiles_m", C.c_int),
                 ("tiles_n", C.c_int), ("raster_rows", C.c_int), ("vector_stores", C.c_int), ("b_row_major", C.c_int), ("status", C.c_uint64),
                 ("scale_a", C.c_uint64), ("scale_b", C.c_uint64), ("bias", C.c_uint64), ("l2_policy", C.c_int), ("batches", C.c_int),
                 ("row_scale", C.c_uint64), ("column_scale", C.c_uint64), ("alpha", C.c_float), ("scaled_by_alpha", C.c_int),
-                ("batch_stride_c", C.c_longlong), ("row_absmax", C.c_uint64)]
+                ("batch_stride_c", C.c_longlong), ("row_absmax", C.c_uint64), ("partials", C.c_uint64), ("split_counters", C.c_uint64),
+                ("max_contributors", C.c_int), ("split_tiles", C.c_int), ("row_bias", C.c_uint64), ("residual", C.c_uint64),
+                ("ldr", C.c_longlong), ("beta", C.c_float), ("accumulate", C.c_int), ("row_sum", C.c_uint64)]
+
+
+assert C.sizeof(_Params) == 192
 
 
 class _TensorMap(C.Structure):

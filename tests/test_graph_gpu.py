@@ -96,6 +96,37 @@ def test_scratch_cannot_grow_inside_a_capture():
     assert c.download().any()
 
 
+def test_a_graph_keeps_its_scratch_when_the_handle_outgrows_it():
+    """A recording holds the address of the scratch block it was made with.  A later, larger product makes the handle
+    take a bigger block; the old one must stay allocated for the graph, whose replays still compute the recorded product,
+    and is released with the graph."""
+    gpu = G.Gpu(0)
+    try:
+        stream = gpu.stream()
+        m, n, k = 136, 200, 132
+        a_bits, b_bits = make_operands("f32", m, n, k)
+        expected = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k)        # warm-up: the first, small scratch block
+        a, b = gpu.upload(a_bits, G.F32), gpu.upload(b_bits, G.F32)
+        c = gpu.zeros(G.F32, m * n)
+        graph = stream.capture(lambda s: G.matmul(s, a, b, c, [m, n, k]))
+        executable = graph.instantiate()
+        big = 1024                                                                       # 24 MiB of split copies: the block grows
+        big_a, big_b = make_operands("f32", big, big, big, seed=9)
+        big_expected = run_matmul(gpu, stream, "f32", "f32", big_a, big_b, big, big, big)
+        for _ in range(2):
+            gpu._lib.gpurs_fill_u8(stream._handle, c.pointer, 0x7F, c.nbytes)
+            executable.launch(stream)
+            stream.synchronize()
+            assert np.array_equal(c.download(), expected)
+            assert np.array_equal(run_matmul(gpu, stream, "f32", "f32", big_a, big_b, big, big, big), big_expected)
+        del executable, graph            # the old block goes with the graph
+        assert np.array_equal(run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k), expected)
+        assert gpu.status() == [0, 0, 0, 0]
+        del a, b, c
+    finally:
+        gpu.close()
+
+
 def test_graph_of_another_handle_is_rejected(gpu, stream):
     other = G.Gpu(0)
     c = gpu.zeros(G.F32, 64)

@@ -250,6 +250,22 @@ def test_row_major_right_operand_with_pitch(gpu, stream):
     got = decode_output(run_matmul(gpu, stream, "bf16", "f32", a, padded, m, n, k, G.ALGO_AUTO, b_row_major=True, ldb=ldb), "f32")
     assert relative_error(got.reshape(m, n), O.matmul_rows(O.FMT_BF16, a, b, n, k, np.arange(m))) <= 1e-3
     fa, fb = make_operands("f32", m, n, k)
-    with pytest.raises(G.GpursError) as raised:           # 32-bit operands are read n x k only
-        run_matmul(gpu, stream, "f32", "f32", fa, np.ascontiguousarray(fb.reshape(n, k).T).reshape(-1), m, n, k, G.ALGO_AUTO, b_row_major=True)
+    with pytest.raises(G.GpursError) as raised:           # one TF32 pass reads 32-bit operands n x k only
+        run_matmul(gpu, stream, "f32", "f32", fa, np.ascontiguousarray(fb.reshape(n, k).T).reshape(-1), m, n, k, G.ALGO_AUTO, b_row_major=True,
+                   precision=G.PRECISION_TF32)
     assert raised.value.code == 100009
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (200, 301, 132), (129, 64, 2048)])
+def test_f32_row_major_right_operand(gpu, stream, shape):
+    """The f32 configuration as it is stated, row-major C = A * B: B is k x n.  The full-precision path copies (splits) its
+    operands anyway, and writes the copy of a k x n operand transposed; same bits as the n x k call, 1e-4 against fp64."""
+    m, n, k = shape
+    a, b = make_operands("f32", m, n, k)
+    ldb = (n + 3) // 4 * 4                                # 16-byte row pitch
+    row_major = np.full(k * ldb, np.nan, np.float32)      # NaN in the padding columns: never read
+    row_major.reshape(k, ldb)[:, :n] = b.reshape(n, k).T
+    got = run_matmul(gpu, stream, "f32", "f32", a, row_major, m, n, k, G.ALGO_AUTO, b_row_major=True, ldb=ldb)
+    assert np.array_equal(got, run_matmul(gpu, stream, "f32", "f32", a, b, m, n, k))
+    rows = spread_rows(m)
+    assert relative_error(got.reshape(m, n)[rows].astype(np.float64), O.matmul_rows(O.FMT_F32, a, b, n, k, rows)) <= 1e-4

@@ -70,3 +70,42 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
     for worker in workers:
         output, _ = worker.communicate(timeout=240)
         assert worker.returncode == 0, output.decode()[-2000:]
+
+
+COMM_WORKER = r"""
+import sys
+sys.path.insert(0, sys.argv[1])
+import ctypes as C
+import torch.distributed as dist
+import gpurs_b200 as G
+from gpurs_b200 import _ffi
+from gpurs_b200.sharding import allgather_objects, broadcast_from_rank0
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+# what Communicator does before it touches a GPU: rank 0 makes the id through the C ABI, every rank receives the same bytes
+unique = broadcast_from_rank0(dist)(G.comm_unique_id() if rank == 0 else None)
+everyone = allgather_objects(dist)(unique)
+ok = len(unique) == _ffi.COMM_ID_BYTES and everyone[0] == everyone[1] == unique and any(unique)
+other = broadcast_from_rank0(dist)(G.comm_unique_id() if rank == 0 else None)
+ok = ok and other != unique                                    # every id is fresh
+library = _ffi.load()
+handle = C.c_void_p()
+raw = (C.c_uint8 * _ffi.COMM_ID_BYTES).from_buffer_copy(unique)
+ok = ok and library.gpurs_comm_init(None, raw, 2, rank, C.byref(handle)) == _ffi.E_INVALID_ARGUMENT and not handle.value
+ok = ok and library.gpurs_comm_allgather(None, None, 0, 0) == _ffi.E_INVALID_ARGUMENT
+dist.barrier(); dist.destroy_process_group()
+sys.exit(0 if ok else 1)
+"""
+
+
+def test_two_rank_gloo_communicator_id_exchange(tmp_path):
+    """The host half of the NCCL all-gather, on CPU: the id is made by one rank through the C ABI (no GPU is needed for
+    that), reaches the other through a gloo group, and the calls that need a GPU refuse null handles."""
+    script = tmp_path / "comm_worker.py"
+    script.write_text(COMM_WORKER)
+    port = str(29950 + os.getpid() % 40)
+    workers = [subprocess.Popen([sys.executable, str(script), str(ROOT), port, str(rank)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+               for rank in range(2)]
+    for worker in workers:
+        output, _ = worker.communicate(timeout=240)
+        assert worker.returncode == 0, output.decode()[-2000:]

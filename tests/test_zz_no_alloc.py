@@ -49,6 +49,69 @@ def test_static_entry_matches_the_allocating_entry_twice_in_a_row():
         gpu.close()
 
 
+def free_bytes(gpu):
+    free, total = C.c_size_t(), C.c_size_t()
+    assert gpu._lib.gpurs_memory_info(gpu._handle, C.byref(free), C.byref(total)) == 0
+    return free.value
+
+
+def test_static_entry_allocates_nothing():
+    """What the entry exists for: on a handle that has never run the allocating fp32 product, calls through the static
+    entry leave the device's free memory exactly where it was, and each call is two launches (split, product).  The
+    first call is the warm-up that loads the kernel image; the measurement starts after it."""
+    gpu = G.Gpu(0)
+    try:
+        stream = gpu.stream()
+        m, n, k = 512, 384, 640
+        a_host, b_host = O.fill_uniform_f32(m * k, 5), O.fill_uniform_f32(n * k, 6)
+        a, b, c = gpu.upload(a_host), gpu.upload(b_host), gpu.zeros(G.F32, m * n)
+        assert static_matmul(gpu, stream, a, b, c, m, n, k) == 0
+        stream.synchronize()
+        before, launches = free_bytes(gpu), gpu.launches
+        for _ in range(3):
+            assert static_matmul(gpu, stream, a, b, c, m, n, k) == 0
+        stream.synchronize()
+        assert free_bytes(gpu) == before, "a call through the static entry changed the device's free memory"
+        assert gpu.launches - launches == 6
+        rows = np.arange(0, m, 16)
+        got = c.download().reshape(m, n).astype(np.float64)
+        assert relative_error(got[rows], O.matmul_rows(O.FMT_F32, a_host, b_host, n, k, rows)) <= TOLERANCE
+        # the allocating entry, for contrast, takes its scratch from the device on its first call
+        regular = gpu.zeros(G.F32, m * n)
+        before = free_bytes(gpu)
+        G.matmul(stream, a, b, regular, [m, n, k])
+        stream.synchronize()
+        assert free_bytes(gpu) < before
+        assert relative_error(got, regular.download().reshape(m, n).astype(np.float64)) <= TOLERANCE
+    finally:
+        gpu.close()
+
+
+def test_static_entry_survives_closing_and_reopening_the_handle():
+    """The array's address is looked up at every call, under the handle that makes the call: a second handle opened after
+    the first was closed computes the same product."""
+    m, n, k = 256, 320, 512
+    a_host, b_host = O.fill_uniform_f32(m * k, 31), O.fill_uniform_f32(n * k, 32)
+    results = []
+    for _ in range(2):
+        gpu = G.Gpu(0)
+        try:
+            stream = gpu.stream()
+            a, b = gpu.upload(a_host), gpu.upload(b_host)
+            c_static, c_regular = gpu.zeros(G.F32, m * n), gpu.zeros(G.F32, m * n)
+            assert static_matmul(gpu, stream, a, b, c_static, m, n, k) == 0
+            G.matmul(stream, a, b, c_regular, [m, n, k])
+            stream.synchronize()
+            got = c_static.download()
+            assert relative_error(got.astype(np.float64), c_regular.download().astype(np.float64)) <= TOLERANCE
+            assert gpu.status() == [0, 0, 0, 0]
+            results.append(got)
+            del a, b, c_static, c_regular
+        finally:
+            gpu.close()
+    assert np.array_equal(results[0], results[1])
+
+
 def test_static_entry_rejects_what_does_not_fit():
     gpu = G.Gpu(0)
     try:
@@ -63,6 +126,9 @@ def test_static_entry_rejects_what_does_not_fit():
         assert static_matmul(gpu, stream, small, small, small, 64, 64, 62) == _ffi.E_INVALID_VIEW      # rows are not 16-byte multiples
         assert static_matmul(gpu, stream, small, small, small, 32, 32, 64) == _ffi.E_ALIASING          # output over an operand
         assert gpu._lib.gpurs_matmul_f32_static(None, 1, 1, 4, 0, 0, 0) == _ffi.E_INVALID_ARGUMENT
+        # sizes at the edge of what 64-bit arithmetic on the split sizes holds are size errors, not wrapped sums
+        assert static_matmul(gpu, stream, small, small, small, 0x7fffffff, 0x7fffffff, 0x7fffffff // 3 // 4 * 4) == _ffi.E_SIZE_OVERFLOW
+        assert static_matmul(gpu, stream, small, small, small, 64, 64, 0x7fffffff // 3 + 1) == _ffi.E_SIZE_OVERFLOW
         assert gpu.launches == before
         assert _ffi.STATIC_SCRATCH_BYTES == 32 << 20
     finally:
