@@ -230,3 +230,19 @@ def reference_sample_indices(rows: int, columns: int) -> np.ndarray:
 
 def threads() -> int:
     return int(lib().gpurs_oracle_threads())
+
+
+def set_threads(count: int) -> int:
+    """Run the loops on `count` threads from now on (whatever OMP_NUM_THREADS said at start-up); returns the new count."""
+    lib().gpurs_oracle_set_threads(C.c_int(int(count)))
+    return threads()
+
+
+def usable_cores() -> int:
+    """Cores this process may run on (its affinity mask), which is what a timed CPU baseline should use."""
+    import os
+
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1

@@ -390,7 +390,9 @@ API void gpurs_oracle_matmul_rows_i8(const int8_t *left, const int8_t *right, si
 #ifdef _OPENMP
 #include <omp.h>
 API int gpurs_oracle_threads(void) { return omp_get_max_threads(); }
-API void gpurs_oracle_set_threads(int n) { omp_set_num_threads(n); }
+/* Sets it (a launcher such as torch.distributed.run exports OMP_NUM_THREADS=1 to its children; the timed CPU baseline
+ * is meant to use every core the process may run on). */
+API void gpurs_oracle_set_threads(int count) { omp_set_num_threads(count > 0 ? count : 1); }
 #else
 API int gpurs_oracle_threads(void) { return 1; }
 API void gpurs_oracle_set_threads(int n) { (void)n; }
