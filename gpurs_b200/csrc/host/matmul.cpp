@@ -355,6 +355,71 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
+// The block-scaled FP8 product on CTA pairs (kernels/gemm_blockscaled_tcgen05.cuh): 256 x 256 tiles, every K-block issued as two
+// products of 128 columns.  Each CTA loads its 128 rows of A and, of each 128-column half of the B tile, its 64 rows.
+int launch_blockscaled(gpurs_stream *stream, const launcher::Gemm &g) {
+    gpurs_gpu *gpu = stream->gpu;
+    const uint32_t shared_bytes = std::max(uint32_t(gemm::BLOCKSCALED_SHARED), g.launch ? g.launch->shared_bytes : 0u);
+    uint64_t explicit_grid = 0;
+    int result = explicit_ctas("gpurs_matmul", g.launch, 2, uint32_t(gemm::SCALED_THREADS), uint32_t(gemm::BLOCKSCALED_SHARED), explicit_grid);
+    if (result != GPURS_OK) return result;
+    char name[96];
+    std::snprintf(name, sizeof name, "%s_cg2", g.stem);
+    gpurs_kernel *kernel = nullptr;
+    result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t ob = uint64_t(g.output_bytes);
+    alignas(64) CUtensorMap map_a, map_b, map_c;
+    const uint64_t dims_a[2] = {g.k, g.m}, dims_b[2] = {g.k, g.n}, stride_a[1] = {g.lda}, stride_b[1] = {g.ldb};
+    const uint32_t box_a[2] = {128, uint32_t(gemm::BLOCK_M)}, box_b[2] = {128, 64};
+    result = gpurs_tensor_map_encode(gpu, &map_a, GPURS_E4M3, 2, g.a, dims_a, stride_a, box_a, 3, 3);
+    if (result != GPURS_OK) return result;
+    result = gpurs_tensor_map_encode(gpu, &map_b, GPURS_E4M3, 2, g.b, dims_b, stride_b, box_b, 3, 3);
+    if (result != GPURS_OK) return result;
+    gemm::Params params;
+    std::memset(&params, 0, sizeof params);
+    params.c = reinterpret_cast<void *>(g.c);
+    params.ldc = (long long)g.ldc;
+    params.m = int(g.m), params.n = int(g.n), params.k = int(g.k);
+    params.tiles_m = int((g.m + 255) / 256), params.tiles_n = int((g.n + 255) / 256);
+    params.raster_rows = g.raster_rows > 0 ? g.raster_rows : 8;
+    params.vector_stores = (g.c % 16 == 0 && (g.ldc * ob) % 16 == 0) ? 1 : 0;
+    params.status = reinterpret_cast<unsigned int *>(gpu->status);
+    params.scale_a = reinterpret_cast<const float *>(g.scale_a);
+    params.scale_b = reinterpret_cast<const float *>(g.scale_b);
+    params.bias = reinterpret_cast<const float *>(g.bias);
+    params.row_scale = reinterpret_cast<const float *>(g.row_scale);
+    params.column_scale = reinterpret_cast<const float *>(g.column_scale);
+    params.alpha = g.alpha;
+    params.scaled_by_alpha = (g.alpha != 0.0f && g.alpha != 1.0f) ? 1 : 0;
+    params.row_bias = reinterpret_cast<const float *>(g.row_bias);
+    params.residual = reinterpret_cast<const void *>(g.residual);
+    params.ldr = (long long)g.ldr;
+    params.beta = g.beta;
+    std::memset(&map_c, 0, sizeof map_c);
+    if (params.vector_stores == 1) {
+        const uint64_t dims_c[2] = {g.n, g.m}, stride_c[1] = {g.ldc * ob};
+        const uint32_t box_c[2] = {uint32_t(gemm::ROW_BYTES / g.output_bytes), 32};
+        result = gpurs_tensor_map_encode(gpu, &map_c, g.output_type, 2, g.c, dims_c, stride_c, box_c, 3, 3);
+        if (result != GPURS_OK) return result;
+    }
+    const uint64_t tiles = uint64_t(params.tiles_m) * uint64_t(params.tiles_n);
+    if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
+    const uint64_t ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
+    const uint64_t pairs = std::min(std::max<uint64_t>(1, ctas / 2), tiles);
+    // the kernel numbers the 128-column products of one CTA pair with 32 bits
+    if (((tiles + pairs - 1) / pairs) * ((g.k + 127) / 128) * 2 > 0xffffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many K-blocks per CTA pair");
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(pairs * 2);
+    config.block[0] = uint32_t(gemm::SCALED_THREADS);
+    config.shared_bytes = shared_bytes;
+    config.cluster[0] = 2;
+    config.cluster[1] = config.cluster[2] = 1;
+    void *arguments[4] = {&map_a, &map_b, &map_c, &params};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
 // Host mirror of gemm::SkinnyParams (kernels/gemm_skinny_tcgen05.cuh).
 struct SkinnyParams {
     float *c;
@@ -583,8 +648,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES | GPURS_ALGO_SPLIT_LAST_ROUND)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
         return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
-    // Kernels that promote every K-block to registers hand an accumulator back and forth once per block;
-    // across a CTA pair that hand-off costs more than the pair saves, so they default to one-CTA tiles.
+    // Kernels that promote K-blocks to registers hand an accumulator back and forth between the tensor core and the CUDA cores.
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
     const bool skinny_possible = m <= uint64_t(gemm::SKINNY_MAX_ROWS) && (desc->a_type == GPURS_F16 || desc->a_type == GPURS_BF16) &&
@@ -622,7 +686,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (group == GPURS_ALGO_AUTO && desc->launch && (desc->launch->cluster[0] == 1 || desc->launch->cluster[0] == 2) && !promoted)
         group = desc->launch->cluster[0] == 2 ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group == GPURS_ALGO_AUTO && skinny_possible && !desc->launch) group = GPURS_ALGO_SKINNY;
-    if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
+    // The fp32 (three-pass TF32) product stays on one-CTA tiles; the block-scaled FP8 product has a CTA-pair kernel of its own
+    // (four accumulators in flight) that outruns the one-CTA one wherever a pair tile has two row blocks to work on.
+    if (group == GPURS_ALGO_AUTO) group = (m > 128 && (!promoted || (desc->scale_a != 0 && !desc->accumulate))) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR && group != GPURS_ALGO_SKINNY)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     if (desc->bias && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "a bias is for floating-point outputs");
@@ -708,6 +774,11 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         gemm.scale_a = desc->scale_a;
         gemm.scale_b = desc->scale_b;
         gemm.threads = gemm::SCALED_THREADS;
+        if (gemm.cta_group == 2 && !gemm.accumulate) {
+            // CTA pairs: the kernel that keeps four accumulators in flight
+            gemm.stem = desc->c_type == GPURS_BF16 ? "gpurs_gemm_e4m3_blockscaled_bf16" : "gpurs_gemm_e4m3_blockscaled_f32";
+            return launch_blockscaled(stream, gemm);
+        }
     }
 
     if (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT) {

@@ -165,9 +165,8 @@ __device__ __forceinline__ void gemm_grouped_body(const CUtensorMap *map_w, cons
         const int quadrant = warp % 4;
         int acc = 0;
         uint32_t acc_phase = 0;
-        Params out;                       // what store_chunk reads: the output, clipped to this expert's rows
-        out.c = p.c, out.ldc = p.ldc, out.n = p.n, out.vector_stores = p.vector_stores, out.bias = nullptr;
-        out.row_scale = out.column_scale = nullptr, out.scaled_by_alpha = 0;
+        Params out{};                     // what store_chunk reads: the output, clipped to this expert's rows; no algebra (all zero)
+        out.c = p.c, out.ldc = p.ldc, out.n = p.n, out.vector_stores = p.vector_stores;
         for (int tile = blockIdx.x; grouped_tile(p, tile, expert, first_row, end_row, tile_n); tile += gridDim.x) {
             const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) {

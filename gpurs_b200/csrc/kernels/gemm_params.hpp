@@ -75,6 +75,10 @@ constexpr int BLOCK_N = 256;       // columns per tile
 constexpr int STAGES_SINGLE = 4;   // pipeline depth of the one-CTA kernels (48 KiB per stage)
 constexpr int STAGES_PAIR = 6;     // pipeline depth of the CTA-pair kernels (32 KiB per stage and CTA)
 
+// Dynamic shared memory of the CTA-pair block-scaled FP8 entries (gemm_blockscaled_tcgen05.cuh): 6 stages of 32 KiB, 24 barriers,
+// one 4 KiB output box per promotion warp, alignment slack.
+constexpr int BLOCKSCALED_SHARED = ((6 * 32768 + (2 * 6 + 12) * 8 + 8 + 16 + 1023) / 1024) * 1024 + 8 * 32 * 128 + 1024;
+
 template <int BLOCK_N, int CTA_GROUP, int STAGES>
 struct SharedLayout {
     static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;

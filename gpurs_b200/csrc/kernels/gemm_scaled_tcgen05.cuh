@@ -44,6 +44,11 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
     static_assert(!SPLIT, "the two-halves variant was measured slower and is not wired into the loops below");
     constexpr int MMA_N = BN / HALVES;
     constexpr uint32_t IDESC = instruction_descriptor(1, ELEMENT_FORMAT, BLOCK_M * CTA_GROUP, MMA_N);   // f32 accumulate
+    // A tcgen05.commit costs the issuing thread about 250 cycles, half of what the tensor core needs for a K-block.  Where an
+    // accumulator holds exactly one K-block (the scaled product on one CTA), its completion is also the moment the K-block's
+    // shared-memory stage is free: a promotion warp that has seen the accumulator complete hands the stage back to the
+    // producer, and the MMA thread issues one commit per K-block instead of two.
+    constexpr bool PROMOTION_FREES_STAGES = SCALED && CTA_GROUP == 1;
     constexpr int ELEMENT_BYTES = KIND == ptx::KIND_F16 ? 2 : (KIND == ptx::KIND_TF32 ? 4 : 1);
     constexpr int BLOCK_K = ROW_BYTES / ELEMENT_BYTES;   // elements of K per stage (128 for FP8: one scale block)
 
@@ -143,6 +148,8 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
+            const uint64_t a_desc0 = ptx::smem_descriptor_k_major_sw128(stage_a(0)), b_desc0 = ptx::smem_descriptor_k_major_sw128(stage_b(0));
+            constexpr uint64_t STAGE_STEP = uint64_t(L::STAGE_BYTES >> 4);
             for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
                 for (int first = 0; first < k_blocks && ok; first += PERIOD) {
                     // one accumulator takes PERIOD K-blocks, then goes to the promotion warps
@@ -162,13 +169,13 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                             break;
                         }
                         ptx::tcgen05_fence_after();
-                        const uint64_t a_desc = ptx::smem_descriptor_k_major_sw128(stage_a(stage));
-                        const uint64_t b_desc = ptx::smem_descriptor_k_major_sw128(stage_b(stage));
+                        const uint64_t a_desc = a_desc0 + uint64_t(stage) * STAGE_STEP, b_desc = b_desc0 + uint64_t(stage) * STAGE_STEP;
+                        ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc, b_desc, IDESC, uint32_t(kb != first));
 #pragma unroll
-                        for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
-                            ptx::tcgen05_mma<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
-                                                              b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC, uint32_t(kb != first || j != 0));
-                        if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                        for (int j = 1; j < ROW_BYTES / MMA_K_BYTES; j++)
+                            ptx::tcgen05_mma_accumulate<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j * (MMA_K_BYTES >> 4)), IDESC);
+                        if constexpr (PROMOTION_FREES_STAGES) {}
+                        else if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
                         else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
@@ -188,6 +195,7 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
         const int scale_pitch = k_blocks;
         int acc = 0;
         uint32_t acc_phase = 0;
+        int release_stage = 0;
         bool ok = true;
         for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
             int tile_m, tile_n;
@@ -200,10 +208,15 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
 #pragma unroll
             for (int i = 0; i < SCALE_BLOCK; i++) sums[i] = 0.0f;
             float scale = SCALED ? __ldg(row_scales) * __ldg(block_scales) : 1.0f;
+            // Scales are fetched two blocks ahead and multiplied one block ahead: a warp issues in order, and a product placed
+            // right behind its loads would hold the warp for the whole trip to L2.
+            float row_part = SCALED ? __ldg(row_scales + min(1, k_blocks - 1)) : 1.0f, block_part = SCALED ? __ldg(block_scales + min(1, k_blocks - 1)) : 1.0f;
             for (int kb = 0; kb < k_blocks; kb += PERIOD) {
-                // fetch the next block's scale while waiting for this block's products
-                const int next = min(kb + PERIOD, k_blocks - 1);
-                const float next_scale = SCALED ? __ldg(row_scales + next) * __ldg(block_scales + next) : 1.0f;
+                const float next_scale = row_part * block_part;
+                if constexpr (SCALED) {
+                    const int ahead = min(kb + 2, k_blocks - 1);
+                    row_part = __ldg(row_scales + ahead), block_part = __ldg(block_scales + ahead);
+                }
                 const int slot = acc * 2 + (SPLIT ? half : 0);
                 const bool ready = ptx::mbarrier_wait(acc_full_bar(slot), acc_phase, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) {
@@ -212,6 +225,11 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                     break;
                 }
                 ptx::tcgen05_fence_after();
+                if constexpr (PROMOTION_FREES_STAGES) {
+                    // the K-block's products are complete: its stage goes back to the producer
+                    if (epilogue_warp == 0 && lane == 0) ptx::mbarrier_arrive(empty_bar(release_stage));
+                    if (++release_stage == STAGES) release_stage = 0;
+                }
                 const uint32_t address = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN + uint32_t(half * SCALE_BLOCK);
 #pragma unroll
                 for (int pair = 0; pair < SCALE_BLOCK / 64; pair++) {

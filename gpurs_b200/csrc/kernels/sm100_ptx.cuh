@@ -70,6 +70,14 @@ __device__ __forceinline__ void mbarrier_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// The same arrive without release semantics.  A release at cluster scope makes the arriving thread wait for every
+// memory operation it still has in flight (global loads included) before the arrive is performed, which costs about a
+// thousand cycles per hand-off; a thread that hands back TENSOR memory it has finished reading (tcgen05.wait::ld has
+// returned, tcgen05.fence::before_thread_sync executed) publishes nothing through ordinary memory and needs no release.
+__device__ __forceinline__ void mbarrier_arrive_cluster_relaxed(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
 __device__ __forceinline__ void mbarrier_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -214,6 +222,28 @@ __device__ __forceinline__ void tcgen05_mma(uint32_t d_tmem, uint64_t a_desc, ui
 #undef GPURS_MMA
 }
 
+// D[tmem] += A[smem] * B[smem]: the accumulating form with its predicate fixed, so that the issuing thread spends no
+// instruction on it.
+template <int KIND, int CTA_GROUP>
+__device__ __forceinline__ void tcgen05_mma_accumulate(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+#define GPURS_MMA(KINDSTR, GROUPSTR)                                                                      \
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\t"                                        \
+                 "tcgen05.mma.cta_group::" GROUPSTR ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t}"          \
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc) : "memory")
+    if constexpr (CTA_GROUP == 1) {
+        if constexpr (KIND == KIND_F16) GPURS_MMA("f16", "1");
+        else if constexpr (KIND == KIND_TF32) GPURS_MMA("tf32", "1");
+        else if constexpr (KIND == KIND_I8) GPURS_MMA("i8", "1");
+        else GPURS_MMA("f8f6f4", "1");
+    } else {
+        if constexpr (KIND == KIND_F16) GPURS_MMA("f16", "2");
+        else if constexpr (KIND == KIND_TF32) GPURS_MMA("tf32", "2");
+        else if constexpr (KIND == KIND_I8) GPURS_MMA("i8", "2");
+        else GPURS_MMA("f8f6f4", "2");
+    }
+#undef GPURS_MMA
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: lane i of the warp receives columns [c, c+32) of
 // TMEM lane (base lane + i).
 __device__ __forceinline__ void tmem_load_32x32(uint32_t address, uint32_t (&r)[32]) {
@@ -295,6 +325,21 @@ __device__ __forceinline__ void registers_decrease() { asm volatile("setmaxnreg.
 }  // namespace ptx
 
 namespace ptx {
+
+// Two fp32 values kept together in one 64-bit register, the operand form of the packed fp32 instructions.
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t low, uint32_t high) {
+    uint64_t packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "r"(low), "r"(high));
+    return packed;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t packed, uint32_t &low, uint32_t &high) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(low), "=r"(high) : "l"(packed));
+}
+// sums += values * scales, lane by lane, on operands that already are pairs: no packing or unpacking around the instruction
+// (with sums held as pairs for a whole K loop, the moves that fma2 below spends around every instruction disappear).
+__device__ __forceinline__ void fma_f32x2(uint64_t &sums, uint64_t values, uint64_t scales) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(sums) : "l"(values), "l"(scales));
+}
 
 // (sum0, sum1) += (value0, value1) * scale, both lanes in one packed instruction.
 __device__ __forceinline__ void fma2(float &sum0, float &sum1, uint32_t value0, uint32_t value1, float scale) {
