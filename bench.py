@@ -406,12 +406,50 @@ def run_leg(G, gpu, stream, dist, workload: str, m: int, rank: int, world: int, 
     error = max_over_ranks(dist, error if error is not None else 0.0) if error is not None else None
     tflops = whole_job_flops / (ms_per_step * 1e-3) / 1e12
     per_gpu = tflops / world
+    baseline = None
+    if workload == "f16_4096_example" and rank == 0:
+        baseline = reference_design_leg(gpu, stream, prepared)
     leg = {"value": tflops, "unit": "TFLOP/s" if kind != "i8" else "TOP/s", "ms_per_step": ms_per_step, "steps": LEG_STEPS, "warmup": LEG_WARMUP,
            "m_per_gpu": m, "n": n, "k": k, "dtype": kind, "output": out, "launches_per_step": int(launches),
            "roofline": roofline(workload, kind, per_gpu, prepared.flops, prepared.algorithmic_bytes),
            "max_error_vs_oracle": error, "tolerance": tolerance, "check": f"{prepared.check_rows} complete output rows against the CPU oracle, |d| / max(|ref|, 1)",
            "passed": (error is not None and error <= tolerance)}
+    if baseline is not None:
+        baseline["product_over_reference_design"] = baseline["ms_per_step"] / ms_per_step if baseline.get("ms_per_step") else None
+        leg["reference_design"] = baseline
     return leg, prepared
+
+
+def reference_design_leg(gpu, stream, prepared: Prepared) -> dict:
+    """The reference's own sm_100a kernel DESIGN (one CTA per 128 x 256 tile, one thread issuing copies and products, one
+    accumulator, 8-byte stores: examples/blackwell/examples/blackwell_matrix.rs:32-56), restated in CUDA under oracle/ as test
+    infrastructure and timed on the same GPU, same inputs, same protocol as the leg beside it.  Not the reference's binary
+    (that is Rust compiled by its own toolchain), and no part of the product."""
+    try:
+        import oracle as O
+        from oracle.reference_design import ReferenceDesign
+
+        design = ReferenceDesign(gpu)
+    except Exception as error:      # the image is built only where nvcc is installed
+        return {"unavailable": repr(error)}
+    G = prepared.G
+    m, n, k = prepared.shape
+    c = gpu.allocate(G.F32, m * n)
+    launch = design.prepare(prepared.a, prepared.b, c, m, n, k)
+    for _ in range(LEG_WARMUP):
+        design.launch(stream, launch)
+    stream.synchronize()
+    start = stream.record_timed()
+    for _ in range(LEG_STEPS):
+        design.launch(stream, launch)
+    end = stream.record_timed()
+    stream.synchronize()
+    ms_per_step = start.elapsed_ms(end) / LEG_STEPS
+    rows = np.unique(np.linspace(0, m - 1, 4).astype(np.int64))
+    exact = bool(np.array_equal(c.download().reshape(m, n)[rows].astype(np.float64), O.matmul_rows(prepared.fmt, prepared.a_host, prepared.b_host, n, k, rows)))
+    return {"ms_per_step": ms_per_step, "value": prepared.flops / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s", "bit_exact_vs_oracle": exact,
+            "status": [int(x) for x in design.status.download()],
+            "what": "CUDA restatement of the reference example's kernel design (128 x 256 x 64 tiles, 4-stage ring, single issuing thread, one accumulator), bounded waits"}
 
 
 def gather_leg(G, gpu, stream, dist, prepared: Prepared, rank: int, world: int, steps: int) -> dict:
