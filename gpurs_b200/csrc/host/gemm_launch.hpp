@@ -28,6 +28,7 @@ struct Gemm {
     const gpurs_launch_config *launch = nullptr; // the caller's explicit geometry, already checked for plausibility
     uint64_t batches = 1, stride_a = 0, stride_b = 0, stride_c = 0;   // batched entries: matrices and the elements between them
     bool whole_tiles = false;                    // never split the last round's tiles along K
+    int tile_width = 0;                          // 0 the launcher's choice, 512 wide tiles wherever possible, 256 never wide
     bool force_split = false;                    // split it whenever it is not full, whether or not that pays
     bool b_row_major = false;                    // B stored k x n
     int l2_policy = 0;                           // Params::l2_policy

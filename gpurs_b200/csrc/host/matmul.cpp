@@ -107,16 +107,35 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull;
     const int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
     gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
-    const bool stream_k = split_tiles > 0;
+    bool stream_k = split_tiles > 0;
+    // 256 x 512 tiles (kernels/gemm_wide_tcgen05.cuh): a quarter less operand traffic from L2 per flop, which is what bounds the
+    // 256 x 256 tiles.  Plain products on CTA pairs, n x k right operand, C rows on 16-byte boundaries.  By default they are used
+    // where the tile count fills the rounds of the grid nearly as well as the square tiles do (a round of wide tiles is twice as
+    // long; they are taken to be 7 % faster per flop when weighing rounds against each other).
+    const bool algebra_ = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
+                          g.row_sum || g.accumulate;
+    bool wide = false;
+    if (g.tile_width != 256 && !g.force_split && cta_group == 2 && g.metadata == 0 && g.threads == gemm::NUM_THREADS && !batched && !g.gather && !g.b_row_major &&
+        !algebra_ && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0) {
+        const uint64_t wide_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + 511) / 512);
+        const uint64_t pairs = std::max<uint64_t>(1, wanted_ctas / 2);
+        // measured on bf16 8192^3 (14 rounds of square tiles against 7 of wide ones): +8.6 %; on f16 4096^3, where the square tiles'
+        // last round is split along K (3.46 rounds) and wide tiles need 2 whole rounds for 1.73: -6 %
+        const double square_cost = stream_k ? double(all_tiles) / double(pairs) + 0.15 : double((all_tiles + grid_clusters - 1) / std::max<uint64_t>(grid_clusters, 1));
+        const double wide_cost = 2.0 * 0.93 * double((wide_tiles + pairs - 1) / pairs);
+        wide = g.tile_width == 512 || (wide_tiles >= pairs && wide_cost <= square_cost);
+        if (wide_tiles > 0x7fffffffull) wide = false;
+    }
+    if (wide) stream_k = false;
     // The dense tile kernels come without and with the output algebra compiled in ("_ep"): a plain product runs the lean entry.
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
-    const uint32_t shared_bytes = std::max(shared_for(g), g.launch ? g.launch->shared_bytes : 0u);
+    const uint32_t shared_bytes = std::max(wide ? uint32_t(gemm::WIDE_SHARED) : shared_for(g), g.launch ? g.launch->shared_bytes : 0u);
     gpurs_kernel *kernel = nullptr;
     int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
@@ -132,9 +151,9 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)};
     // B as n x k: one box of (128 bytes of k) x (the tile's rows of n).  B as k x n: boxes of (128 bytes of n) x (block_k rows of k).
     // columns of one tile: 256, or 224 for the sparse kernels (two accumulators plus metadata in tensor memory)
-    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : uint64_t(gemm::BLOCK_N);
+    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : wide ? 512 : uint64_t(gemm::BLOCK_N);
     uint64_t dims_b[2] = {g.k, g.n};
-    uint32_t box_b[2] = {block_k, uint32_t(block_n / cta_group)};
+    uint32_t box_b[2] = {block_k, wide ? 128u : uint32_t(block_n / cta_group)};      // wide tiles: the CTA's 128 rows of either half
     if (g.b_row_major) {
         dims_b[0] = g.n, dims_b[1] = g.k;
         box_b[0] = uint32_t(gemm::ROW_BYTES / g.element_bytes), box_b[1] = block_k;
@@ -645,9 +664,11 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     }
 
     int group = desc->algorithm & 0xff;
-    if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES | GPURS_ALGO_SPLIT_LAST_ROUND)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
+    if (desc->algorithm & ~(0xff | GPURS_ALGO_WHOLE_TILES | GPURS_ALGO_SPLIT_LAST_ROUND | GPURS_ALGO_WIDE_TILES | GPURS_ALGO_SQUARE_TILES)) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
         return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
+    if ((desc->algorithm & GPURS_ALGO_WIDE_TILES) && (desc->algorithm & GPURS_ALGO_SQUARE_TILES))
+        return fail(op, GPURS_E_INVALID_ARGUMENT, "wide tiles and square tiles exclude each other");
     // Kernels that promote K-blocks to registers hand an accumulator back and forth between the tensor core and the CUDA cores.
     const bool promoted = desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT);
     // Few rows of A, 16-bit operands, fp32 output: the split-K kernel that streams B once with every multiprocessor.
@@ -756,6 +777,7 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.row_sum = desc->row_sum, gemm.accumulate = desc->accumulate == 1, gemm.launch = desc->launch;
     gemm.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0;
     gemm.force_split = (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND) != 0;
+    gemm.tile_width = (desc->algorithm & GPURS_ALGO_WIDE_TILES) ? 512 : (desc->algorithm & GPURS_ALGO_SQUARE_TILES) ? 256 : 0;
     gemm.b_row_major = b_row_major;
     gemm.gather = gather;
     gemm.batches = batches, gemm.stride_a = stride_a, gemm.stride_b = stride_b, gemm.stride_c = stride_c;

@@ -295,10 +295,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
     auto stage_a = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES; };
     auto stage_b = [&](int s) { return base + uint32_t(s) * L::STAGE_BYTES + L::A_BYTES; };
     auto full_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(s) * 8; };
-    // Stages are handed back to the producer two at a time: a tcgen05.commit costs the issuing thread about as much time as
-    // the tensor core needs for half a stage, so one commit releases a pair of stages (barrier s / 2 serves stages s, s + 1).
-    static_assert(STAGES % 2 == 0, "stages are released in pairs");
-    auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s / 2) * 8; };
+    auto empty_bar = [&](int s) { return base + L::BARRIER_OFFSET + uint32_t(STAGES + s) * 8; };
     auto acc_full_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + a) * 8; };
     auto acc_empty_bar = [&](int a) { return base + L::BARRIER_OFFSET + uint32_t(2 * STAGES + 4 + a) * 8; };
     const uint32_t staging = base + L::STAGING_OFFSET;
@@ -371,7 +368,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                 const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
                 const int row_b = tile_n * BLOCK_N + int(cta_rank) * L::B_ROWS;
                 for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
-                    if ((stage & 1) == 0 && !ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                    if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
                         ok = false;
                         break;
@@ -424,7 +421,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             // Before leaving, see every stage released once more, so that no commit can arrive on a
             // barrier of a CTA that has already exited.
             for (int s = 0; s < STAGES && ok; s++) {
-                if ((stage & 1) == 0) ok = ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag);
+                ok = ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
@@ -438,8 +435,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
             bool ok = true;
             WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
             WorkItem item;
-            // This one thread's instruction stream paces the tensor core (four instructions of 128 tensor cycles per stage):
-            // everything that does not change from stage to stage is computed here, once.
+            // Everything that does not change from stage to stage is computed here, once.  (Releasing the stages in pairs with one
+            // commit per two K-blocks was measured on bf16 8192^3 and changed nothing: this kernel is not bound by its issuing thread.)
             // B as N x K: K-major like A, 32 bytes of K per instruction inside the swizzle span.  B as K x N: N-major
             // (bit 16 of the instruction descriptor), an instruction's K is MMA_K rows of 128 bytes.
             const uint64_t a_desc0 = ptx::smem_descriptor_k_major_sw128(stage_a(0));
@@ -456,8 +453,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                 ptx::tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(acc) * BLOCK_N;
                 for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
-                    // the stage has usually arrived long ago: one probe, and the bounded wait only if it has not
-                    if (!ptx::mbarrier_try_wait(full_bar(stage), phase) && !ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
+                    if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                         report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
                         ok = false;
                         break;
@@ -469,21 +465,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
 #pragma unroll
                     for (int j = 1; j < ROW_BYTES / MMA_K_BYTES; j++)
                         ptx::tcgen05_mma_accumulate<KIND, CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j) * b_step, idesc);
-                    if (stage & 1) {       // the second stage of a pair: both go back to the producer
-                        if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
-                        else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
-                    }
+                    if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
+                    else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(acc_full_bar(acc));
                 else ptx::tcgen05_commit_pair(acc_full_bar(acc), 0x3);
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-            }
-            // an odd number of stages in all: the last one has no partner, and goes back on its own
-            if (ok && (stage & 1)) {
-                if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
-                else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
             }
         }
     } else {

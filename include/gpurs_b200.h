@@ -194,7 +194,12 @@ enum {
      * depend on the shape.  WHOLE_TILES: every tile is multiplied whole by one CTA or CTA pair.  SPLIT_LAST_ROUND: the
      * last round is split whenever it is not full, whether or not that pays. */
     GPURS_ALGO_WHOLE_TILES = 0x100,
-    GPURS_ALGO_SPLIT_LAST_ROUND = 0x200
+    GPURS_ALGO_SPLIT_LAST_ROUND = 0x200,
+    /* CTA-pair tiles are 256 x 256 or, for plain products whose tile count fills the grid well that way, 256 x 512 (a quarter less
+     * operand traffic from L2 per flop, which is what bounds the 256 x 256 tiles).  WIDE_TILES: 256 x 512 wherever that kernel
+     * can run at all; SQUARE_TILES: never.  The result does not depend on the choice. */
+    GPURS_ALGO_WIDE_TILES = 0x400,
+    GPURS_ALGO_SQUARE_TILES = 0x800
 };
 
 /* What the scale arrays of an E4M3 product hold. */

@@ -269,3 +269,29 @@ def test_f32_row_major_right_operand(gpu, stream, shape):
     assert np.array_equal(got, run_matmul(gpu, stream, "f32", "f32", a, b, m, n, k))
     rows = spread_rows(m)
     assert relative_error(got.reshape(m, n)[rows].astype(np.float64), O.matmul_rows(O.FMT_F32, a, b, n, k, rows)) <= 1e-4
+
+
+@pytest.mark.parametrize("kind,out", [("bf16", "bf16"), ("f16", "f32"), ("i8", "i32"), ("e4m3", "bf16"), ("f16", "f16"), ("bf16", "f32"), ("e4m3", "f32")])
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 256), (300, 1100, 192), (256, 520, 64), (1024, 2048, 1100 // 16 * 16), (2304, 1536, 512)])
+def test_wide_tiles_give_the_same_product(gpu, stream, kind, out, m, n, k):
+    """256 x 512 CTA-pair tiles (one 512-column accumulator, handed over in halves) against 256 x 256 ones: the sums and their
+    order do not depend on the tile shape, so the results are equal bit for bit; sampled rows are checked against the oracle.
+    Ragged m and n clip the last boxes; 2304 x 1536 gives one pair several tiles, so halves are reused across tile borders."""
+    a, b = make_operands(kind, m, n, k)
+    before = gpu.launches
+    got = run_matmul(gpu, stream, kind, out, a, b, m, n, k, G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, max_ctas=8 if m == 2304 else 0)
+    assert gpu.launches == before + 1
+    assert np.array_equal(got, run_matmul(gpu, stream, kind, out, a, b, m, n, k, G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES | G.ALGO_WHOLE_TILES))
+    rows = spread_rows(m, 12)
+    values = decode_output(got, out).reshape(m, n)[rows]
+    if kind == "i8":
+        assert np.array_equal(values.astype(np.int64), O.matmul_rows_i8(a, b, n, k, rows))
+    else:
+        assert relative_error(values, O.matmul_rows(KINDS[kind][1], a, b, n, k, rows)) <= (1e-2 if out in ("bf16", "f16") else 1e-3)
+
+
+def test_wide_and_square_tiles_exclude_each_other(gpu, stream):
+    a, b = make_operands("bf16", 256, 512, 64)
+    with pytest.raises(G.GpursError) as raised:
+        run_matmul(gpu, stream, "bf16", "bf16", a, b, 256, 512, 64, G.ALGO_WIDE_TILES | G.ALGO_SQUARE_TILES)
+    assert raised.value.code == 100009

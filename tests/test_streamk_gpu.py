@@ -76,7 +76,7 @@ def test_full_grid_shape_that_splits(gpu, stream):
 
 def test_unknown_algorithm_bits_are_refused(gpu, stream):
     a_bits, b_bits = make_operands("bf16", 128, 128, 64)
-    for algorithm in (0x400, G.ALGO_WHOLE_TILES | G.ALGO_SPLIT_LAST_ROUND):
+    for algorithm in (0x1000, G.ALGO_WHOLE_TILES | G.ALGO_SPLIT_LAST_ROUND, G.ALGO_WIDE_TILES | G.ALGO_SQUARE_TILES):
         with pytest.raises(G.GpursError):
             run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, 128, 128, 64, algorithm=algorithm)
 
