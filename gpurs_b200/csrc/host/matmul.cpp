@@ -127,15 +127,25 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         if (wide_tiles > 0x7fffffffull) wide = false;
     }
     if (wide) stream_k = false;
+    // 512 x 224 tiles of the 2:4-sparse product (kernels/gemm_sparse_tall_tcgen05.cuh): B, most of the sparse kernel's operand
+    // traffic, is fetched once for two row blocks.  Used where they fill the grid's rounds no worse than the 256-row tiles do,
+    // for plain products (that kernel has no output algebra) without an explicit launch geometry (it has its own block size).
+    bool tall = false;
+    if (g.metadata != 0 && cta_group == 2 && !g.gather && g.tile_width != 256 && !algebra_ && !g.launch) {
+        const uint64_t columns = (g.n + gemm::SPARSE_BLOCK_N - 1) / gemm::SPARSE_BLOCK_N;
+        const uint64_t pairs = std::max<uint64_t>(1, wanted_ctas / 2);
+        const uint64_t short_rounds = (((g.m + 255) / 256) * columns + pairs - 1) / pairs, tall_rounds = (((g.m + 511) / 512) * columns + pairs - 1) / pairs;
+        tall = g.tile_width == 512 || (g.m > 256 && 2.0 * 0.8 * double(tall_rounds) <= double(short_rounds));
+    }
     // The dense tile kernels come without and with the output algebra compiled in ("_ep"): a plain product runs the lean entry.
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
-    const uint32_t shared_bytes = std::max(wide ? uint32_t(gemm::WIDE_SHARED) : shared_for(g), g.launch ? g.launch->shared_bytes : 0u);
+    const uint32_t shared_bytes = std::max(wide ? uint32_t(gemm::WIDE_SHARED) : tall ? uint32_t(gemm::SPARSE_TALL_SHARED) : shared_for(g), g.launch ? g.launch->shared_bytes : 0u);
     gpurs_kernel *kernel = nullptr;
     int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
@@ -191,7 +201,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     params.m = int(g.m);
     params.n = int(g.n);
     params.k = int(g.k);
-    const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
+    const uint64_t tile_rows = tall ? 512 : uint64_t(gemm::BLOCK_M) * cta_group;
     params.tiles_m = int((g.m + tile_rows - 1) / tile_rows);
     params.tiles_n = int((g.n + block_n - 1) / block_n);
     // Bands of 2048 rows by default: with one tile per SM in flight, the tiles running together then
@@ -227,7 +237,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     std::memset(&config, 0, sizeof config);
     config.grid[0] = uint32_t(clusters * cta_group);
     config.grid[1] = config.grid[2] = 1;
-    config.block[0] = uint32_t(g.threads);
+    config.block[0] = tall ? uint32_t(gemm::SPARSE_TALL_NUM_THREADS) : uint32_t(g.threads);
     config.block[1] = config.block[2] = 1;
     config.shared_bytes = shared_bytes;
     config.cluster[0] = uint32_t(cta_group);

@@ -117,6 +117,9 @@ constexpr int SPARSE_SHARED_SINGLE = 2 * (BLOCK_M * ROW_BYTES + 2 * SPARSE_BLOCK
 constexpr int SPARSE_SHARED_PAIR = 4 * (BLOCK_M * ROW_BYTES + SPARSE_BLOCK_N * ROW_BYTES + 2048) + (2 * 4 + 4) * 8 + 8 + 1024;
 // the CTA-pair push entry adds 32 KiB of output staging behind the stages (1024-byte aligned)
 constexpr int SPARSE_SHARED_PAIR_PUSH = ((SPARSE_SHARED_PAIR - 1024 + 1023) / 1024) * 1024 + 4 * 2 * 32 * ROW_BYTES + 1024;
+// 512 x 224 pair tiles: three stages of two A tiles, the CTA's half of B and two metadata blocks
+constexpr int SPARSE_TALL_NUM_THREADS = 320;     // producer warp, MMA warp, eight epilogue warps
+constexpr int SPARSE_TALL_SHARED = 3 * (2 * BLOCK_M * ROW_BYTES + SPARSE_BLOCK_N * ROW_BYTES + 2 * 2048) + (2 * 3 + 4) * 8 + 8 + 1024;
 constexpr int SPARSE_METADATA_BLOCK_BYTES = 2048;
 constexpr int SPARSE_BLOCK_K = 128;
 

@@ -26,11 +26,11 @@ def decode_metadata(raw, m, k):
     return ((byte >> (4 * ((starts % 8) // 4))) & 0xF).reshape(-1)
 
 
-def sparse_product(gpu, stream, dense, b, m, n, k, out, algorithm, fmt=G.BF16):
+def sparse_product(gpu, stream, dense, b, m, n, k, out, algorithm, fmt=G.BF16, **options):
     values, metadata, violations = G.compress_24(stream, gpu.upload(dense, fmt), m, k)
     c = gpu.allocate({"f32": G.F32, "bf16": G.BF16}[out], m * n)
     gpu._lib.gpurs_fill_u8(stream._handle, c.pointer, 0x7F, c.nbytes)
-    G.matmul(stream, values, gpu.upload(b, fmt), c, [m, n, k], G.MatmulOptions(algorithm=algorithm, metadata=metadata))
+    G.matmul(stream, values, gpu.upload(b, fmt), c, [m, n, k], G.MatmulOptions(algorithm=algorithm, metadata=metadata, **options))
     stream.synchronize()
     assert violations.download()[0] == 0
     return decode_output(c.download(), out).reshape(m, n)
@@ -94,6 +94,34 @@ def test_sparse_equals_dense_kernel_on_the_same_matrix(gpu, stream):
     # not bit for bit: a sparse instruction sums 32 logical K at a time, a dense one 16, and the fp32
     # accumulator of the tensor core truncates after each
     assert relative_error(sparse, c.download().reshape(m, n).astype(np.float64)) <= 1e-4
+
+
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+@pytest.mark.parametrize("shape,max_ctas", [((512, 224, 128), 0), ((512, 448, 1024), 0), ((700, 500, 1024), 0), ((129, 257, 2048), 0), ((1536, 1000, 512), 4),
+                                            ((2048, 2240, 256), 0)])
+def test_tall_tiles_equal_the_256_row_tiles(gpu, stream, shape, max_ctas, out):
+    """512 x 224 pair tiles sum every output in the same order as the 256 x 224 ones: bit-equal, ragged edges, several tiles
+    per pair (max_ctas 4); both agree with the densified oracle product.  With output algebra the flag changes nothing (that
+    product stays on the 256-row tiles)."""
+    m, n, k = shape
+    dense, b = O.fill_sparse24_bf16(m, k, 21), O.fill_normal_16(O.FMT_BF16, n * k, 22)
+    tall = sparse_product(gpu, stream, dense, b, m, n, k, out, G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, max_ctas=max_ctas)
+    short = sparse_product(gpu, stream, dense, b, m, n, k, out, G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES, max_ctas=max_ctas)
+    assert np.array_equal(tall, short)
+    rows = spread_rows(m, 16)
+    assert relative_error(tall[rows], O.matmul_rows(O.FMT_BF16, dense, b, n, k, rows)) <= (1e-3 if out == "f32" else 1e-2)
+    bias = gpu.upload(np.linspace(-2, 2, n, dtype=np.float32), G.F32)
+    assert np.array_equal(sparse_product(gpu, stream, dense, b, m, n, k, out, G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, max_ctas=max_ctas, bias=bias),
+                          sparse_product(gpu, stream, dense, b, m, n, k, out, G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES, max_ctas=max_ctas, bias=bias))
+
+
+def test_tall_tiles_f16(gpu, stream):
+    m, n, k = 1024, 448, 512
+    dense = O.f16_from_f32(O.bf16_to_f32(O.fill_sparse24_bf16(m, k, 23)))
+    b = O.fill_normal_16(O.FMT_F16, n * k, 24)
+    tall = sparse_product(gpu, stream, dense, b, m, n, k, "f32", G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, fmt=G.F16)
+    assert np.array_equal(tall, sparse_product(gpu, stream, dense, b, m, n, k, "f32", G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES, fmt=G.F16))
+    assert relative_error(tall, O.matmul_rows(O.FMT_F16, dense, b, n, k, np.arange(m))) <= 1e-3
 
 
 def test_sparse_configuration_shard(gpu, stream):
