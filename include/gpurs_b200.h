@@ -197,7 +197,8 @@ enum {
     GPURS_ALGO_SPLIT_LAST_ROUND = 0x200,
     /* CTA-pair tiles are 256 x 256 or, for plain products whose tile count fills the grid well that way, 256 x 512 (a quarter less
      * operand traffic from L2 per flop, which is what bounds the 256 x 256 tiles).  WIDE_TILES: 256 x 512 wherever that kernel
-     * can run at all; SQUARE_TILES: never.  The result does not depend on the choice. */
+     * can run at all; SQUARE_TILES: never.  A 2:4-sparse product has the same choice between its 256 x 224 and 512 x 224 pair
+     * tiles (the right operand fetched once for two row blocks).  The result does not depend on the choice. */
     GPURS_ALGO_WIDE_TILES = 0x400,
     GPURS_ALGO_SQUARE_TILES = 0x800
 };
