@@ -116,14 +116,17 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
                           g.row_sum || g.accumulate;
     bool wide = false;
     if (g.tile_width != 256 && !g.force_split && cta_group == 2 && g.metadata == 0 && g.threads == gemm::NUM_THREADS && !batched && !g.gather && !g.b_row_major &&
-        !algebra_ && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0) {
+        !algebra_ && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0 &&
+        (!g.launch || g.launch->block[0] == 0)) {      // that kernel has its own block size
         const uint64_t wide_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + 511) / 512);
         const uint64_t pairs = std::max<uint64_t>(1, wanted_ctas / 2);
         // measured on bf16 8192^3 (14 rounds of square tiles against 7 of wide ones): +8.6 %; on f16 4096^3, where the square tiles'
         // last round is split along K (3.46 rounds) and wide tiles need 2 whole rounds for 1.73: -6 %
         const double square_cost = stream_k ? double(all_tiles) / double(pairs) + 0.15 : double((all_tiles + grid_clusters - 1) / std::max<uint64_t>(grid_clusters, 1));
         const double wide_cost = 2.0 * 0.93 * double((wide_tiles + pairs - 1) / pairs);
-        wide = g.tile_width == 512 || (wide_tiles >= pairs && wide_cost <= square_cost);
+        // (a single partial round of wide tiles counts as a whole one: 64 wide tiles on 74 pairs, the 1024-row shard of int8
+        // 8192^3, measured 49.2 us against 51.1 us for 128 square tiles with the last round split along K)
+        wide = g.tile_width == 512 || (all_tiles > pairs && wide_cost <= square_cost);
         if (wide_tiles > 0x7fffffffull) wide = false;
     }
     if (wide) stream_k = false;
@@ -237,7 +240,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     std::memset(&config, 0, sizeof config);
     config.grid[0] = uint32_t(clusters * cta_group);
     config.grid[1] = config.grid[2] = 1;
-    config.block[0] = tall ? uint32_t(gemm::SPARSE_TALL_NUM_THREADS) : uint32_t(g.threads);
+    config.block[0] = tall ? uint32_t(gemm::SPARSE_TALL_NUM_THREADS) : wide ? uint32_t(gemm::WIDE_NUM_THREADS) : uint32_t(g.threads);
     config.block[1] = config.block[2] = 1;
     config.shared_bytes = shared_bytes;
     config.cluster[0] = uint32_t(cta_group);

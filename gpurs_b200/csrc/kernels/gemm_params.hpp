@@ -81,6 +81,7 @@ constexpr int BLOCKSCALED_SHARED = ((6 * 32768 + (2 * 6 + 12) * 8 + 8 + 16 + 102
 
 // Dynamic shared memory of the 256 x 512 CTA-pair entries (gemm_wide_tcgen05.cuh): 4 stages of 48 KiB, 12 barriers, 32 KiB of
 // output staging, alignment slack.
+constexpr int WIDE_NUM_THREADS = 320;     // producer warp, MMA warp, eight epilogue warps
 constexpr int WIDE_SHARED = ((4 * 49152 + (2 * 4 + 4) * 8 + 8 + 1023) / 1024) * 1024 + 4 * 2 * 32 * 128 + 1024;
 
 template <int BLOCK_N, int CTA_GROUP, int STAGES>

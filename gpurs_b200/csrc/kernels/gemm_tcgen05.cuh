@@ -526,21 +526,24 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                 // previous store still reads its buffer.
                 constexpr int COLUMNS_PER_BOX = (OUT == OUT_F32 || OUT == OUT_I32) ? 32 : 64;
                 const int warp_row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32;
+                // the read of box b + 1 is in flight while box b is staged and stored
+                constexpr int BOXES = BLOCK_N / COLUMNS_PER_BOX;
+                uint32_t low[32], high[32];
+                ptx::tmem_load_32x32(lane_base, low);
+                if constexpr (COLUMNS_PER_BOX == 64) ptx::tmem_load_32x32(lane_base + 32, high);
 #pragma unroll 1
-                for (int box = 0; box < BLOCK_N / COLUMNS_PER_BOX; box++) {
+                for (int box = 0; box < BOXES; box++) {
                     const int column = tile_n * BLOCK_N + box * COLUMNS_PER_BOX;
                     uint32_t packed[32];
+                    ptx::tmem_load_wait();
                     if constexpr (COLUMNS_PER_BOX == 32) {
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
-                        ptx::tmem_load_wait();
-                        if constexpr (ALGEBRA) apply_epilogue<OUT>(p, packed, row, column);
-                        if (reduce) row_max = fold_absmax(p, packed, column, row_max);
-                        if (summing) row_total = fold_sum(p, packed, column, row_total);
+                        if constexpr (ALGEBRA) apply_epilogue<OUT>(p, low, row, column);
+                        if (reduce) row_max = fold_absmax(p, low, column, row_max);
+                        if (summing) row_total = fold_sum(p, low, column, row_total);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) packed[i] = low[i];
+                        if (box + 1 < BOXES) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
                     } else {
-                        uint32_t low[32], high[32];
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
-                        ptx::tmem_load_wait();
                         if constexpr (ALGEBRA) {
                             apply_epilogue<OUT>(p, low, row, column);
                             apply_epilogue<OUT>(p, high, row, column + 32);
@@ -551,6 +554,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
                             packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
+                        }
+                        if (box + 1 < BOXES) {
+                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64), low);
+                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64 + 32), high);
                         }
                     }
                     if (warp_row < p.m && column < p.n) {    // warp-uniform: boxes wholly outside C are skipped

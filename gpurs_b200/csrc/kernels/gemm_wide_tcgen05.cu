@@ -2,7 +2,7 @@
 #include "gemm_wide_tcgen05.cuh"
 
 #define GPURS_WIDE_KERNEL(NAME, KIND, FORMAT, ACC, OUT)                                                            \
-    extern "C" __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)                                             \
+    extern "C" __global__ void __launch_bounds__(gemm::WIDE_THREADS, 1)                                            \
     NAME(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,                     \
          const __grid_constant__ CUtensorMap map_c, const __grid_constant__ gemm::Params params) {                 \
         gemm::gemm_wide_body<KIND, FORMAT, ACC, OUT>(&map_a, &map_b, &map_c, params);                              \

@@ -14,15 +14,21 @@
 //
 // Layout per stage and CTA: 128 rows of A (16 KiB), then the CTA's 128 rows of either half of the B tile (2 x 16 KiB): the
 // leader holds the first 128 rows of B of each half, the other CTA the last 128, so that a product of N = 256 finds 128 rows
-// in either CTA at one shared-memory offset.  4 stages of 48 KiB, 32 KiB of output staging.  Roles as in gemm_tcgen05.cuh:
-// warp 0 producer, warp 1 MMA issuer (leader), warps 2..5 epilogue.  Plain epilogue only (round, stage, TMA store), C with
-// 16-byte aligned rows; everything else takes the 256-column kernels.
+// in either CTA at one shared-memory offset.  4 stages of 48 KiB, 32 KiB of output staging.  Roles: warp 0 producer, warp 1 MMA
+// issuer (leader), warps 2..9 epilogue: two warps per quadrant of tensor-memory lanes, one for the first and one for the second
+// 128 columns of either half, one staging box each.  (A launch of one round ends with every tile's read-out exposed at once;
+// with four epilogue warps that tail was measured at 6.6 us for 32-bit outputs, which a 1024-row shard of an 8192^3 product
+// cannot afford.)  Plain epilogue only (round, stage, TMA store), C with 16-byte aligned rows; everything else takes the
+// 256-column kernels.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
 namespace gemm {
 
 constexpr int WIDE_BLOCK_N = 512, WIDE_STAGES = 4;
+constexpr int WIDE_EPILOGUE_WARPS = 8;
+constexpr int WIDE_THREADS = 64 + 32 * WIDE_EPILOGUE_WARPS;
+static_assert(WIDE_THREADS == WIDE_NUM_THREADS, "the host sizes the launch from gemm_params.hpp");
 
 struct WideLayout {
     static constexpr int A_BYTES = BLOCK_M * ROW_BYTES;
@@ -34,7 +40,7 @@ struct WideLayout {
     static constexpr int TMEM_SLOT_OFFSET = BARRIER_OFFSET + NUM_BARRIERS * 8;
     static constexpr int ABORT_OFFSET = TMEM_SLOT_OFFSET + 4;
     static constexpr int STAGING_OFFSET = ((ABORT_OFFSET + 4 + 1023) / 1024) * 1024;
-    static constexpr int STAGING_BYTES = EPILOGUE_WARPS * 2 * 32 * ROW_BYTES;
+    static constexpr int STAGING_BYTES = WIDE_EPILOGUE_WARPS * 32 * ROW_BYTES;      // one box of 32 rows x 128 bytes per epilogue warp
     static constexpr int TOTAL = STAGING_OFFSET + STAGING_BYTES;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;
     static_assert(DYNAMIC_BYTES <= 232448, "more than the 227 KiB a CTA may have");
@@ -80,7 +86,7 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
         }
         for (int h = 0; h < 2; h++) {
             ptx::mbarrier_init(acc_full_bar(h), 1);
-            ptx::mbarrier_init(acc_empty_bar(h), EPILOGUE_WARPS * 2);
+            ptx::mbarrier_init(acc_empty_bar(h), WIDE_EPILOGUE_WARPS * 2);
         }
         ptx::fence_mbarrier_init();
         ptx::prefetch_tensor_map(map_a);
@@ -176,9 +182,12 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
         }
     } else {
         // ------------------------------------------------------------------ epilogue: half 0, then half 1
-        const int quadrant = warp % 4;
+        const int quadrant = warp % 4;                 // the 32 lanes of tensor memory this warp may read
+        const int side = (warp - 2) / 4;               // 0: the first 128 columns of either half, 1: the last 128
+        const uint32_t buffer = staging + uint32_t(warp - 2) * 32 * ROW_BYTES;
+        constexpr int COLUMNS_PER_BOX = (OUT == OUT_F32 || OUT == OUT_I32) ? 32 : 64;
+        constexpr int BOXES = 128 / COLUMNS_PER_BOX;   // per warp and half
         uint32_t tile_phase = 0;
-        int stores = 0;
         bool ok = true;
         for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
             int tile_m, tile_n;
@@ -192,28 +201,34 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                     break;
                 }
                 ptx::tcgen05_fence_after();
-                const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(half) * HALF;
-                constexpr int COLUMNS_PER_BOX = (OUT == OUT_F32 || OUT == OUT_I32) ? 32 : 64;
-#pragma unroll 1
-                for (int box = 0; box < HALF / COLUMNS_PER_BOX; box++) {
-                    const int column = tile_n * WIDE_BLOCK_N + half * HALF + box * COLUMNS_PER_BOX;
+                const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(half * HALF + side * 128);
+                // the read of box b + 1 is in flight while box b is staged and stored
+                uint32_t low[32], high[32];
+                ptx::tmem_load_32x32(lane_base, low);
+                if constexpr (COLUMNS_PER_BOX == 64) ptx::tmem_load_32x32(lane_base + 32, high);
+#pragma unroll
+                for (int box = 0; box < BOXES; box++) {
+                    const int column = tile_n * WIDE_BLOCK_N + half * HALF + side * 128 + box * COLUMNS_PER_BOX;
                     uint32_t packed[32];
+                    ptx::tmem_load_wait();
                     if constexpr (COLUMNS_PER_BOX == 32) {
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 32), packed);
-                        ptx::tmem_load_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) packed[i] = low[i];
+                        if (box + 1 < BOXES) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
                     } else {
-                        uint32_t low[32], high[32];
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64), low);
-                        ptx::tmem_load_32x32(lane_base + uint32_t(box * 64 + 32), high);
-                        ptx::tmem_load_wait();
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
                             packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
                         }
+                        if (box + 1 < BOXES) {
+                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64), low);
+                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64 + 32), high);
+                        }
                     }
-                    if (box == HALF / COLUMNS_PER_BOX - 1) {
-                        // the half has left tensor memory: the next tile's products may overwrite it while these boxes are stored
+                    if (box == BOXES - 1) {
+                        // this warp's part of the half has left tensor memory: once all sixteen warps of the pair have said so,
+                        // the next tile's products may overwrite it while these boxes are stored
                         ptx::tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) {
@@ -222,9 +237,7 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                         }
                     }
                     if (warp_row < p.m && column < p.n) {    // warp-uniform: boxes wholly outside C are skipped
-                        const uint32_t buffer = staging + uint32_t(((warp - 2) * 2 + (stores & 1)) * 32 * ROW_BYTES);
-                        stores++;
-                        if (lane == 0) ptx::tma_store_wait_read<1>();       // the store that used this buffer two boxes ago
+                        if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous store has read the buffer
                         __syncwarp();
 #pragma unroll
                         for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
@@ -241,7 +254,8 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
             }
             tile_phase ^= 1;
         }
-        if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
+        // the stores have read their shared-memory source; the grid's completion orders their writes before whatever follows
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------------- teardown

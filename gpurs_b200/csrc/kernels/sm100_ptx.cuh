@@ -326,21 +326,6 @@ __device__ __forceinline__ void registers_decrease() { asm volatile("setmaxnreg.
 
 namespace ptx {
 
-// Two fp32 values kept together in one 64-bit register, the operand form of the packed fp32 instructions.
-__device__ __forceinline__ uint64_t pack_f32x2(uint32_t low, uint32_t high) {
-    uint64_t packed;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "r"(low), "r"(high));
-    return packed;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t packed, uint32_t &low, uint32_t &high) {
-    asm("mov.b64 {%0, %1}, %2;" : "=r"(low), "=r"(high) : "l"(packed));
-}
-// sums += values * scales, lane by lane, on operands that already are pairs: no packing or unpacking around the instruction
-// (with sums held as pairs for a whole K loop, the moves that fma2 below spends around every instruction disappear).
-__device__ __forceinline__ void fma_f32x2(uint64_t &sums, uint64_t values, uint64_t scales) {
-    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(sums) : "l"(values), "l"(scales));
-}
-
 // (sum0, sum1) += (value0, value1) * scale, both lanes in one packed instruction.
 __device__ __forceinline__ void fma2(float &sum0, float &sum1, uint32_t value0, uint32_t value1, float scale) {
     asm("{\n\t.reg .b64 v, s, d;\n\t"
