@@ -498,6 +498,23 @@ def gather_leg(G, gpu, stream, dist, prepared: Prepared, rank: int, world: int, 
     result["fused"] = {"ms_per_step": fused_ms, "value": world * flops / (fused_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                        "bytes_sent_per_gpu": int((world - 1) * shard_bytes), "equals_collective_result": bool(agree.item()),
                        "link_bound_ms": link_bound_ms, "how": "gpurs_matmul_allgather: one kernel per GPU, remote TMA stores from the epilogue"}
+    # third way: bands of rows multiplied by the plain kernels, every finished band sent by the copy engines while the next is
+    # multiplied.  The gathered matrix is overwritten first, so that the comparison below sees this form's own output.
+    dist.barrier()
+    gpu._lib.gpurs_fill_u8(stream._handle, gathered.local.pointer, 0x7F, gathered.local.nbytes)
+    stream.synchronize()
+    dist.barrier()
+    import dataclasses
+    by_copies = dataclasses.replace(prepared.options, algorithm=prepared.options.algorithm | G.ALGO_GATHER_BY_COPIES)
+    copies_ms = timed(lambda: G.matmul_allgather(stream, prepared.a, prepared.b, gathered, prepared.shape, rank * m, by_copies))
+    same = bool(np.array_equal(gathered.local.download().view(np.uint8), gathered_by_nccl))
+    agree = torch.tensor([1 if same else 0], device="cuda")
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    result["copy_engines"] = {"ms_per_step": copies_ms, "value": world * flops / (copies_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                              "bytes_sent_per_gpu": int((world - 1) * shard_bytes), "equals_collective_result": bool(agree.item()),
+                              "link_bound_ms": link_bound_ms,
+                              "how": "gpurs_matmul_allgather with GPURS_ALGO_GATHER_BY_COPIES: the block in bands of rows, each sent to every peer by "
+                                     "the copy engines (one stream per peer) while the next band is multiplied"}
     dist.barrier()
     gathered.close()
     comm.close()

@@ -31,6 +31,7 @@ ALGO_AUTO, ALGO_SINGLE_CTA, ALGO_CTA_PAIR, ALGO_SKINNY = 0, 1, 2, 3
 ALGO_WHOLE_TILES = 0x100   # flag: never split the last round's tiles along K
 ALGO_SPLIT_LAST_ROUND = 0x200   # flag: split it whenever it is not full
 ALGO_WIDE_TILES = 0x400   # flag: 256 x 512 pair tiles (2:4 sparse: 512 x 224) wherever possible
+ALGO_GATHER_BY_COPIES = 0x1000   # flag, matmul_allgather only: bands of rows sent by the copy engines
 ALGO_SQUARE_TILES = 0x800   # flag: never 256 x 512 (2:4 sparse: 512 x 224) tiles
 PRECISION_DEFAULT, PRECISION_TF32 = 0, 1
 SCALES_FP32_BLOCKS, SCALES_MX = 0, 1

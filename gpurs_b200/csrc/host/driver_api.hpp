@@ -44,6 +44,7 @@ namespace driver {
     X(cuMemHostAlloc)             \
     X(cuMemFreeHost)              \
     X(cuMemcpy2DAsync)            \
+    X(cuMemcpyDtoDAsync)          \
     X(cuIpcGetMemHandle)          \
     X(cuIpcOpenMemHandle)         \
     X(cuIpcCloseMemHandle)        \

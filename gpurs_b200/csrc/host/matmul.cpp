@@ -890,7 +890,70 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
     gpurs_matmul_desc local = *desc;
     local.ldc = pitch;
     local.c_len = 0;
-    return matmul_checked(op, stream, &local, a, b, gather->full[gather->rank] + gather->row_offset * pitch * ob, gather);
+    const gpurs_device_ptr mine = gather->full[gather->rank] + gather->row_offset * pitch * ob;
+    if (!(desc->algorithm & GPURS_ALGO_GATHER_BY_COPIES)) return matmul_checked(op, stream, &local, a, b, mine, gather);
+
+    // Copy-engine form: the block is multiplied in up to four bands of rows (whole 512-row tiles) by the plain kernels, into
+    // this GPU's copy; when a band is complete, one helper stream per peer copies it to that peer over NVLink while the next
+    // band is multiplied.  The caller's stream continues after all copies (they are its work).
+    local.algorithm &= ~GPURS_ALGO_GATHER_BY_COPIES;
+    gpurs_gpu *gpu = stream->gpu;
+    runtime::Enter enter(gpu);
+    const driver::Api *api = gpu->api;
+    const uint32_t peers = gather->world - 1;
+    const uint64_t granule = 512;
+    const uint64_t bands = std::min<uint64_t>(4, std::max<uint64_t>(1, m / granule));
+    const uint64_t band_rows = ((m + bands - 1) / bands + granule - 1) / granule * granule;
+    int result = runtime::copy_pipeline(gpu, bands + peers);
+    if (result == GPURS_OK) result = runtime::peer_pipeline(gpu, peers);
+    if (result != GPURS_OK) return result;
+    const uint64_t a_pitch = desc->lda ? desc->lda : (desc->metadata ? desc->k / 2 : desc->k);
+    const uint64_t metadata_per_row_block = desc->metadata ? (desc->k / 128) * uint64_t(gemm::SPARSE_METADATA_BLOCK_BYTES) : 0;
+    bool copied = false;
+    for (uint64_t band = 0; band * band_rows < m && result == GPURS_OK; band++) {
+        const uint64_t first = band * band_rows, rows = std::min(band_rows, m - first);
+        gpurs_matmul_desc part = local;
+        part.m = rows;
+        if (desc->metadata) part.metadata = desc->metadata + (first / 128) * metadata_per_row_block;
+        if (desc->row_scale) part.row_scale = desc->row_scale + first * sizeof(float);
+        if (desc->row_bias) part.row_bias = desc->row_bias + first * sizeof(float);
+        if (desc->row_absmax) part.row_absmax = desc->row_absmax + first * sizeof(float);
+        if (desc->row_sum) part.row_sum = desc->row_sum + first * sizeof(float);
+        if (desc->residual) part.residual = desc->residual + first * (desc->ldr ? desc->ldr : n) * ob;
+        const uint64_t c_offset = first * pitch * ob;
+        result = matmul_checked(op, stream, &part, a + first * a_pitch * eb, b, mine + c_offset, nullptr);
+        if (result != GPURS_OK) break;
+        CUevent multiplied = gpu->events[band];
+        CUresult code = api->cuEventRecord(multiplied, stream->handle);
+        for (uint32_t i = 0; i < peers && code == CUDA_SUCCESS; i++) {
+            const uint32_t target = (gather->rank + 1 + i) % gather->world;
+            const CUdeviceptr to = gather->full[target] + gather->row_offset * pitch * ob + c_offset;
+            code = api->cuStreamWaitEvent(gpu->peer_streams[i], multiplied, 0);
+            if (code != CUDA_SUCCESS) break;
+            if (pitch == n) {
+                code = api->cuMemcpyDtoDAsync(to, mine + c_offset, rows * n * ob, gpu->peer_streams[i]);
+            } else {
+                CUDA_MEMCPY2D copy;
+                std::memset(&copy, 0, sizeof copy);
+                copy.srcMemoryType = copy.dstMemoryType = CU_MEMORYTYPE_DEVICE;
+                copy.srcDevice = mine + c_offset, copy.dstDevice = to;
+                copy.srcPitch = copy.dstPitch = pitch * ob;
+                copy.WidthInBytes = n * ob;
+                copy.Height = rows;
+                code = api->cuMemcpy2DAsync(&copy, gpu->peer_streams[i]);
+            }
+            copied = true;
+        }
+        if (code != CUDA_SUCCESS) result = runtime::fail_driver(api, "gpurs_matmul_allgather copy", code);
+    }
+    // whatever happened, the caller's stream continues only after the helper streams have drained
+    for (uint32_t i = 0; i < peers && copied; i++) {
+        CUevent sent = gpu->events[bands + i];
+        CUresult code = api->cuEventRecord(sent, gpu->peer_streams[i]);
+        if (code == CUDA_SUCCESS) code = api->cuStreamWaitEvent(stream->handle, sent, 0);
+        if (code != CUDA_SUCCESS && result == GPURS_OK) result = runtime::fail_driver(api, "gpurs_matmul_allgather join", code);
+    }
+    return result;
 }
 
 // Operands and result in HOST memory: copy in, multiply, copy out, with the three overlapped.  One operand goes up whole,

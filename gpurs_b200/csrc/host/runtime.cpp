@@ -184,6 +184,15 @@ int copy_pipeline(gpurs_gpu *gpu, size_t count) {
     return GPURS_OK;
 }
 
+int peer_pipeline(gpurs_gpu *gpu, size_t count) {
+    while (gpu->peer_streams.size() < count) {
+        CUstream stream = nullptr;
+        GPURS_TRY(gpu->api, cuStreamCreate(&stream, CU_STREAM_NON_BLOCKING));
+        gpu->peer_streams.push_back(stream);
+    }
+    return GPURS_OK;
+}
+
 }  // namespace runtime
 
 using runtime::Enter;
@@ -275,6 +284,7 @@ void gpurs_gpu_free(gpurs_gpu *gpu) {
         if (gpu->copy_in) gpu->api->cuStreamDestroy(gpu->copy_in);
         if (gpu->copy_out) gpu->api->cuStreamDestroy(gpu->copy_out);
         for (CUevent event : gpu->events) gpu->api->cuEventDestroy(event);
+        for (CUstream stream : gpu->peer_streams) gpu->api->cuStreamDestroy(stream);
     }
     gpu->api->cuDevicePrimaryCtxRelease(gpu->device);
     delete gpu;

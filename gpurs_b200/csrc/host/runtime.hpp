@@ -50,6 +50,8 @@ struct gpurs_gpu {
     // caller's stream and are tied to it by events.
     CUstream copy_in = nullptr, copy_out = nullptr;
     std::vector<CUevent> events;
+    // One stream per peer for the copies of gpurs_matmul_allgather's copy-engine form (created on first use).
+    std::vector<CUstream> peer_streams;
     Scratch workspace;   // grow-only: the hi/lo split copies of fp32 operands
     Scratch turns;       // fixed: the turn counters of split-K products, zero between launches
 };
@@ -114,6 +116,8 @@ int turns_acquire(gpurs_stream *stream, size_t bytes, CUdeviceptr *out);
 int turns_release(gpurs_stream *stream);
 // At least `count` reusable events (no timing) in gpu->events, and the two helper streams.
 int copy_pipeline(gpurs_gpu *gpu, size_t count);
+// At least `count` streams in gpu->peer_streams.
+int peer_pipeline(gpurs_gpu *gpu, size_t count);
 
 }  // namespace runtime
 

@@ -200,7 +200,12 @@ enum {
      * can run at all; SQUARE_TILES: never.  A 2:4-sparse product has the same choice between its 256 x 224 and 512 x 224 pair
      * tiles (the right operand fetched once for two row blocks).  The result does not depend on the choice. */
     GPURS_ALGO_WIDE_TILES = 0x400,
-    GPURS_ALGO_SQUARE_TILES = 0x800
+    GPURS_ALGO_SQUARE_TILES = 0x800,
+    /* gpurs_matmul_allgather only: multiply the block in bands of rows with the plain kernels and send every finished band to
+     * the other GPUs with the copy engines (one helper stream per peer) while the next band is multiplied, instead of storing
+     * to all GPUs from the product's epilogue.  The call is stream-ordered as always: work enqueued on `stream` after it sees
+     * this GPU's copies sent. */
+    GPURS_ALGO_GATHER_BY_COPIES = 0x1000
 };
 
 /* What the scale arrays of an E4M3 product hold. */

@@ -30,12 +30,15 @@ def gather_in_one_process(gpu, stream, kind, out, a_bits, b_bits, m, n, k, world
         desc = _ffi.MatmulDesc()
         desc.a_type, desc.c_type, desc.m, desc.n, desc.k = element, OUTPUTS[out], rows, n, k
         desc.bias = options["bias"].pointer if "bias" in options else 0
+        desc.algorithm = options.get("algorithm", 0)
+        if "row_bias" in options:
+            desc.row_bias = options["row_bias"].pointer + 4 * first      # the local product's rows start at the block's first row
         gather = _ffi.GatherDesc()
         gather.world, gather.rank, gather.row_offset, gather.total_rows = world, rank, first, m
         for peer, copy in enumerate(copies):
             gather.full[peer] = copy.pointer
         code = gpu._lib.gpurs_matmul_allgather(stream._handle, C.byref(desc), C.byref(gather), a.pointer, b.pointer)
-        assert code == 0, gpu._lib.gpurs_last_error().decode()
+        assert code == 0, str(G.GpursError(code))
     stream.synchronize()
     return [copy.download() for copy in copies]
 
@@ -66,6 +69,29 @@ def test_bias_is_added_before_the_push(gpu, stream):
     bias = gpu.upload((np.arange(n) / 8.0).astype(np.float32))
     whole = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=G.ALGO_CTA_PAIR, bias=bias)
     for copy in gather_in_one_process(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, 2, bias=bias):
+        assert np.array_equal(copy, whole)
+
+
+@pytest.mark.parametrize("kind,out", [("bf16", "bf16"), ("bf16", "f32"), ("i8", "i32"), ("f32", "f32")])
+@pytest.mark.parametrize("m,n,k,world", [(512, 512, 256, 2), (1000, 520, 144, 3), (4096, 1024, 128, 2), (8192, 512, 64, 8), (300, 264, 64, 4)])
+def test_copy_engine_form_fills_every_copy(gpu, stream, kind, out, m, n, k, world):
+    """GPURS_ALGO_GATHER_BY_COPIES: the block in bands of rows (four bands of 512 rows for the 2048-row blocks here), every band
+    sent to the other copies by copy streams: each copy equals the single-GPU product bit for bit, for output types the push
+    kernels do not have as well (the bands are plain products)."""
+    a_bits, b_bits = make_operands(kind, m, n, k)
+    whole = run_matmul(gpu, stream, kind, out, a_bits, b_bits, m, n, k)
+    for copy in gather_in_one_process(gpu, stream, kind, out, a_bits, b_bits, m, n, k, world, algorithm=G.ALGO_GATHER_BY_COPIES):
+        assert np.array_equal(copy, whole)
+
+
+def test_copy_engine_form_offsets_the_row_vectors(gpu, stream):
+    m, n, k, world = 4096, 384, 128, 2
+    a_bits, b_bits = make_operands("f16", m, n, k)
+    bias = gpu.upload((np.arange(n) / 8.0).astype(np.float32))
+    row_bias = gpu.upload((np.arange(m) % 97).astype(np.float32))
+    whole = run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, bias=bias, row_bias=row_bias)
+    for copy in gather_in_one_process(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, world, bias=bias, row_bias=row_bias,
+                                      algorithm=G.ALGO_GATHER_BY_COPIES):
         assert np.array_equal(copy, whole)
 
 
