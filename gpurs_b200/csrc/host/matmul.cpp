@@ -544,6 +544,27 @@ int split_tf32(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gp
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
+// Both operands (n x k right operand) in one launch.
+int split_tf32_pair(gpurs_stream *stream, gpurs_device_ptr left, uint64_t left_pitch, gpurs_device_ptr left_destination, uint64_t left_rows,
+                    gpurs_device_ptr right, uint64_t right_pitch, gpurs_device_ptr right_destination, uint64_t right_rows, uint64_t k) {
+    gpurs_gpu *gpu = stream->gpu;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, "gpurs_split_tf32_pair", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t quads = (left_rows + right_rows) * (k / 4);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    const uint64_t blocks = std::min<uint64_t>((quads + 255) / 256, uint64_t(gpu->multiprocessors) * 8);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, blocks));
+    config.block[0] = 256;
+    const void *left_pointer = reinterpret_cast<const void *>(left), *right_pointer = reinterpret_cast<const void *>(right);
+    void *left_out = reinterpret_cast<void *>(left_destination), *right_out = reinterpret_cast<void *>(right_destination);
+    long long left_stride = (long long)left_pitch, right_stride = (long long)right_pitch;
+    int left_count = int(left_rows), right_count = int(right_rows), depth = int(k);
+    void *arguments[9] = {&left_pointer, &left_stride, &left_out, &left_count, &right_pointer, &right_stride, &right_out, &right_count, &depth};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
 // The same split for a right operand stored k x n: written transposed, as the n x 3k array the product reads K-major.
 int split_tf32_transposed(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t n, uint64_t k) {
     gpurs_gpu *gpu = stream->gpu;
@@ -833,9 +854,12 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         CUdeviceptr scratch = 0;
         result = runtime::workspace_acquire(stream, a_split + b_split, &scratch);
         if (result != GPURS_OK) return result;
-        result = split_tf32(stream, a, lda, scratch, m, k, 0);
-        if (result == GPURS_OK) result = b_row_major ? split_tf32_transposed(stream, b, ldb, scratch + a_split, n, k)
-                                                     : split_tf32(stream, b, ldb, scratch + a_split, n, k, 1);
+        if (b_row_major) {
+            result = split_tf32(stream, a, lda, scratch, m, k, 0);
+            if (result == GPURS_OK) result = split_tf32_transposed(stream, b, ldb, scratch + a_split, n, k);
+        } else {
+            result = split_tf32_pair(stream, a, lda, scratch, m, b, ldb, scratch + a_split, n, k);
+        }
         gemm.b_row_major = false;     // the split copy is n x 3k whatever B was
         gemm.a = scratch, gemm.b = scratch + a_split;
         gemm.lda = gemm.ldb = 3 * k;

@@ -310,7 +310,7 @@ __device__ __forceinline__ void gemm_blockscaled_body(const CUtensorMap *map_a, 
                 }
             }
         }
-        if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
+        if (lane == 0) ptx::tma_store_wait_read<0>();   // the stores have read their source; the grid's completion orders their writes
     }
 
     // ---------------------------------------------------------------------- teardown

@@ -670,7 +670,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap *map_a, const CUtens
                 }
             }
         }
-        if (lane == 0) ptx::tma_store_wait<0>();   // this warp's stores have been performed before the block exits
+        if (lane == 0) {
+            // PUSH: the stores travel to other GPUs, and the kernel's completion is what tells the host they have been performed.
+            // Otherwise it is enough that the stores have read their shared-memory source before the block exits: the grid's
+            // completion orders their writes before whatever follows on the stream.
+            if constexpr (PUSH) ptx::tma_store_wait<0>();
+            else ptx::tma_store_wait_read<0>();
+        }
     }
 
     // ---------------------------------------------------------------------- teardown

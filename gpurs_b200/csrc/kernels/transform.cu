@@ -41,6 +41,38 @@ gpurs_split_tf32(const float *__restrict__ source, long long source_pitch, float
     }
 }
 
+// Both operands of a product in one launch (left operand order 0, right operand order 1): quads of the left operand first.
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_split_tf32_pair(const float *__restrict__ left, long long left_pitch, float *__restrict__ left_destination, int left_rows,
+                      const float *__restrict__ right, long long right_pitch, float *__restrict__ right_destination, int right_rows, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    const long long quads_per_row = k / 4;
+    const long long left_total = (long long)left_rows * quads_per_row, total = left_total + (long long)right_rows * quads_per_row;
+    for (long long index = blockIdx.x * (long long)blockDim.x + threadIdx.x; index < total; index += (long long)gridDim.x * blockDim.x) {
+        const bool is_left = index < left_total;
+        const long long local = is_left ? index : index - left_total;
+        const long long row = local / quads_per_row, quad = local - row * quads_per_row;
+        const float *source = is_left ? left + row * left_pitch : right + row * right_pitch;
+        const float4 x = *reinterpret_cast<const float4 *>(source + quad * 4);
+        float4 hi, lo;
+        uint32_t bits;
+#define GPURS_SPLIT(component)                                                              \
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x.component));                         \
+    hi.component = __uint_as_float(bits);                                                     \
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x.component - hi.component));          \
+    lo.component = __uint_as_float(bits);
+        GPURS_SPLIT(x)
+        GPURS_SPLIT(y)
+        GPURS_SPLIT(z)
+        GPURS_SPLIT(w)
+#undef GPURS_SPLIT
+        float *out = (is_left ? left_destination : right_destination) + row * 3ll * k + quad * 4;
+        *reinterpret_cast<float4 *>(out) = hi;
+        *reinterpret_cast<float4 *>(out + k) = is_left ? hi : lo;
+        *reinterpret_cast<float4 *>(out + 2ll * k) = is_left ? lo : hi;
+    }
+}
+
 // The same split for a right operand stored K x N (row-major B of C = A * B): tiles of 32 x 32 elements go through shared
 // memory, so that the reads run along N and the writes along K, and the destination is the N x 3K array [hi | lo | hi] the
 // product reads K-major.  Block = 32 x 8 threads, one tile per block and grid-stride step.
