@@ -8,6 +8,8 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <utility>
+#include <vector>
 
 namespace {
 
@@ -1017,7 +1019,17 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
     const bool by_columns = !in_one_piece && !b_row_major && n > m;
     const uint64_t extent = by_columns ? n : m;
     const uint64_t block_extent = (in_one_piece || extent <= 512) ? extent : std::max<uint64_t>(256, ((extent + 7) / 8 + 255) / 256 * 256);
-    const uint64_t blocks = (extent + block_extent - 1) / block_extent;
+    // The last block's product and its way back to the host follow the last copy in and overlap nothing: the blocks taper off at
+    // the end (the last full-size block goes as a half and two quarters, whole 256-wide tiles each).
+    std::vector<std::pair<uint64_t, uint64_t>> pieces;      // first row (or column) and extent of every block
+    for (uint64_t first = 0; first < extent;) {
+        const uint64_t left = extent - first;
+        uint64_t count = std::min(block_extent, left);
+        if (!in_one_piece && !pieces.empty() && left <= block_extent && left >= 512) count = ((left / 2 + 255) / 256) * 256;
+        pieces.emplace_back(first, count);
+        first += count;
+    }
+    const uint64_t blocks = pieces.size();
     int result = runtime::copy_pipeline(gpu, 2 * blocks + 3);
     if (result != GPURS_OK) return result;
     const driver::Api *api = gpu->api;
@@ -1070,7 +1082,7 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
     local.lda = lda, local.ldb = ldb, local.ldc = ldc;
     const uint64_t k_blocks = (k + 127) / 128;
     for (uint64_t block = 0; block < blocks && result == GPURS_OK; block++) {
-        const uint64_t first = block * block_extent, count = std::min(block_extent, extent - first);
+        const uint64_t first = pieces[block].first, count = pieces[block].second;
         CUevent arrived = events[3 + 2 * block], c_ready = events[4 + 2 * block];
         // where this block's operand rows and its part of C start, in bytes
         const uint64_t operand_offset = first * (by_columns ? ldb : lda) * eb;
