@@ -104,10 +104,22 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         if (checked != GPURS_OK) return checked;
     }
     const uint64_t wanted_ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
-    const uint64_t grid_clusters = std::min(std::max<uint64_t>(1, wanted_ctas / cta_group), std::max<uint64_t>(all_tiles, 1));
+    const uint64_t full_clusters = std::max<uint64_t>(1, wanted_ctas / cta_group);
+    uint64_t grid_clusters = std::min(full_clusters, std::max<uint64_t>(all_tiles, 1));
     const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
     const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull;
-    const int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
+    int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
+    // Fewer tiles than CTA groups and a deep K (the reference's SplitDepth case, crates/gpurs/src/gpu/tensor/schedule): every tile
+    // is split along K among up to STREAM_MAX_SHARE groups, which the same schedule expresses as "all tiles belong to the split
+    // round".  It must pay for the parts' trip through memory (about 30 K-blocks' time, as above).
+    if (may_split && split_tiles == 0 && !explicit_grid && all_tiles > 0 && all_tiles * 2 <= full_clusters && depth_blocks >= 2) {
+        const uint64_t shares = std::min<uint64_t>(std::min<uint64_t>(gemm::STREAM_MAX_SHARE, full_clusters / all_tiles), uint64_t(depth_blocks));
+        const uint64_t saved = uint64_t(depth_blocks) - (uint64_t(depth_blocks) + shares - 1) / shares;
+        if (shares >= 2 && (g.force_split || saved >= 40)) {
+            split_tiles = int(all_tiles);
+            grid_clusters = all_tiles * shares;
+        }
+    }
     gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
     bool stream_k = split_tiles > 0;
     // 256 x 512 tiles (kernels/gemm_wide_tcgen05.cuh): a quarter less operand traffic from L2 per flop, which is what bounds the
@@ -237,7 +249,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
     uint64_t ctas = wanted_ctas;
     uint64_t clusters = std::max<uint64_t>(1, ctas / cta_group);
-    clusters = std::min(clusters, tiles);
+    clusters = stream_k ? grid_clusters : std::min(clusters, tiles);      // a split round may use more groups than there are tiles
     gpurs_launch_config config;
     std::memset(&config, 0, sizeof config);
     config.grid[0] = uint32_t(clusters * cta_group);

@@ -74,6 +74,29 @@ def test_full_grid_shape_that_splits(gpu, stream):
     assert np.array_equal(got.reshape(size, size)[rows].astype(np.float64), O.matmul_rows(O.FMT_F16, a_bits, b_bits, size, size, rows))
 
 
+@pytest.mark.parametrize("algorithm", [G.ALGO_CTA_PAIR, G.ALGO_SINGLE_CTA])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 16384), (520, 300, 8192), (128, 256, 12288)])
+def test_few_tiles_and_a_deep_k_are_split_among_idle_groups(gpu, stream, algorithm, m, n, k):
+    """Fewer tiles than CTA groups, K thousands deep (the reference's SplitDepth case): every tile's K-blocks go to up to four
+    groups.  Integers: bit-equal to the whole-tile product and the oracle; the example's exact inputs: bit-equal; floats: within
+    tolerance and the same bits on every run."""
+    a_bits, b_bits = make_operands("i8", m, n, k)
+    whole = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES)
+    for _ in range(2):
+        got = run_matmul(gpu, stream, "i8", "i32", a_bits, b_bits, m, n, k, algorithm=algorithm)
+        assert np.array_equal(got, whole)
+    rows = np.arange(0, m, 37)
+    assert np.array_equal(got.reshape(m, n)[rows].astype(np.int64), O.matmul_rows(O.FMT_I8, a_bits, b_bits, n, k, rows).astype(np.int64))
+    a_bits, b_bits = make_operands("f16", m, n, k, pattern="example")
+    assert np.array_equal(run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm),
+                          run_matmul(gpu, stream, "f16", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES))
+    a_bits, b_bits = make_operands("bf16", m, n, k)
+    got = run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, m, n, k, algorithm=algorithm)
+    assert relative_error(decode_output(got, "bf16").reshape(m, n)[rows], O.matmul_rows(O.FMT_BF16, a_bits, b_bits, n, k, rows)) <= 1e-2
+    assert np.array_equal(got, run_matmul(gpu, stream, "bf16", "bf16", a_bits, b_bits, m, n, k, algorithm=algorithm))
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_unknown_algorithm_bits_are_refused(gpu, stream):
     a_bits, b_bits = make_operands("bf16", 128, 128, 64)
     for algorithm in (0x1000, G.ALGO_WHOLE_TILES | G.ALGO_SPLIT_LAST_ROUND, G.ALGO_WIDE_TILES | G.ALGO_SQUARE_TILES):
