@@ -33,6 +33,8 @@ struct Gemm {
     bool b_row_major = false;                    // B stored k x n
     int l2_policy = 0;                           // Params::l2_policy
     gpurs_device_ptr metadata = 0;               // 2:4-sparse A only: `a` then holds the kept values, k the logical depth
+    gpurs_device_ptr partials = 0;               // room for the parts of tiles split along K, if the caller already holds the workspace
+    uint64_t partials_bytes = 0;
     const gpurs_gather_desc *gather = nullptr;   // push epilogue: C is a block of rows of a matrix kept on every GPU of the box
 };
 

@@ -89,25 +89,34 @@ bool overlap(uint64_t a, uint64_t a_bytes, uint64_t b, uint64_t b_bytes) { retur
 
 using launcher::Gemm;
 
-int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
-    gpurs_gpu *gpu = stream->gpu;
-    const int cta_group = g.cta_group;
-    const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
-    char name[96];
-    const bool batched = g.batches > 1;
-    // Stream-K: decided here from the tile count and the grid, by the same arithmetic the kernel uses to find its work.
-    const uint64_t tile_rows_ = uint64_t(gemm::BLOCK_M) * cta_group;
-    const uint64_t all_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
-    uint64_t explicit_grid = 0;
-    {
-        const int checked = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(g.threads), shared_for(g), explicit_grid);
-        if (checked != GPURS_OK) return checked;
+namespace {
+
+// How a dense or promoted tile product divides its tiles over the grid: which tiles (if any) are split along K.
+struct SplitPlan {
+    uint64_t all_tiles, wanted_ctas, grid_clusters;
+    int depth_blocks, split_tiles;
+    bool promoted_kernel;
+    gemm::StreamSchedule schedule;
+    // scratch for the parts of the split tiles
+    size_t partial_bytes(int cta_group) const {
+        return split_tiles > 0 ? size_t(schedule.split_tiles) * gemm::max_contributors(schedule) * (size_t(gemm::BLOCK_M) * cta_group) * gemm::BLOCK_N * 4 : 0;
     }
+};
+
+SplitPlan plan_split(const gpurs_gpu *gpu, const Gemm &g, uint64_t explicit_grid) {
+    SplitPlan plan;
+    const int cta_group = g.cta_group;
+    const uint64_t eb = uint64_t(g.element_bytes);
+    const bool batched = g.batches > 1;
+    const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
+    const uint64_t all_tiles = ((g.m + tile_rows - 1) / tile_rows) * ((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
     const uint64_t wanted_ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     const uint64_t full_clusters = std::max<uint64_t>(1, wanted_ctas / cta_group);
     uint64_t grid_clusters = std::min(full_clusters, std::max<uint64_t>(all_tiles, 1));
     const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
-    const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && g.threads == gemm::NUM_THREADS && all_tiles <= 0x7fffffffull;
+    const bool promoted_kernel = g.metadata == 0 && g.threads == gemm::SCALED_THREADS;      // promotes every K-block to registers: same schedule
+    const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && (g.threads == gemm::NUM_THREADS || promoted_kernel) &&
+                           all_tiles <= 0x7fffffffull;
     int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
     // Fewer tiles than CTA groups and a deep K (the reference's SplitDepth case, crates/gpurs/src/gpu/tensor/schedule): every tile
     // is split along K among up to STREAM_MAX_SHARE groups, which the same schedule expresses as "all tiles belong to the split
@@ -120,7 +129,32 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
             grid_clusters = all_tiles * shares;
         }
     }
-    gemm::StreamSchedule schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
+    plan.all_tiles = all_tiles, plan.wanted_ctas = wanted_ctas, plan.grid_clusters = grid_clusters;
+    plan.depth_blocks = depth_blocks, plan.split_tiles = split_tiles, plan.promoted_kernel = promoted_kernel;
+    plan.schedule = gemm::make_stream_schedule(int(std::min<uint64_t>(all_tiles, 0x7fffffff)), depth_blocks, int(grid_clusters), split_tiles);
+    return plan;
+}
+
+}  // namespace
+
+int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
+    gpurs_gpu *gpu = stream->gpu;
+    const int cta_group = g.cta_group;
+    const uint64_t eb = uint64_t(g.element_bytes), ob = uint64_t(g.output_bytes);
+    char name[96];
+    const bool batched = g.batches > 1;
+    // Stream-K: decided here from the tile count and the grid, by the same arithmetic the kernel uses to find its work.
+    const uint64_t tile_rows_ = uint64_t(gemm::BLOCK_M) * cta_group;
+    uint64_t explicit_grid = 0;
+    {
+        const int checked = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(g.threads), shared_for(g), explicit_grid);
+        if (checked != GPURS_OK) return checked;
+    }
+    const SplitPlan plan = plan_split(gpu, g, explicit_grid);
+    const uint64_t all_tiles = plan.all_tiles, wanted_ctas = plan.wanted_ctas, grid_clusters = plan.grid_clusters;
+    const int depth_blocks = plan.depth_blocks, split_tiles = plan.split_tiles;
+    const bool promoted_kernel = plan.promoted_kernel;
+    const gemm::StreamSchedule schedule = plan.schedule;
     bool stream_k = split_tiles > 0;
     // 256 x 512 tiles (kernels/gemm_wide_tcgen05.cuh): a quarter less operand traffic from L2 per flop, which is what bounds the
     // 256 x 256 tiles.  Plain products on CTA pairs, n x k right operand, C rows on 16-byte boundaries.  By default they are used
@@ -158,7 +192,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? (algebra ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? ((algebra && !promoted_kernel) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
@@ -309,13 +343,16 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     if (stream_k) {
         // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch
         const int most = gemm::max_contributors(schedule);
-        const size_t partial_bytes = size_t(schedule.split_tiles) * most * tile_rows * gemm::BLOCK_N * 4;
-        CUdeviceptr partials = 0, counters = 0;
-        result = runtime::workspace_acquire(stream, partial_bytes, &partials);
+        const size_t partial_bytes = plan.partial_bytes(cta_group);
+        CUdeviceptr partials = g.partials, counters = 0;
+        const bool borrowed_here = partials == 0;       // a caller that holds the workspace already passes its own room for the parts
+        if (!borrowed_here && g.partials_bytes < partial_bytes) return fail("gpurs_matmul", GPURS_E_INVALID_ARGUMENT, "too little room for the partial tiles");
+        if (borrowed_here) result = runtime::workspace_acquire(stream, partial_bytes, &partials);
         if (result != GPURS_OK) return result;
-        result = runtime::turns_acquire(stream, std::max<size_t>(size_t(schedule.split_tiles) * 4 * cta_group * sizeof(uint32_t), 4096), &counters);
+        // one arrival counter per tile and warp that finishes rows of it: 4 epilogue warps per CTA, 8 promotion warps
+        result = runtime::turns_acquire(stream, std::max<size_t>(size_t(schedule.split_tiles) * (promoted_kernel ? 8 : 4) * cta_group * sizeof(uint32_t), 4096), &counters);
         if (result != GPURS_OK) {
-            runtime::workspace_release(stream);     // nothing was enqueued: the next borrower need not wait for this one
+            if (borrowed_here) runtime::workspace_release(stream);     // nothing was enqueued: the next borrower need not wait for this one
             return result;
         }
         params.partials = reinterpret_cast<void *>(partials);
@@ -323,8 +360,9 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         params.max_contributors = most;
         params.split_tiles = split_tiles;
         void *stream_arguments[4] = {&map_a, &map_b, &map_c, &params};
-        result = runtime::launch(kernel, stream, &config, stream_arguments, true);
-        const int released = runtime::workspace_release(stream), turned = runtime::turns_release(stream);
+        void *promoted_arguments[3] = {&map_a, &map_b, &params};
+        result = runtime::launch(kernel, stream, &config, promoted_kernel ? promoted_arguments : stream_arguments, true);
+        const int released = borrowed_here ? runtime::workspace_release(stream) : GPURS_OK, turned = runtime::turns_release(stream);
         return result != GPURS_OK ? result : released != GPURS_OK ? released : turned;
     }
     void *arguments[3] = {&map_a, &map_b, &params};
@@ -755,9 +793,11 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (group == GPURS_ALGO_AUTO && desc->launch && (desc->launch->cluster[0] == 1 || desc->launch->cluster[0] == 2) && !promoted)
         group = desc->launch->cluster[0] == 2 ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group == GPURS_ALGO_AUTO && skinny_possible && !desc->launch) group = GPURS_ALGO_SKINNY;
-    // The fp32 (three-pass TF32) product stays on one-CTA tiles; the block-scaled FP8 product has a CTA-pair kernel of its own
-    // (four accumulators in flight) that outruns the one-CTA one wherever a pair tile has two row blocks to work on.
-    if (group == GPURS_ALGO_AUTO) group = (m > 128 && (!promoted || (desc->scale_a != 0 && !desc->accumulate))) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
+    // The promoted products (fp32 as three TF32 passes, block-scaled FP8) stay on one-CTA tiles: their accumulator hand-offs then
+    // never cross to another CTA.  The block-scaled product also has a CTA-pair kernel (four accumulators in flight, chosen with
+    // GPURS_ALGO_CTA_PAIR); measured side by side on one box it is the slower one (4096 x 7168 x 7168: 1745-1755 against
+    // 1882-1913 TFLOP/s; 8192^3: 1950 against 2075).
+    if (group == GPURS_ALGO_AUTO) group = (m > 128 && !promoted) ? GPURS_ALGO_CTA_PAIR : GPURS_ALGO_SINGLE_CTA;
     if (group != GPURS_ALGO_SINGLE_CTA && group != GPURS_ALGO_CTA_PAIR && group != GPURS_ALGO_SKINNY)
         return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown algorithm");
     if (desc->bias && desc->c_type == GPURS_I32) return fail(op, GPURS_E_INVALID_ARGUMENT, "a bias is for floating-point outputs");
@@ -865,19 +905,25 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
             result = explicit_ctas(op, desc->launch, gemm.cta_group, uint32_t(gemm.threads), shared_for(gemm), unused);
             if (result != GPURS_OK) return result;
         }
+        // the product may split tiles along K: the parts share the borrowed workspace with the split operands
+        gemm.lda = gemm.ldb = 3 * k;
+        gemm.k = 3 * k;
+        gemm.b_row_major = false;     // the split copy is n x 3k whatever B was
+        uint64_t explicit_grid = 0;
+        explicit_ctas(op, desc->launch, gemm.cta_group, uint32_t(gemm.threads), shared_for(gemm), explicit_grid);
+        const uint64_t operands = (a_split + b_split + 255) / 256 * 256;
+        const size_t parts = plan_split(gpu, gemm, explicit_grid).partial_bytes(gemm.cta_group);
         CUdeviceptr scratch = 0;
-        result = runtime::workspace_acquire(stream, a_split + b_split, &scratch);
+        result = runtime::workspace_acquire(stream, operands + parts, &scratch);
         if (result != GPURS_OK) return result;
+        gemm.partials = parts ? scratch + operands : 0, gemm.partials_bytes = parts;
         if (b_row_major) {
             result = split_tf32(stream, a, lda, scratch, m, k, 0);
             if (result == GPURS_OK) result = split_tf32_transposed(stream, b, ldb, scratch + a_split, n, k);
         } else {
             result = split_tf32_pair(stream, a, lda, scratch, m, b, ldb, scratch + a_split, n, k);
         }
-        gemm.b_row_major = false;     // the split copy is n x 3k whatever B was
         gemm.a = scratch, gemm.b = scratch + a_split;
-        gemm.lda = gemm.ldb = 3 * k;
-        gemm.k = 3 * k;
         // The tensor core's fp32 accumulator truncates after every instruction; promoting each K-block to
         // registers keeps the sum round-to-nearest, which the 1e-4 bound needs once K reaches thousands.
         gemm.stem = "gpurs_gemm_tf32_promoted_f32";

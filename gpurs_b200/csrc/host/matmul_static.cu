@@ -130,5 +130,6 @@ extern "C" int gpurs_matmul_f32_static(gpurs_stream *stream, uint64_t m, uint64_
     gemm.raster_rows = 0;
     gemm.max_ctas = 0;
     gemm.threads = gemm::SCALED_THREADS;
+    gemm.whole_tiles = true;      // tiles split along K would borrow the handle's workspace, which is allocated memory
     return launcher::launch_gemm(stream, gemm);
 }

@@ -28,7 +28,10 @@ constexpr int SCALE_BLOCK = 128;             // K-depth and B-row extent of one 
 // accumulator of the tensor core truncates after every instruction, so a long K loop drifts towards
 // zero, while sums promoted to registers every K-block are added with round-to-nearest.  The fp32
 // (three-pass TF32) product uses the unscaled form.
-template <int KIND, int ELEMENT_FORMAT, int OUT, bool SCALED, int CTA_GROUP, int STAGES>
+// STREAMK: the K-blocks of the tiles of a split round are spread over the CTA groups (gemm_schedule.hpp), as in gemm_body: a
+// group's share of a tile is promoted like a whole tile, written to scratch as a 32-bit partial tile, and whichever
+// promotion warp brings the last part of its 32 rows x 128 columns adds the parts in the contributors' order and stores.
+template <int KIND, int ELEMENT_FORMAT, int OUT, bool SCALED, int CTA_GROUP, int STAGES, bool STREAMK = false>
 __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const Params &p) {
     constexpr int BN = BLOCK_N;
     using L = SharedLayout<BN, CTA_GROUP, STAGES>;
@@ -111,12 +114,15 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
                 int tile_m, tile_n;
                 tile_position(tile, p, tile_m, tile_n);
                 const int row_a = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M;
                 const int row_b = tile_n * BN + int(cta_rank) * L::B_ROWS;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
                     if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
                         ok = false;
@@ -150,8 +156,11 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             bool ok = true;
             const uint64_t a_desc0 = ptx::smem_descriptor_k_major_sw128(stage_a(0)), b_desc0 = ptx::smem_descriptor_k_major_sw128(stage_b(0));
             constexpr uint64_t STAGE_STEP = uint64_t(L::STAGE_BYTES >> 4);
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
-                for (int first = 0; first < k_blocks && ok; first += PERIOD) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
+                for (int first = item.kb_begin; first < item.kb_end && ok; first += PERIOD) {
                     // one accumulator takes PERIOD K-blocks, then goes to the promotion warps
                     const int slot = acc * 2;
                     if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(slot), acc_phase ^ 1, abort_flag)) {
@@ -161,7 +170,7 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                     }
                     ptx::tcgen05_fence_after();
                     const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
-                    const int last = min(first + PERIOD, k_blocks);
+                    const int last = min(first + PERIOD, item.kb_end);
                     for (int kb = first; kb < last; kb++) {
                         if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                             report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
@@ -197,7 +206,10 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
         uint32_t acc_phase = 0;
         int release_stage = 0;
         bool ok = true;
-        for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+        WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+        WorkItem item;
+        while (ok && walker.next(item)) {
+            const int tile = item.tile;
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
@@ -207,11 +219,12 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
             float sums[SCALE_BLOCK];
 #pragma unroll
             for (int i = 0; i < SCALE_BLOCK; i++) sums[i] = 0.0f;
-            float scale = SCALED ? __ldg(row_scales) * __ldg(block_scales) : 1.0f;
+            float scale = SCALED ? __ldg(row_scales + item.kb_begin) * __ldg(block_scales + item.kb_begin) : 1.0f;
             // Scales are fetched two blocks ahead and multiplied one block ahead: a warp issues in order, and a product placed
             // right behind its loads would hold the warp for the whole trip to L2.
-            float row_part = SCALED ? __ldg(row_scales + min(1, k_blocks - 1)) : 1.0f, block_part = SCALED ? __ldg(block_scales + min(1, k_blocks - 1)) : 1.0f;
-            for (int kb = 0; kb < k_blocks; kb += PERIOD) {
+            const int second = min(item.kb_begin + 1, k_blocks - 1);
+            float row_part = SCALED ? __ldg(row_scales + second) : 1.0f, block_part = SCALED ? __ldg(block_scales + second) : 1.0f;
+            for (int kb = item.kb_begin; kb < item.kb_end; kb += PERIOD) {
                 const float next_scale = row_part * block_part;
                 if constexpr (SCALED) {
                     const int ahead = min(kb + 2, k_blocks - 1);
@@ -258,12 +271,56 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                 scale = next_scale;
             }
             if (!ok) break;
+            if (STREAMK && item.split_tile >= 0) {
+                // This group multiplied only its share of the tile's K-blocks: the sums go to scratch as one part of the tile, laid
+                // out as in gemm_body ([group of four columns][row] x 16 bytes), and the warp that brings the last part of these
+                // 32 rows x 128 columns adds the parts up in the contributors' order and stores.  Nobody waits for anybody.
+                constexpr int TILE_ROWS = BLOCK_M * CTA_GROUP;
+                constexpr size_t PART = size_t(TILE_ROWS) * BN / 4;      // one part, in 16-byte units
+                const int row_in_tile = int(cta_rank) * BLOCK_M + quadrant * 32 + int(lane);
+                uint4 *parts = reinterpret_cast<uint4 *>(p.partials) + size_t(item.split_tile) * p.max_contributors * PART + size_t(half) * (SCALE_BLOCK / 4) * TILE_ROWS +
+                               row_in_tile;
+                uint4 *mine = parts + size_t(item.contributor) * PART;
 #pragma unroll
-            for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
-                uint32_t values[32];
+                for (int i = 0; i < SCALE_BLOCK / 4; i++)
+                    mine[size_t(i) * TILE_ROWS] = make_uint4(__float_as_uint(sums[4 * i]), __float_as_uint(sums[4 * i + 1]), __float_as_uint(sums[4 * i + 2]),
+                                                             __float_as_uint(sums[4 * i + 3]));
+                unsigned int *counter = p.split_counters + item.split_tile * (8 * CTA_GROUP) + int(cta_rank) * 8 + half * 4 + quadrant;
+                __threadfence();
+                __syncwarp();
+                unsigned int earlier = 0;
+                if (lane == 0) earlier = atomicAdd(counter, 1u);
+                earlier = __shfl_sync(0xffffffffu, earlier, 0);
+                if (earlier == unsigned(item.contributors - 1)) {
+                    __threadfence();
+                    if (lane == 0) *counter = 0;       // ready for the next launch
+#pragma unroll 1
+                    for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
+                        uint32_t sum[32];
 #pragma unroll
-                for (int i = 0; i < 32; i++) values[i] = __float_as_uint(sums[chunk * 32 + i]);
-                store_chunk<OUT>(p, values, row, column + chunk * 32);
+                        for (int i = 0; i < 32; i++) sum[i] = 0;    // +0.0f: the first part is added to it exactly
+                        for (int q = 0; q < item.contributors; q++) {
+                            uint4 loaded[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) loaded[i] = __ldcg(parts + size_t(q) * PART + size_t(chunk * 8 + i) * TILE_ROWS);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const uint32_t w[4] = {loaded[i].x, loaded[i].y, loaded[i].z, loaded[i].w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) sum[4 * i + j] = __float_as_uint(__fadd_rn(__uint_as_float(sum[4 * i + j]), __uint_as_float(w[j])));
+                            }
+                        }
+                        store_chunk<OUT>(p, sum, row, column + chunk * 32);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int chunk = 0; chunk < SCALE_BLOCK / 32; chunk++) {
+                    uint32_t values[32];
+#pragma unroll
+                    for (int i = 0; i < 32; i++) values[i] = __float_as_uint(sums[chunk * 32 + i]);
+                    store_chunk<OUT>(p, values, row, column + chunk * 32);
+                }
             }
         }
     }
