@@ -97,6 +97,44 @@ def test_few_tiles_and_a_deep_k_are_split_among_idle_groups(gpu, stream, algorit
     assert gpu.status() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("algorithm,max_ctas,m,n", GEOMETRIES[1:])
+def test_promoted_products_split_the_same_way(gpu, stream, algorithm, max_ctas, m, n):
+    """The kernels that promote every K-block to registers (fp32 as three TF32 passes, block-scaled FP8) take part in the same
+    schedule: a group's share of a tile goes to scratch and the last promotion warp adds the parts in order.  fp32: within 1e-4
+    of fp64 and within 1e-5 of the whole-tile product; FP8: within the configuration's 2e-2 / 1e-4; the same bits on every run."""
+    k = 1024
+    a_bits, b_bits = make_operands("f32", m, n, k)
+    split = dict(algorithm=algorithm | G.ALGO_SPLIT_LAST_ROUND, max_ctas=max_ctas)
+    got = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, **split)
+    whole = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, algorithm=algorithm | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
+    rows = np.arange(0, m, 29)
+    assert relative_error(got.reshape(m, n)[rows].astype(np.float64), O.matmul_rows(O.FMT_F32, a_bits, b_bits, n, k, rows)) <= 1e-4
+    assert relative_error(got.astype(np.float64), whole.astype(np.float64)) <= 1e-5
+    assert np.array_equal(got, run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, **split))
+    a_source, b_source = O.fill_normal_f32(m * k, 3), O.fill_normal_f32(n * k, 4)
+    a_codes, sa = O.quantize_e4m3(a_source, m, k, 1)
+    b_codes, sb = O.quantize_e4m3(b_source, n, k, 128)
+    scales = dict(scale_a=gpu.upload(sa), scale_b=gpu.upload(sb))
+    expected = O.matmul_rows(O.FMT_E4M3, a_codes, b_codes, n, k, rows, sa, sb)
+    for out, tolerance in (("f32", 1e-4), ("bf16", 2e-2)):
+        got = run_matmul(gpu, stream, "e4m3", out, a_codes, b_codes, m, n, k, **split, **scales)
+        assert relative_error(decode_output(got, out).reshape(m, n)[rows], expected) <= tolerance
+        assert np.array_equal(got, run_matmul(gpu, stream, "e4m3", out, a_codes, b_codes, m, n, k, **split, **scales))
+    assert gpu.status() == [0, 0, 0, 0]
+
+
+def test_fp32_split_depth(gpu, stream):
+    """The fp32 configuration's shape class: few one-CTA tiles, 3k deep: split among idle CTAs by default."""
+    m, n, k = 256, 512, 4096
+    a_bits, b_bits = make_operands("f32", m, n, k)
+    got = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k)
+    whole = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, algorithm=G.ALGO_WHOLE_TILES)
+    rows = np.arange(0, m, 7)
+    assert relative_error(got.reshape(m, n)[rows].astype(np.float64), O.matmul_rows(O.FMT_F32, a_bits, b_bits, n, k, rows)) <= 1e-4
+    assert relative_error(got.astype(np.float64), whole.astype(np.float64)) <= 1e-5
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_unknown_algorithm_bits_are_refused(gpu, stream):
     a_bits, b_bits = make_operands("bf16", 128, 128, 64)
     for algorithm in (0x1000, G.ALGO_WHOLE_TILES | G.ALGO_SPLIT_LAST_ROUND, G.ALGO_WIDE_TILES | G.ALGO_SQUARE_TILES):
