@@ -636,6 +636,25 @@ int split_tf32_transposed(gpurs_stream *stream, gpurs_device_ptr source, uint64_
     return runtime::launch(kernel, stream, &config, arguments, true);
 }
 
+// A k x n right operand copied as n x k (pitch k) for the kernels that read B K-major only.
+int transpose_copy(gpurs_stream *stream, gpurs_device_ptr source, uint64_t pitch, gpurs_device_ptr destination, uint64_t n, uint64_t k, uint64_t element_bytes) {
+    gpurs_gpu *gpu = stream->gpu;
+    gpurs_kernel *kernel = nullptr;
+    int result = runtime::builtin_kernel(gpu, element_bytes == 1 ? "gpurs_transpose_b8" : element_bytes == 2 ? "gpurs_transpose_b16" : "gpurs_transpose_b32", 0, &kernel);
+    if (result != GPURS_OK) return result;
+    const uint64_t tiles = ((n + 31) / 32) * ((k + 31) / 32);
+    gpurs_launch_config config;
+    std::memset(&config, 0, sizeof config);
+    config.grid[0] = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(tiles, uint64_t(gpu->multiprocessors) * 8)));
+    config.block[0] = 256;
+    const void *source_pointer = reinterpret_cast<const void *>(source);
+    void *destination_pointer = reinterpret_cast<void *>(destination);
+    long long source_pitch = (long long)pitch;
+    int columns = int(n), depth = int(k);
+    void *arguments[5] = {&source_pointer, &source_pitch, &destination_pointer, &columns, &depth};
+    return runtime::launch(kernel, stream, &config, arguments, true);
+}
+
 }  // namespace
 
 namespace {
@@ -712,6 +731,27 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     if (desc->scale_a && desc->a_type != GPURS_E4M3) return fail(op, GPURS_E_INVALID_ARGUMENT, "scales are for E4M3 operands only");
     if (desc->scale_a && (desc->scale_a % 4 || desc->scale_b % 4)) return fail(op, GPURS_E_INVALID_VIEW, "scale arrays must be 4-byte aligned");
     if (desc->scale_kind != GPURS_SCALES_FP32_BLOCKS && desc->scale_kind != GPURS_SCALES_MX) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown scale kind");
+    // A k x n right operand (the reference's row-major B of C = A * B): the dense 16-bit and 8-bit kernels read it in place and
+    // the full-precision fp32 product transposes it while splitting it; every other kernel (2:4-sparse, scaled FP8, one-pass
+    // TF32) reads B K-major only and gets a transposed copy in the handle's workspace first, then runs as an n x k product on
+    // whole tiles (tiles split along K would need the workspace as well).
+    if (b_row_major && gpu && !gather && batches == 1 &&
+        (sparse || desc->scale_a != 0 || (desc->a_type == GPURS_F32 && desc->precision != GPURS_PRECISION_DEFAULT))) {
+        if ((k * eb) % 16) return fail(op, GPURS_E_INVALID_VIEW, "operand bases and row pitches must be multiples of 16 bytes");
+        if (m == 0 || n == 0 || k == 0) return GPURS_OK;
+        if (n > (1ull << 40) / k) return fail(op, GPURS_E_SIZE_OVERFLOW, "the transposed copy of the right operand would exceed 2^40 elements");
+        gpurs_matmul_desc local = *desc;
+        local.b_row_major = 0, local.ldb = 0, local.b_len = 0;
+        local.algorithm = (local.algorithm & ~GPURS_ALGO_SPLIT_LAST_ROUND) | GPURS_ALGO_WHOLE_TILES;
+        runtime::Enter enter(gpu);
+        CUdeviceptr copy = 0;
+        int result = runtime::workspace_acquire(stream, n * k * eb, &copy);
+        if (result != GPURS_OK) return result;
+        result = transpose_copy(stream, b, ldb, copy, n, k, eb);
+        if (result == GPURS_OK) result = matmul_checked(op, stream, &local, a, copy, c, nullptr);
+        const int released = runtime::workspace_release(stream);
+        return result != GPURS_OK ? result : released;
+    }
     if (desc->scale_kind == GPURS_SCALES_MX) {
         // Power-of-two scales per 32 elements, applied by the tensor core: its own kernel, dispatched here.
         if (!desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "both scale arrays or neither must be given");
@@ -1073,7 +1113,9 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
     // of C), whole 256-wide tiles each; every block is multiplied when it has arrived and its part of C starts back at
     // once.  Products that prepare B per call (fp32 operands, whose split copy of B would be rebuilt for every block)
     // and small ones go in one piece.
-    const bool in_one_piece = desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT;
+    // (a k x n right operand of a kernel that reads B K-major only is copied transposed per call as well)
+    const bool in_one_piece = (desc->a_type == GPURS_F32 && desc->precision == GPURS_PRECISION_DEFAULT) ||
+                              (b_row_major && (desc->metadata != 0 || desc->scale_a != 0 || desc->a_type == GPURS_F32));
     const bool by_columns = !in_one_piece && !b_row_major && n > m;
     const uint64_t extent = by_columns ? n : m;
     const uint64_t block_extent = (in_one_piece || extent <= 512) ? extent : std::max<uint64_t>(256, ((extent + 7) / 8 + 255) / 256 * 256);

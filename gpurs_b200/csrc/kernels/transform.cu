@@ -108,6 +108,46 @@ gpurs_split_tf32_transposed(const float *__restrict__ source, long long source_p
     }
 }
 
+// A right operand stored K x N copied as N x K (what the kernels without an N-major read take): tiles of 32 x 32 elements
+// through shared memory, reads along N, writes along K.  Block = 32 x 8 threads, one tile per block and grid-stride step.
+template <typename T>
+__device__ __forceinline__ void transpose_body(const T *__restrict__ source, long long source_pitch, T *__restrict__ destination, int n, int k) {
+    __shared__ T tile[32][33];
+    const int tiles_n = (n + 31) / 32, tiles_k = (k + 31) / 32;
+    const int x = threadIdx.x % 32, y = threadIdx.x / 32;
+    for (long long t = blockIdx.x; t < (long long)tiles_n * tiles_k; t += gridDim.x) {
+        const int tile_k = int(t / tiles_n), tile_n = int(t - (long long)tile_k * tiles_n);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int kk = tile_k * 32 + y + 8 * i, nn = tile_n * 32 + x;
+            if (kk < k && nn < n) tile[y + 8 * i][x] = source[kk * source_pitch + nn];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int nn = tile_n * 32 + y + 8 * i, kk = tile_k * 32 + x;
+            if (nn < n && kk < k) destination[(long long)nn * k + kk] = tile[x][y + 8 * i];
+        }
+        __syncthreads();
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_transpose_b8(const uint8_t *__restrict__ source, long long source_pitch, uint8_t *__restrict__ destination, int n, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    transpose_body(source, source_pitch, destination, n, k);
+}
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_transpose_b16(const uint16_t *__restrict__ source, long long source_pitch, uint16_t *__restrict__ destination, int n, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    transpose_body(source, source_pitch, destination, n, k);
+}
+extern "C" __global__ void __launch_bounds__(256)
+gpurs_transpose_b32(const uint32_t *__restrict__ source, long long source_pitch, uint32_t *__restrict__ destination, int n, int k) {
+    GPURS_AFTER_PREVIOUS_KERNEL();
+    transpose_body(source, source_pitch, destination, n, k);
+}
+
 #include "gemm_sparse_tcgen05.cuh"
 
 // 2:4 compression of a 16-bit matrix (no counterpart in the reference, which has no sparse path).  One

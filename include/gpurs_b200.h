@@ -244,8 +244,11 @@ typedef struct gpurs_matmul_desc {
     int32_t l2_policy;               /* L2 residency hint of the operand loads (dense kernels): 0 library default,
                                         1 keep A / stream B, 2 stream A / keep B, 3 keep both, 4 no hints */
     int32_t b_row_major;             /* 0: B is n x k, k contiguous (the reference's "right_transposed" operand); 1: B is k x n,
-                                        n contiguous (C = A * B with all three row-major), ldb >= n; dense 16-bit and 8-bit tile
-                                        kernels only */
+                                        n contiguous (C = A * B with all three row-major), ldb >= n.  The dense 16-bit and 8-bit
+                                        tile kernels read it in place and the full-precision fp32 product transposes it while
+                                        splitting it; the other kernels (2:4-sparse, scaled FP8, one-pass TF32) get a transposed
+                                        copy in the handle's workspace first (one more launch; k * element size a multiple of
+                                        16 bytes; single products, not the gathering one) */
     gpurs_device_ptr bias;           /* optional fp32 [n] added to every row of C before the output rounding (float outputs;
                                         the epilogue of the reference's skinny example, examples/ada/examples/skinny_matrix.rs:60-64) */
     /* More epilogue algebra for float outputs, the steps the reference offers on accumulator tiles (`scale`, `scale_rows`,

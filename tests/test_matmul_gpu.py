@@ -249,11 +249,30 @@ def test_row_major_right_operand_with_pitch(gpu, stream):
     padded.reshape(k, ldb)[:, :n] = b.reshape(n, k).T
     got = decode_output(run_matmul(gpu, stream, "bf16", "f32", a, padded, m, n, k, G.ALGO_AUTO, b_row_major=True, ldb=ldb), "f32")
     assert relative_error(got.reshape(m, n), O.matmul_rows(O.FMT_BF16, a, b, n, k, np.arange(m))) <= 1e-3
+
+
+@pytest.mark.parametrize("shape", [(256, 264, 192), (129, 300, 1024), (520, 1100, 384)])
+def test_row_major_right_operand_of_the_k_major_only_kernels(gpu, stream, shape):
+    """One-pass TF32 and block-scaled FP8 read B K-major only: a k x n operand (with a pitch) is copied transposed into the
+    handle's workspace first, and the product equals the n x k call bit for bit."""
+    m, n, k = shape
+    ldb = n + 8
     fa, fb = make_operands("f32", m, n, k)
-    with pytest.raises(G.GpursError) as raised:           # one TF32 pass reads 32-bit operands n x k only
-        run_matmul(gpu, stream, "f32", "f32", fa, np.ascontiguousarray(fb.reshape(n, k).T).reshape(-1), m, n, k, G.ALGO_AUTO, b_row_major=True,
-                   precision=G.PRECISION_TF32)
-    assert raised.value.code == 100009
+    padded = np.full(k * ldb, np.nan, np.float32)
+    padded.reshape(k, ldb)[:, :n] = fb.reshape(n, k).T
+    expected = run_matmul(gpu, stream, "f32", "f32", fa, fb, m, n, k, G.ALGO_AUTO, precision=G.PRECISION_TF32)
+    got = run_matmul(gpu, stream, "f32", "f32", fa, padded, m, n, k, G.ALGO_AUTO, b_row_major=True, ldb=ldb, precision=G.PRECISION_TF32)
+    assert np.array_equal(got, expected)
+    if k % 128 == 0:
+        a, sa, b, sb = scaled_operands(m, n, k, seed=9)
+        scales = dict(scale_a=gpu.upload(sa), scale_b=gpu.upload(sb))
+        ldb = (n + 15) // 16 * 16 + 16              # row pitches stay multiples of 16 bytes
+        wide = np.full(k * ldb, 0x7F, np.uint8)
+        wide.reshape(k, ldb)[:, :n] = b.reshape(n, k).T
+        for algorithm in ALGORITHMS:
+            expected = run_matmul(gpu, stream, "e4m3", "bf16", a, b, m, n, k, algorithm, **scales)
+            assert np.array_equal(run_matmul(gpu, stream, "e4m3", "bf16", a, wide, m, n, k, algorithm, b_row_major=True, ldb=ldb, **scales), expected)
+    assert gpu.status() == [0, 0, 0, 0]
 
 
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (200, 301, 132), (129, 64, 2048)])

@@ -105,7 +105,7 @@ def test_what_the_mx_product_rejects(gpu, stream):
     assert code(scale_a=sa, scale_b=sb) == 0
     assert code() == _ffi.E_INVALID_ARGUMENT                                    # no scales
     assert code(scale_a=sa, scale_b=sb, algorithm=G.ALGO_SKINNY) == _ffi.E_INVALID_ARGUMENT
-    assert code(scale_a=sa, scale_b=sb, b_row_major=True) == _ffi.E_INVALID_ARGUMENT
+    assert code(scale_a=sa, scale_b=sb, b_row_major=True) == 0                  # k x n right operand: copied transposed first
     assert code(shape=(m, n, 96), scale_a=sa, scale_b=sb) == _ffi.E_INVALID_VIEW  # depth not a multiple of 128
     assert code(scale_a=sa, scale_b=sb, batches=2) in (_ffi.E_INVALID_ARGUMENT, _ffi.E_LENGTH_MISMATCH)
     with pytest.raises(G.GpursError):

@@ -124,6 +124,15 @@ def test_tall_tiles_f16(gpu, stream):
     assert relative_error(tall, O.matmul_rows(O.FMT_F16, dense, b, n, k, np.arange(m))) <= 1e-3
 
 
+def test_sparse_with_a_row_major_right_operand(gpu, stream):
+    """B stored k x n, as the sparse configuration states C = A * B: copied transposed into the workspace, same bits as n x k."""
+    m, n, k = 512, 448, 1024
+    dense, b = O.fill_sparse24_bf16(m, k, 31), O.fill_normal_16(O.FMT_BF16, n * k, 32)
+    expected = sparse_product(gpu, stream, dense, b, m, n, k, "bf16", G.ALGO_AUTO)
+    row_major = np.ascontiguousarray(b.reshape(n, k).T).reshape(-1)
+    assert np.array_equal(sparse_product(gpu, stream, dense, row_major, m, n, k, "bf16", G.ALGO_AUTO, b_row_major=True), expected)
+
+
 def test_sparse_configuration_shard(gpu, stream):
     """One GPU's share of the sparse configuration: A 2048 x 8192 (of 16384 x 8192, 2:4), B 8192 x 8192,
     bf16 out, max rel err 1e-2 against the densified fp64 product."""
