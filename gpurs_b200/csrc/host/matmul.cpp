@@ -109,14 +109,15 @@ SplitPlan plan_split(const gpurs_gpu *gpu, const Gemm &g, uint64_t explicit_grid
     const uint64_t eb = uint64_t(g.element_bytes);
     const bool batched = g.batches > 1;
     const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
-    const uint64_t all_tiles = ((g.m + tile_rows - 1) / tile_rows) * ((g.n + gemm::BLOCK_N - 1) / gemm::BLOCK_N);
+    const bool sparse = g.metadata != 0;       // 224-column tiles, stages of 128 logical K
+    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : uint64_t(gemm::BLOCK_N);
+    const uint64_t all_tiles = ((g.m + tile_rows - 1) / tile_rows) * ((g.n + block_n - 1) / block_n);
     const uint64_t wanted_ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     const uint64_t full_clusters = std::max<uint64_t>(1, wanted_ctas / cta_group);
     uint64_t grid_clusters = std::min(full_clusters, std::max<uint64_t>(all_tiles, 1));
-    const int depth_blocks = int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
-    const bool promoted_kernel = g.metadata == 0 && g.threads == gemm::SCALED_THREADS;      // promotes every K-block to registers: same schedule
-    const bool may_split = !g.whole_tiles && !batched && !g.gather && g.metadata == 0 && (g.threads == gemm::NUM_THREADS || promoted_kernel) &&
-                           all_tiles <= 0x7fffffffull;
+    const int depth_blocks = sparse ? int((g.k + gemm::SPARSE_BLOCK_K - 1) / gemm::SPARSE_BLOCK_K) : int((g.k * eb + gemm::ROW_BYTES - 1) / gemm::ROW_BYTES);
+    const bool promoted_kernel = !sparse && g.threads == gemm::SCALED_THREADS;      // promotes every K-block to registers: same schedule
+    const bool may_split = !g.whole_tiles && !batched && !g.gather && (g.threads == gemm::NUM_THREADS || promoted_kernel) && all_tiles <= 0x7fffffffull;
     int split_tiles = may_split ? gemm::stream_split_tiles(int(all_tiles), depth_blocks, int(grid_clusters), g.force_split) : 0;
     // Fewer tiles than CTA groups and a deep K (the reference's SplitDepth case, crates/gpurs/src/gpu/tensor/schedule): every tile
     // is split along K among up to STREAM_MAX_SHARE groups, which the same schedule expresses as "all tiles belong to the split
@@ -186,13 +187,14 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         const uint64_t columns = (g.n + gemm::SPARSE_BLOCK_N - 1) / gemm::SPARSE_BLOCK_N;
         const uint64_t pairs = std::max<uint64_t>(1, wanted_ctas / 2);
         const uint64_t short_rounds = (((g.m + 255) / 256) * columns + pairs - 1) / pairs, tall_rounds = (((g.m + 511) / 512) * columns + pairs - 1) / pairs;
-        tall = g.tile_width == 512 || (g.m > 256 && 2.0 * 0.8 * double(tall_rounds) <= double(short_rounds));
+        tall = g.tile_width == 512 || (!g.force_split && g.m > 256 && 2.0 * 0.8 * double(tall_rounds) <= double(short_rounds));
     }
+    if (tall) stream_k = false;
     // The dense tile kernels come without and with the output algebra compiled in ("_ep"): a plain product runs the lean entry.
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? ((algebra && !promoted_kernel) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? ((algebra && dense_tile) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
@@ -361,7 +363,8 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         params.split_tiles = split_tiles;
         void *stream_arguments[4] = {&map_a, &map_b, &map_c, &params};
         void *promoted_arguments[3] = {&map_a, &map_b, &params};
-        result = runtime::launch(kernel, stream, &config, promoted_kernel ? promoted_arguments : stream_arguments, true);
+        void *sparse_stream_arguments[4] = {&map_a, &map_b, &map_e, &params};
+        result = runtime::launch(kernel, stream, &config, sparse ? sparse_stream_arguments : promoted_kernel ? promoted_arguments : stream_arguments, true);
         const int released = borrowed_here ? runtime::workspace_release(stream) : GPURS_OK, turned = runtime::turns_release(stream);
         return result != GPURS_OK ? result : released != GPURS_OK ? released : turned;
     }

@@ -124,6 +124,26 @@ def test_tall_tiles_f16(gpu, stream):
     assert relative_error(tall, O.matmul_rows(O.FMT_F16, dense, b, n, k, np.arange(m))) <= 1e-3
 
 
+@pytest.mark.parametrize("algorithm,max_ctas,shape", [(G.ALGO_CTA_PAIR | G.ALGO_SPLIT_LAST_ROUND | G.ALGO_SQUARE_TILES, 8, (512, 1120, 1024)),
+                                                       (G.ALGO_SINGLE_CTA | G.ALGO_SPLIT_LAST_ROUND, 6, (640, 672, 512)),
+                                                       (G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES, 0, (256, 448, 8192)),
+                                                       (G.ALGO_SINGLE_CTA, 0, (200, 300, 6144))])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+def test_sparse_tiles_split_along_k(gpu, stream, algorithm, max_ctas, shape, out):
+    """The stream-K schedule on the sparse kernel: a last round split by force on a small grid (10 pair tiles on 4 pairs, 15
+    tiles on 6 CTAs), and few tiles with a deep K split among idle groups by default.  Against the densified oracle product,
+    close to the whole-tile product, and the same bits on every run."""
+    m, n, k = shape
+    dense, b = O.fill_sparse24_bf16(m, k, 41), O.fill_normal_16(O.FMT_BF16, n * k, 42)
+    got = sparse_product(gpu, stream, dense, b, m, n, k, out, algorithm, max_ctas=max_ctas)
+    rows = spread_rows(m, 12)
+    assert relative_error(got[rows], O.matmul_rows(O.FMT_BF16, dense, b, n, k, rows)) <= (1e-3 if out == "f32" else 1e-2)
+    whole = sparse_product(gpu, stream, dense, b, m, n, k, out, (algorithm & ~G.ALGO_SPLIT_LAST_ROUND) | G.ALGO_WHOLE_TILES, max_ctas=max_ctas)
+    assert relative_error(got, whole) <= (1e-3 if out == "f32" else 1e-2)      # another order of the tensor core's truncating adds (8192 deep: 5e-4)
+    assert np.array_equal(got, sparse_product(gpu, stream, dense, b, m, n, k, out, algorithm, max_ctas=max_ctas))
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_sparse_with_a_row_major_right_operand(gpu, stream):
     """B stored k x n, as the sparse configuration states C = A * B: copied transposed into the workspace, same bits as n x k."""
     m, n, k = 512, 448, 1024
