@@ -153,7 +153,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     }
     const SplitPlan plan = plan_split(gpu, g, explicit_grid);
     const uint64_t all_tiles = plan.all_tiles, wanted_ctas = plan.wanted_ctas, grid_clusters = plan.grid_clusters;
-    const int depth_blocks = plan.depth_blocks, split_tiles = plan.split_tiles;
+    const int split_tiles = plan.split_tiles;
     const bool promoted_kernel = plan.promoted_kernel;
     const gemm::StreamSchedule schedule = plan.schedule;
     bool stream_k = split_tiles > 0;
@@ -1133,11 +1133,12 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
         first += count;
     }
     const uint64_t blocks = pieces.size();
-    int result = runtime::copy_pipeline(gpu, 2 * blocks + 3);
+    int result = runtime::copy_pipeline(gpu, 3 * blocks + 8);
     if (result != GPURS_OK) return result;
     const driver::Api *api = gpu->api;
     CUevent *events = gpu->events.data();
     CUevent begun = events[0], whole_arrived = events[1], finished = events[2];
+    size_t next_event = 3;
 
     // Both helper streams start after the work already on the caller's stream (it may still be using the buffers).
     GPURS_TRY(api, cuEventRecord(begun, stream->handle));
@@ -1173,51 +1174,60 @@ extern "C" int gpurs_matmul_host(gpurs_stream *stream, const gpurs_matmul_desc *
     auto checked = [&](CUresult code, const char *what) { return code == CUDA_SUCCESS ? int(GPURS_OK) : runtime::fail_driver(api, what, code); };
     const uint8_t *bytes_a = static_cast<const uint8_t *>(host_a), *bytes_b = static_cast<const uint8_t *>(host_b);
     uint8_t *bytes_c = static_cast<uint8_t *>(host_c);
-    if (k) {
-        const CUresult code = by_columns ? copy_rows(true, a, host_a, m, k * eb, lda * eb, gpu->copy_in)
-                                         : copy_rows(true, b, host_b, b_rows, b_columns * eb, ldb * eb, gpu->copy_in);
-        if (code) result = driver_failed(code);
-        if (result == GPURS_OK) result = checked(api->cuEventRecord(whole_arrived, gpu->copy_in), "cuEventRecord");
-        if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(stream->handle, whole_arrived, 0), "cuStreamWaitEvent");
-    }
-    gpurs_matmul_desc local = *desc;
-    local.a_len = local.b_len = local.c_len = 0;
-    local.lda = lda, local.ldb = ldb, local.ldc = ldc;
     const uint64_t k_blocks = (k + 127) / 128;
-    for (uint64_t block = 0; block < blocks && result == GPURS_OK; block++) {
-        const uint64_t first = pieces[block].first, count = pieces[block].second;
-        CUevent arrived = events[3 + 2 * block], c_ready = events[4 + 2 * block];
-        // where this block's operand rows and its part of C start, in bytes
-        const uint64_t operand_offset = first * (by_columns ? ldb : lda) * eb;
-        const uint64_t c_offset = by_columns ? first * ob : first * ldc * ob;
+    const uint64_t ldr = desc->ldr ? desc->ldr : n;
+
+    // Rows [first, first + count) of an operand (A, or B stored n x k) go up; the caller's stream waits for them.
+    auto upload = [&](bool left, uint64_t first, uint64_t count) -> int {
+        const uint64_t pitch = left ? lda : ldb, offset = first * pitch * eb;
+        const CUresult code = copy_rows(true, (left ? a : b) + offset, (left ? bytes_a : bytes_b) + offset, count, k * eb, pitch * eb, gpu->copy_in);
+        if (code) return driver_failed(code);
+        CUevent arrived = events[next_event++];
+        int status = checked(api->cuEventRecord(arrived, gpu->copy_in), "cuEventRecord");
+        if (status == GPURS_OK) status = checked(api->cuStreamWaitEvent(stream->handle, arrived, 0), "cuStreamWaitEvent");
+        return status;
+    };
+    // C[row .. row + rows, column .. column + columns) = A's rows times B's rows (columns of C), every vector and matrix of the
+    // output algebra moved along; then that part of C starts its way back.
+    auto multiply_and_return = [&](uint64_t row, uint64_t rows, uint64_t column, uint64_t columns) -> int {
+        gpurs_matmul_desc local = *desc;
+        local.a_len = local.b_len = local.c_len = 0;
+        local.lda = lda, local.ldb = ldb, local.ldc = ldc;
+        local.m = rows, local.n = columns;
+        if (desc->bias) local.bias = desc->bias + column * sizeof(float);
+        if (desc->column_scale) local.column_scale = desc->column_scale + column * sizeof(float);
+        if (desc->scale_b) local.scale_b = desc->scale_b + (column / 128) * k_blocks * sizeof(float);
+        if (desc->row_scale) local.row_scale = desc->row_scale + row * sizeof(float);
+        if (desc->scale_a) local.scale_a = desc->scale_a + row * k_blocks * sizeof(float);
+        if (desc->row_bias) local.row_bias = desc->row_bias + row * sizeof(float);
+        if (desc->row_absmax) local.row_absmax = desc->row_absmax + row * sizeof(float);
+        if (desc->row_sum) local.row_sum = desc->row_sum + row * sizeof(float);
+        if (desc->residual) local.residual = desc->residual + (row * ldr + column) * ob, local.ldr = ldr;
+        const uint64_t b_offset = b_row_major ? column * eb : column * ldb * eb, c_offset = (row * ldc + column) * ob;
+        int status = matmul_checked(op, stream, &local, a + row * lda * eb, b + b_offset, c + c_offset, nullptr);
+        if (status != GPURS_OK) return status;
+        CUevent c_ready = events[next_event++];
+        status = checked(api->cuEventRecord(c_ready, stream->handle), "cuEventRecord");
+        if (status == GPURS_OK) status = checked(api->cuStreamWaitEvent(gpu->copy_out, c_ready, 0), "cuStreamWaitEvent");
+        if (status != GPURS_OK) return status;
+        const CUresult code = copy_rows(false, c + c_offset, bytes_c + c_offset, rows, columns * ob, ldc * ob, gpu->copy_out);
+        return code ? driver_failed(code) : int(GPURS_OK);
+    };
+
+    {
         if (k) {
-            const CUresult code = by_columns ? copy_rows(true, b + operand_offset, bytes_b + operand_offset, count, k * eb, ldb * eb, gpu->copy_in)
-                                             : copy_rows(true, a + operand_offset, bytes_a + operand_offset, count, k * eb, lda * eb, gpu->copy_in);
+            const CUresult code = by_columns ? copy_rows(true, a, host_a, m, k * eb, lda * eb, gpu->copy_in)
+                                             : copy_rows(true, b, host_b, b_rows, b_columns * eb, ldb * eb, gpu->copy_in);
             if (code) result = driver_failed(code);
-            if (result == GPURS_OK) result = checked(api->cuEventRecord(arrived, gpu->copy_in), "cuEventRecord");
-            if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(stream->handle, arrived, 0), "cuStreamWaitEvent");
+            if (result == GPURS_OK) result = checked(api->cuEventRecord(whole_arrived, gpu->copy_in), "cuEventRecord");
+            if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(stream->handle, whole_arrived, 0), "cuStreamWaitEvent");
+        }
+        for (uint64_t block = 0; block < blocks && result == GPURS_OK; block++) {
+            const uint64_t first = pieces[block].first, count = pieces[block].second;
+            if (k) result = upload(!by_columns, first, count);
             if (result != GPURS_OK) break;
+            result = by_columns ? multiply_and_return(0, m, first, count) : multiply_and_return(first, count, 0, n);
         }
-        if (by_columns) {
-            // columns [first, first + count) of C: the per-column vectors and B's scale rows move along
-            local.n = count;
-            local.bias = desc->bias ? desc->bias + first * sizeof(float) : 0;
-            local.column_scale = desc->column_scale ? desc->column_scale + first * sizeof(float) : 0;
-            local.scale_b = desc->scale_b ? desc->scale_b + (first / 128) * k_blocks * sizeof(float) : 0;
-            result = matmul_checked(op, stream, &local, a, b + operand_offset, c + c_offset, nullptr);
-        } else {
-            local.m = count;
-            local.row_scale = desc->row_scale ? desc->row_scale + first * sizeof(float) : 0;
-            local.scale_a = desc->scale_a ? desc->scale_a + first * k_blocks * sizeof(float) : 0;
-            result = matmul_checked(op, stream, &local, a + operand_offset, b, c + c_offset, nullptr);
-        }
-        if (result != GPURS_OK) break;
-        result = checked(api->cuEventRecord(c_ready, stream->handle), "cuEventRecord");
-        if (result == GPURS_OK) result = checked(api->cuStreamWaitEvent(gpu->copy_out, c_ready, 0), "cuStreamWaitEvent");
-        if (result != GPURS_OK) break;
-        const CUresult code = by_columns ? copy_rows(false, c + c_offset, bytes_c + c_offset, m, count * ob, ldc * ob, gpu->copy_out)
-                                         : copy_rows(false, c + c_offset, bytes_c + c_offset, count, n * ob, ldc * ob, gpu->copy_out);
-        if (code) result = driver_failed(code);
     }
     const int joined = join();
     return result != GPURS_OK ? result : joined;

@@ -413,6 +413,11 @@ def matmul_host(stream: Stream, host_a: int, host_b: int, host_c: int, a: Device
     desc.row_scale = options.row_scale.pointer if options.row_scale else 0
     desc.column_scale = options.column_scale.pointer if options.column_scale else 0
     desc.alpha = options.alpha
+    desc.row_absmax = options.row_absmax.pointer if options.row_absmax else 0
+    desc.row_bias = options.row_bias.pointer if options.row_bias else 0
+    desc.residual = options.residual.pointer if options.residual else 0
+    desc.ldr, desc.beta = options.ldr, options.beta
+    desc.row_sum = options.row_sum.pointer if options.row_sum else 0
     _check(stream.gpu._lib.gpurs_matmul_host(stream._handle, C.byref(desc), host_a, host_b, host_c, a.pointer, b.pointer, c.pointer))
 
 

@@ -59,6 +59,25 @@ def test_host_call_equals_the_device_call(gpu, stream, kind, out, m, n, k):
     assert np.array_equal(got.view(np.uint8), expected.view(np.uint8))
 
 
+@pytest.mark.parametrize("m,n,k", [(2048, 512, 256), (512, 2048, 128)])
+def test_row_and_column_algebra_follows_the_blocks(gpu, stream, m, n, k):
+    """Blocks of rows (m = 2048) and blocks of columns (n = 2048): the per-row and per-column vectors, the residual matrix and the
+    row reductions are addressed block by block; same bits as one call on resident operands."""
+    a_bits, b_bits = make_operands("bf16", m, n, k)
+    rng = np.random.default_rng(5)
+    bias, row_bias = gpu.upload(rng.standard_normal(n).astype(np.float32)), gpu.upload(rng.standard_normal(m).astype(np.float32))
+    row_scale, column_scale = gpu.upload((1 + rng.random(m)).astype(np.float32)), gpu.upload((1 + rng.random(n)).astype(np.float32))
+    residual = gpu.upload(rng.standard_normal(m * n).astype(np.float32))
+    sums = [gpu.zeros(G.F32, m), gpu.zeros(G.F32, m)]
+    peaks = [gpu.zeros(G.F32, m), gpu.zeros(G.F32, m)]
+    options = dict(bias=bias, row_bias=row_bias, row_scale=row_scale, column_scale=column_scale, residual=residual, beta=0.5, alpha=1.5)
+    expected = run_matmul(gpu, stream, "bf16", "f32", a_bits, b_bits, m, n, k, row_sum=sums[0], row_absmax=peaks[0], **options)
+    got = host_product(gpu, stream, "bf16", "f32", a_bits, b_bits, m, n, k, row_sum=sums[1], row_absmax=peaks[1], **options)
+    assert np.array_equal(got, expected)
+    assert np.array_equal(peaks[0].download(), peaks[1].download())
+    assert np.allclose(sums[0].download(), sums[1].download(), rtol=1e-5, atol=1e-3)       # atomic adds of the tiles' parts: any order
+
+
 @pytest.mark.parametrize("m,n,k", [(2048, 512, 384), (256, 2048, 256), (640, 1536, 128)])
 def test_block_scales_follow_their_blocks(gpu, stream, m, n, k):
     """Block-scaled FP8 by blocks of rows (m > n: A's scale rows move with the block) and by blocks of columns (n > m:
