@@ -170,12 +170,16 @@ def measured_peaks() -> dict:
 
 def measured_traffic(workload: str):
     """DRAM bytes one launch of the workload's dominant kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of an
-    ncu capture), from the table the profile summaries keep; None until that workload has been captured."""
-    path = ROOT / "profiles" / "traffic.json"
+    ncu capture), from the table the profile summaries keep (rows `| workload | bytes | kernel | from |`); None until that
+    workload has been captured."""
+    path = ROOT / "profiles" / "dram_traffic_per_launch.md"
     if not path.exists():
         return None
-    entry = json.loads(path.read_text()).get(workload)
-    return int(entry["dram_bytes_per_launch"]) if entry else None
+    for row in path.read_text().splitlines():
+        cells = [cell.strip() for cell in row.strip().strip("|").split("|")]
+        if len(cells) >= 2 and cells[0] == workload and cells[1].isdigit():
+            return int(cells[1])
+    return None
 
 
 def roofline(workload: str, kind: str, tflops: float, flops: float, algorithmic_bytes: int) -> dict:
