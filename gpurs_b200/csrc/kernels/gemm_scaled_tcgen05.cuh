@@ -256,8 +256,10 @@ __device__ __forceinline__ void gemm_promoted_body(const CUtensorMap *map_a, con
                         ptx::tcgen05_fence_before();
                         __syncwarp();
                         if (lane == 0) {
-                            if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(slot));
-                            else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(slot), 0));
+                            // nothing is published through ordinary memory (the accumulator has been read out when
+                            // tcgen05.wait::ld returns): no release, which at cluster scope would wait for this thread's stores
+                            if (CTA_GROUP == 1 || leader) ptx::mbarrier_arrive(acc_empty_bar(slot));
+                            else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(slot), 0));
                         }
                     }
 #pragma unroll
