@@ -361,8 +361,9 @@ __device__ __forceinline__ void gemm_sparse_body(const CUtensorMap *map_a, const
             ptx::tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                if constexpr (CTA_GROUP == 1) ptx::mbarrier_arrive(acc_empty_bar(acc));
-                else ptx::mbarrier_arrive_cluster(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                // no release needed: the accumulator has been read out, nothing is published through ordinary memory
+                if (CTA_GROUP == 1 || leader) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(acc), 0));
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
