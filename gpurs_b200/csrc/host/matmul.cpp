@@ -163,9 +163,12 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     // long; they are taken to be 7 % faster per flop when weighing rounds against each other).
     const bool algebra_ = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                           g.row_sum || g.accumulate;
+    // the wide kernel's epilogue has the element-wise algebra (its `_ep` entries, float outputs), not the row reductions nor the
+    // accumulation into C
+    const bool unstaged_algebra = g.row_absmax || g.row_sum || g.accumulate || (algebra_ && g.output_type == GPURS_I32);
     bool wide = false;
     if (g.tile_width != 256 && !g.force_split && cta_group == 2 && g.metadata == 0 && g.threads == gemm::NUM_THREADS && !batched && !g.gather && !g.b_row_major &&
-        !algebra_ && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0 &&
+        !unstaged_algebra && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0 &&
         (!g.launch || g.launch->block[0] == 0)) {      // that kernel has its own block size
         const uint64_t wide_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + 511) / 512);
         const uint64_t pairs = std::max<uint64_t>(1, wanted_ctas / 2);
@@ -194,7 +197,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? "%s_w512_cg%d" : stream_k ? ((algebra && dense_tile) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? (algebra ? "%s_w512_ep_cg%d" : "%s_w512_cg%d") : stream_k ? ((algebra && dense_tile) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;

@@ -18,8 +18,8 @@
 // issuer (leader), warps 2..9 epilogue: two warps per quadrant of tensor-memory lanes, one for the first and one for the second
 // 128 columns of either half, one staging box each.  (A launch of one round ends with every tile's read-out exposed at once;
 // with four epilogue warps that tail was measured at 6.6 us for 32-bit outputs, which a 1024-row shard of an 8192^3 product
-// cannot afford.)  Plain epilogue only (round, stage, TMA store), C with 16-byte aligned rows; everything else takes the
-// 256-column kernels.
+// cannot afford.)  Epilogue: round, stage, TMA store, with the element-wise output algebra in the `_ep` entries; C with 16-byte aligned
+// rows; row reductions, accumulation into C and everything else take the 256-column kernels.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -47,7 +47,9 @@ struct WideLayout {
     static_assert(DYNAMIC_BYTES == WIDE_SHARED, "the host sizes the launch from gemm_params.hpp");
 };
 
-template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT>
+// ALGEBRA: the epilogue applies the element-wise output algebra of Params (alpha, row and column scales, bias, row bias,
+// residual) as the 256-column kernels do; the entries without it are the ones a plain product runs.
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, bool ALGEBRA = false>
 __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p) {
     using L = WideLayout;
     constexpr int STAGES = WIDE_STAGES, HALF = 256;
@@ -212,10 +214,15 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                     uint32_t packed[32];
                     ptx::tmem_load_wait();
                     if constexpr (COLUMNS_PER_BOX == 32) {
+                        if constexpr (ALGEBRA) apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
 #pragma unroll
                         for (int i = 0; i < 32; i++) packed[i] = low[i];
                         if (box + 1 < BOXES) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
                     } else {
+                        if constexpr (ALGEBRA) {
+                            apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
+                            apply_epilogue<OUT>(p, high, warp_row + int(lane), column + 32);
+                        }
 #pragma unroll
                         for (int i = 0; i < 16; i++) {
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);

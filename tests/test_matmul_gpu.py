@@ -309,6 +309,28 @@ def test_wide_tiles_give_the_same_product(gpu, stream, kind, out, m, n, k):
         assert relative_error(values, O.matmul_rows(KINDS[kind][1], a, b, n, k, rows)) <= (1e-2 if out in ("bf16", "f16") else 1e-3)
 
 
+@pytest.mark.parametrize("kind,out", [("bf16", "bf16"), ("f16", "f32"), ("e4m3", "bf16"), ("bf16", "f32"), ("f16", "f16")])
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 256), (700, 1100, 192)])
+def test_wide_tiles_apply_the_output_algebra(gpu, stream, kind, out, m, n, k):
+    """The wide tiles' `_ep` entries: alpha, row and column scales, bias, row bias and a residual matrix (C itself the second
+    time) give the same bits as on the 256 x 256 tiles; products with row reductions stay on those whatever the flag says."""
+    a, b = make_operands(kind, m, n, k)
+    rng = np.random.default_rng(11)
+    vectors = dict(bias=gpu.upload(rng.standard_normal(n).astype(np.float32)), row_bias=gpu.upload(rng.standard_normal(m).astype(np.float32)),
+                   row_scale=gpu.upload((1 + rng.random(m)).astype(np.float32)), column_scale=gpu.upload((1 + rng.random(n)).astype(np.float32)), alpha=0.75)
+    wide, square = G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES | G.ALGO_WHOLE_TILES
+    got = run_matmul(gpu, stream, kind, out, a, b, m, n, k, wide, **vectors)
+    assert np.array_equal(got, run_matmul(gpu, stream, kind, out, a, b, m, n, k, square, **vectors))
+    residual = gpu.upload(got.copy(), {"bf16": G.BF16, "f16": G.F16, "f32": G.F32}[out])
+    with_residual = run_matmul(gpu, stream, kind, out, a, b, m, n, k, wide, residual=residual, beta=0.5, **vectors)
+    assert np.array_equal(with_residual, run_matmul(gpu, stream, kind, out, a, b, m, n, k, square, residual=residual, beta=0.5, **vectors))
+    assert not np.array_equal(with_residual, got)
+    sums = [gpu.zeros(G.F32, m), gpu.zeros(G.F32, m)]
+    reduced = run_matmul(gpu, stream, kind, out, a, b, m, n, k, wide, row_absmax=sums[0], **vectors)
+    assert np.array_equal(reduced, got)
+    assert np.array_equal(sums[0].download(), (lambda s: (run_matmul(gpu, stream, kind, out, a, b, m, n, k, square, row_absmax=s, **vectors), s.download())[1])(sums[1]))
+
+
 def test_wide_and_square_tiles_exclude_each_other(gpu, stream):
     a, b = make_operands("bf16", 256, 512, 64)
     with pytest.raises(G.GpursError) as raised:
