@@ -150,10 +150,40 @@ __device__ __forceinline__ void apply_epilogue(const Params &p, uint32_t (&acc)[
             for (int i = 0; i < 32; i++) acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), addend));
         }
         if (p.residual != nullptr && row < p.m) {
+            constexpr int ELEMENT_BYTES = OUT == OUT_F32 ? 4 : 2;
+            const uint8_t *source = reinterpret_cast<const uint8_t *>(p.residual) + (size_t(row) * size_t(p.ldr) + size_t(column)) * ELEMENT_BYTES;
+            if (whole_chunk && (reinterpret_cast<uintptr_t>(source) & 15) == 0) {
+                // the row's 32 elements as 16-byte loads (plain loads: the residual may be C itself)
+                const uint4 *vector = reinterpret_cast<const uint4 *>(source);
 #pragma unroll
-            for (int i = 0; i < 32; i++)
-                if (column + i < p.n)
-                    acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), __fmul_rn(p.beta, residual_element<OUT>(p, row, column + i))));
+                for (int i = 0; i < 32 * ELEMENT_BYTES / 16; i++) {
+                    const uint4 v = vector[i];
+                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if constexpr (OUT == OUT_F32) {
+                            const int e = 4 * i + j;
+                            acc[e] = __float_as_uint(__fadd_rn(__uint_as_float(acc[e]), __fmul_rn(p.beta, __uint_as_float(words[j]))));
+                        } else {
+                            const int e = 8 * i + 2 * j;
+                            float low, high;
+                            if constexpr (OUT == OUT_BF16) {
+                                low = __uint_as_float(words[j] << 16), high = __uint_as_float(words[j] & 0xffff0000u);
+                            } else {
+                                const __half2 pair = *reinterpret_cast<const __half2 *>(&words[j]);
+                                low = __low2float(pair), high = __high2float(pair);
+                            }
+                            acc[e] = __float_as_uint(__fadd_rn(__uint_as_float(acc[e]), __fmul_rn(p.beta, low)));
+                            acc[e + 1] = __float_as_uint(__fadd_rn(__uint_as_float(acc[e + 1]), __fmul_rn(p.beta, high)));
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (column + i < p.n)
+                        acc[i] = __float_as_uint(__fadd_rn(__uint_as_float(acc[i]), __fmul_rn(p.beta, residual_element<OUT>(p, row, column + i))));
+            }
         }
     }
 }
