@@ -167,6 +167,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     // accumulation into C
     const bool unstaged_algebra = g.row_absmax || g.row_sum || g.accumulate || (algebra_ && g.output_type == GPURS_I32);
     bool wide = false;
+    uint64_t wide_columns = 512;
     if (g.tile_width != 256 && !g.force_split && cta_group == 2 && g.metadata == 0 && g.threads == gemm::NUM_THREADS && !batched && !g.gather && !g.b_row_major &&
         !unstaged_algebra && g.element_type != GPURS_F32 && g.l2_policy == 0 && g.n > 256 && g.c % 16 == 0 && (g.ldc * ob) % 16 == 0 &&
         (!g.launch || g.launch->block[0] == 0)) {      // that kernel has its own block size
@@ -180,6 +181,12 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
         // 8192^3, measured 49.2 us against 51.1 us for 128 square tiles with the last round split along K)
         wide = g.tile_width == 512 || (all_tiles > pairs && wide_cost <= square_cost);
         if (wide_tiles > 0x7fffffffull) wide = false;
+        // 256 x 480 tiles (second half 224 columns; 32-bit outputs, no output algebra) where they need fewer rounds x columns than
+        // the 512-wide ones: 8192 columns on 1024 rows are 64 tiles of 512 for 74 pairs, one round either way, or 72 of 480
+        if (wide && g.tile_width != 512 && g.output_bytes == 4 && !algebra_) {
+            const uint64_t narrower_tiles = ((g.m + tile_rows_ - 1) / tile_rows_) * ((g.n + 479) / 480);
+            if (480 * ((narrower_tiles + pairs - 1) / pairs) < 512 * ((wide_tiles + pairs - 1) / pairs)) wide_columns = 480;
+        }
     }
     if (wide) stream_k = false;
     // 512 x 224 tiles of the 2:4-sparse product (kernels/gemm_sparse_tall_tcgen05.cuh): B, most of the sparse kernel's operand
@@ -197,7 +204,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const bool algebra = g.bias || g.row_scale || g.column_scale || (g.alpha != 0.0f && g.alpha != 1.0f) || g.row_absmax || g.row_bias || g.residual ||
                          g.row_sum || g.accumulate;
     const bool dense_tile = g.metadata == 0 && g.threads == gemm::NUM_THREADS;
-    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? (algebra ? "%s_w512_ep_cg%d" : "%s_w512_cg%d") : stream_k ? ((algebra && dense_tile) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
+    const char *form = g.gather ? "%s_push_cg%d" : batched ? "%s_batched_cg%d" : tall ? "%s_t512_cg%d" : wide ? (wide_columns == 480 ? "%s_w480_cg%d" : algebra ? "%s_w512_ep_cg%d" : "%s_w512_cg%d") : stream_k ? ((algebra && dense_tile) ? "%s_sk_ep_cg%d" : "%s_sk_cg%d")
                        : (algebra && dense_tile) ? "%s_ep_cg%d" : "%s_cg%d";
     std::snprintf(name, sizeof name, form, g.stem, cta_group);
     const bool sparse = g.metadata != 0;
@@ -217,7 +224,7 @@ int launcher::launch_gemm(gpurs_stream *stream, const Gemm &g) {
     const uint32_t box_a[2] = {block_k, uint32_t(gemm::BLOCK_M)};
     // B as n x k: one box of (128 bytes of k) x (the tile's rows of n).  B as k x n: boxes of (128 bytes of n) x (block_k rows of k).
     // columns of one tile: 256, or 224 for the sparse kernels (two accumulators plus metadata in tensor memory)
-    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : wide ? 512 : uint64_t(gemm::BLOCK_N);
+    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : wide ? wide_columns : uint64_t(gemm::BLOCK_N);
     uint64_t dims_b[2] = {g.k, g.n};
     uint32_t box_b[2] = {block_k, wide ? 128u : uint32_t(block_n / cta_group)};      // wide tiles: the CTA's 128 rows of either half
     if (g.b_row_major) {

@@ -49,11 +49,16 @@ struct WideLayout {
 
 // ALGEBRA: the epilogue applies the element-wise output algebra of Params (alpha, row and column scales, bias, row bias,
 // residual) as the 256-column kernels do; the entries without it are the ones a plain product runs.
-template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, bool ALGEBRA = false>
+// SECOND: columns of the tile's second half, 256 or 224.  A 256 + 224 = 480-column tile exists for shapes whose 512-wide tiles
+// fill the grid badly (8192 columns on 1024 rows: 64 tiles of 512 for 74 CTA pairs, 72 of 480); its second half is a product of
+// N = 224 on 112 rows of B per CTA (the 128-row box is loaded all the same), and its outputs are 32-bit (whole 32-column boxes).
+template <int KIND, int ELEMENT_FORMAT, int ACC_FORMAT, int OUT, bool ALGEBRA = false, int SECOND = 256>
 __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_c, const Params &p) {
     using L = WideLayout;
-    constexpr int STAGES = WIDE_STAGES, HALF = 256;
-    constexpr uint32_t IDESC = instruction_descriptor(ACC_FORMAT, ELEMENT_FORMAT, 2 * BLOCK_M, HALF);
+    constexpr int STAGES = WIDE_STAGES, HALF = 256, TILE_N = HALF + SECOND;
+    static_assert(SECOND == 256 || (SECOND == 224 && (OUT == OUT_F32 || OUT == OUT_I32)), "second half: 256 columns, or 224 with 32-bit outputs");
+    constexpr uint32_t IDESC_FIRST = instruction_descriptor(ACC_FORMAT, ELEMENT_FORMAT, 2 * BLOCK_M, HALF);
+    constexpr uint32_t IDESC_SECOND = instruction_descriptor(ACC_FORMAT, ELEMENT_FORMAT, 2 * BLOCK_M, SECOND);
 
     extern __shared__ uint8_t raw_shared[];
     const uint32_t base = (ptx::smem_u32(raw_shared) + 1023u) & ~1023u;
@@ -118,7 +123,8 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                 int tile_m, tile_n;
                 tile_position(tile, p, tile_m, tile_n);
                 const int row_a = (tile_m * 2 + int(cta_rank)) * BLOCK_M;
-                const int row_b = tile_n * WIDE_BLOCK_N + int(cta_rank) * 128;      // + 256 for the second half
+                const int row_b = tile_n * TILE_N + int(cta_rank) * 128;
+                const int row_b_second = tile_n * TILE_N + HALF + int(cta_rank) * (SECOND / 2);
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
@@ -129,7 +135,7 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                     const uint32_t leader_bar = ptx::map_to_cta(full_bar(stage), 0);
                     ptx::tma_load_2d_pair(stage_a(stage), map_a, kb * block_k, row_a, leader_bar);
                     ptx::tma_load_2d_pair(stage_b(stage, 0), map_b, kb * block_k, row_b, leader_bar);
-                    ptx::tma_load_2d_pair(stage_b(stage, 1), map_b, kb * block_k, row_b + HALF, leader_bar);
+                    ptx::tma_load_2d_pair(stage_b(stage, 1), map_b, kb * block_k, row_b_second, leader_bar);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -169,10 +175,11 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                         }
                         const uint32_t d_tmem = tmem_base + uint32_t(half) * HALF;
                         const uint64_t b_half = b_desc + uint64_t(half) * HALF_STEP;
-                        ptx::tcgen05_mma<KIND, 2>(d_tmem, a_desc, b_half, IDESC, uint32_t(kb != 0));
+                        const uint32_t idesc = half == 0 ? IDESC_FIRST : IDESC_SECOND;
+                        ptx::tcgen05_mma<KIND, 2>(d_tmem, a_desc, b_half, idesc, uint32_t(kb != 0));
 #pragma unroll
                         for (int j = 1; j < ROW_BYTES / MMA_K_BYTES; j++)
-                            ptx::tcgen05_mma_accumulate<KIND, 2>(d_tmem, a_desc + uint64_t(j) * K_STEP, b_half + uint64_t(j) * K_STEP, IDESC);
+                            ptx::tcgen05_mma_accumulate<KIND, 2>(d_tmem, a_desc + uint64_t(j) * K_STEP, b_half + uint64_t(j) * K_STEP, idesc);
                         if (kb == k_blocks - 1) ptx::tcgen05_commit_pair(acc_full_bar(half), 0x3);      // this half of the tile is complete
                     }
                     if (!ok) break;
@@ -204,20 +211,23 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                 }
                 ptx::tcgen05_fence_after();
                 const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(half * HALF + side * 128);
+                // boxes this warp reads of this half: 128 columns' worth, or what is left of a 224-column second half
+                const int boxes = (half == 1 && side == 1) ? (SECOND - 128) / COLUMNS_PER_BOX : BOXES;
                 // the read of box b + 1 is in flight while box b is staged and stored
                 uint32_t low[32], high[32];
                 ptx::tmem_load_32x32(lane_base, low);
                 if constexpr (COLUMNS_PER_BOX == 64) ptx::tmem_load_32x32(lane_base + 32, high);
 #pragma unroll
                 for (int box = 0; box < BOXES; box++) {
-                    const int column = tile_n * WIDE_BLOCK_N + half * HALF + side * 128 + box * COLUMNS_PER_BOX;
+                    if (box >= boxes) break;
+                    const int column = tile_n * TILE_N + half * HALF + side * 128 + box * COLUMNS_PER_BOX;
                     uint32_t packed[32];
                     ptx::tmem_load_wait();
                     if constexpr (COLUMNS_PER_BOX == 32) {
                         if constexpr (ALGEBRA) apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
 #pragma unroll
                         for (int i = 0; i < 32; i++) packed[i] = low[i];
-                        if (box + 1 < BOXES) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
+                        if (box + 1 < boxes) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
                     } else {
                         if constexpr (ALGEBRA) {
                             apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
@@ -228,12 +238,12 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
                             packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
                             packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
                         }
-                        if (box + 1 < BOXES) {
+                        if (box + 1 < boxes) {
                             ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64), low);
                             ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64 + 32), high);
                         }
                     }
-                    if (box == BOXES - 1) {
+                    if (box == boxes - 1) {
                         // this warp's part of the half has left tensor memory: once all sixteen warps of the pair have said so,
                         // the next tile's products may overwrite it while these boxes are stored
                         ptx::tcgen05_fence_before();

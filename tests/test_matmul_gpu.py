@@ -331,6 +331,18 @@ def test_wide_tiles_apply_the_output_algebra(gpu, stream, kind, out, m, n, k):
     assert np.array_equal(sums[0].download(), (lambda s: (run_matmul(gpu, stream, kind, out, a, b, m, n, k, square, row_absmax=s, **vectors), s.download())[1])(sums[1]))
 
 
+@pytest.mark.parametrize("kind,out", [("i8", "i32"), ("f16", "f32"), ("bf16", "f32"), ("e4m3", "f32")])
+@pytest.mark.parametrize("m,n,k,max_ctas", [(256, 960, 256, 0), (700, 1000, 192, 0), (1024, 8192, 128, 0), (1536, 1440, 256, 4)])
+def test_480_column_tiles_give_the_same_product(gpu, stream, kind, out, m, n, k, max_ctas):
+    """32-bit outputs whose 480-column tiles (256 + 224) need fewer rounds x columns than 512-wide ones get those by default:
+    the same sums in the same order as on 256 x 256 tiles, ragged edges and several tiles per pair included."""
+    a, b = make_operands(kind, m, n, k)
+    got = run_matmul(gpu, stream, kind, out, a, b, m, n, k, G.ALGO_CTA_PAIR, max_ctas=max_ctas)
+    assert np.array_equal(got, run_matmul(gpu, stream, kind, out, a, b, m, n, k, G.ALGO_CTA_PAIR | G.ALGO_SQUARE_TILES | G.ALGO_WHOLE_TILES, max_ctas=max_ctas))
+    assert np.array_equal(got, run_matmul(gpu, stream, kind, out, a, b, m, n, k, G.ALGO_CTA_PAIR | G.ALGO_WIDE_TILES, max_ctas=max_ctas))
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_wide_and_square_tiles_exclude_each_other(gpu, stream):
     a, b = make_operands("bf16", 256, 512, 64)
     with pytest.raises(G.GpursError) as raised:
