@@ -103,14 +103,14 @@ struct SplitPlan {
     }
 };
 
-SplitPlan plan_split(const gpurs_gpu *gpu, const Gemm &g, uint64_t explicit_grid) {
+SplitPlan plan_split(const gpurs_gpu *gpu, const Gemm &g, uint64_t explicit_grid, uint64_t tile_columns = 0) {
     SplitPlan plan;
     const int cta_group = g.cta_group;
     const uint64_t eb = uint64_t(g.element_bytes);
     const bool batched = g.batches > 1;
     const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
     const bool sparse = g.metadata != 0;       // 224-column tiles, stages of 128 logical K
-    const uint64_t block_n = sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : uint64_t(gemm::BLOCK_N);
+    const uint64_t block_n = tile_columns ? tile_columns : sparse ? uint64_t(gemm::SPARSE_BLOCK_N) : uint64_t(gemm::BLOCK_N);
     const uint64_t all_tiles = ((g.m + tile_rows - 1) / tile_rows) * ((g.n + block_n - 1) / block_n);
     const uint64_t wanted_ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     const uint64_t full_clusters = std::max<uint64_t>(1, wanted_ctas / cta_group);
@@ -394,10 +394,17 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     gpurs_gpu *gpu = stream->gpu;
     const int cta_group = g.cta_group;
     const uint32_t shared_bytes = uint32_t(cta_group == 2 ? gemm::MX_SHARED_PAIR : gemm::MX_SHARED_SINGLE);
+    uint64_t explicit_grid = 0;
+    int result = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(gemm::NUM_THREADS), shared_bytes, explicit_grid);
+    if (result != GPURS_OK) return result;
+    // the schedule of the dense kernels on this kernel's 224-column tiles: the last round, or every tile of a small deep product,
+    // split along K
+    const SplitPlan plan = plan_split(gpu, g, explicit_grid, gemm::MX_BLOCK_N);
+    const bool stream_k = plan.split_tiles > 0;
     char name[96];
-    std::snprintf(name, sizeof name, "%s_cg%d", g.stem, cta_group);
+    std::snprintf(name, sizeof name, stream_k ? "%s_sk_cg%d" : "%s_cg%d", g.stem, cta_group);
     gpurs_kernel *kernel = nullptr;
-    int result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
+    result = runtime::builtin_kernel(gpu, name, shared_bytes, &kernel);
     if (result != GPURS_OK) return result;
     const uint64_t tile_rows = uint64_t(gemm::BLOCK_M) * cta_group;
     const uint64_t k_blocks = (g.k + 127) / 128, tiles_m = (g.m + tile_rows - 1) / tile_rows, tiles_n = (g.n + gemm::MX_BLOCK_N - 1) / gemm::MX_BLOCK_N;
@@ -436,20 +443,33 @@ int launch_mx(gpurs_stream *stream, const launcher::Gemm &g) {
     params.accumulate = g.accumulate ? 1 : 0;
     const uint64_t tiles = tiles_m * tiles_n;
     if (tiles > 0x7fffffffull) return fail("gpurs_matmul", GPURS_E_SIZE_OVERFLOW, "too many tiles");
-    uint64_t explicit_grid = 0;
-    result = explicit_ctas("gpurs_matmul", g.launch, cta_group, uint32_t(gemm::NUM_THREADS), shared_bytes, explicit_grid);
-    if (result != GPURS_OK) return result;
     const uint64_t ctas = explicit_grid ? explicit_grid : g.max_ctas > 0 ? uint64_t(g.max_ctas) : uint64_t(gpu->multiprocessors);
     gpurs_launch_config config;
     std::memset(&config, 0, sizeof config);
-    const uint64_t clusters = std::min(std::max<uint64_t>(1, ctas / cta_group), tiles);
+    const uint64_t clusters = stream_k ? plan.grid_clusters : std::min(std::max<uint64_t>(1, ctas / cta_group), tiles);
     config.grid[0] = uint32_t(clusters * cta_group);
     config.block[0] = uint32_t(gemm::NUM_THREADS);
     config.shared_bytes = shared_bytes;
     config.cluster[0] = uint32_t(cta_group);
     config.cluster[1] = config.cluster[2] = 1;
     void *arguments[5] = {&map_a, &map_b, &map_sa, &map_sb, &params};
-    return runtime::launch(kernel, stream, &config, arguments, true);
+    if (!stream_k) return runtime::launch(kernel, stream, &config, arguments, true);
+    // scratch for the partial tiles and their arrival counters, borrowed from the handle for this launch
+    CUdeviceptr partials = 0, counters = 0;
+    result = runtime::workspace_acquire(stream, plan.partial_bytes(cta_group), &partials);
+    if (result != GPURS_OK) return result;
+    result = runtime::turns_acquire(stream, std::max<size_t>(size_t(plan.schedule.split_tiles) * 4 * cta_group * sizeof(uint32_t), 4096), &counters);
+    if (result != GPURS_OK) {
+        runtime::workspace_release(stream);
+        return result;
+    }
+    params.partials = reinterpret_cast<void *>(partials);
+    params.split_counters = reinterpret_cast<unsigned int *>(counters);
+    params.max_contributors = gemm::max_contributors(plan.schedule);
+    params.split_tiles = plan.split_tiles;
+    result = runtime::launch(kernel, stream, &config, arguments, true);
+    const int released = runtime::workspace_release(stream), turned = runtime::turns_release(stream);
+    return result != GPURS_OK ? result : released != GPURS_OK ? released : turned;
 }
 
 // The block-scaled FP8 product on CTA pairs (kernels/gemm_blockscaled_tcgen05.cuh): 256 x 256 tiles, every K-block issued as two
@@ -799,6 +819,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         }
         mx.row_bias = desc->row_bias, mx.residual = desc->residual, mx.ldr = mx_ldr, mx.beta = desc->beta == 0.0f ? 1.0f : desc->beta;
         mx.accumulate = desc->accumulate == 1, mx.launch = desc->launch;
+        if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
+        mx.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0, mx.force_split = (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND) != 0;
         return launch_mx(stream, mx);
     }
 

@@ -82,7 +82,9 @@ __device__ __forceinline__ void tcgen05_copy_32x128b_warpx4(uint32_t tmem_addres
 }
 
 // map_sa / map_sb describe the tiled scales as rows of 16 bytes: box 16 x 32 (one block of A's), 16 x 64 (B's two blocks).
-template <int OUT, int CTA_GROUP, int STAGES>
+// STREAMK: the K-blocks of the tiles of a split round are spread over the CTA groups (gemm_schedule.hpp) and the parts are added
+// up by whoever arrives last, as in gemm_body; a part is laid out like a dense tile's (256 columns wide, 224 used).
+template <int OUT, int CTA_GROUP, int STAGES, bool STREAMK = false>
 __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUtensorMap *map_b, const CUtensorMap *map_sa, const CUtensorMap *map_sb,
                                              const Params &p) {
     using L = MxLayout<CTA_GROUP, STAGES>;
@@ -156,12 +158,15 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
                 int tile_m, tile_n;
                 tile_position(tile, p, tile_m, tile_n);
                 const int row_block = tile_m * CTA_GROUP + int(cta_rank);          // 128-row block of A this CTA owns
                 const int row_a = row_block * BLOCK_M, row_b = tile_n * BN + int(cta_rank) * L::B_ROWS;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
                     if (!ptx::mbarrier_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                         report(p, abort_flag, STATUS_PRODUCER_TIMEOUT, tile, kb);
                         ok = false;
@@ -196,14 +201,17 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
+            WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+            WorkItem item;
+            while (ok && walker.next(item)) {
+                const int tile = item.tile;
                 if (!ptx::mbarrier_wait<CTA_GROUP == 2>(acc_empty_bar(acc), acc_phase ^ 1, abort_flag)) {
                     report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, -1);
                     break;
                 }
                 ptx::tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(acc) * BN;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = item.kb_begin; kb < item.kb_end; kb++) {
                     if (!ptx::mbarrier_wait(full_bar(stage), phase, abort_flag)) {
                         report(p, abort_flag, STATUS_MMA_TIMEOUT, tile, kb);
                         ok = false;
@@ -219,7 +227,7 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
 #pragma unroll
                     for (int j = 0; j < ROW_BYTES / MMA_K_BYTES; j++)
                         tcgen05_mma_mx<CTA_GROUP>(d_tmem, a_desc + uint64_t(j * (MMA_K_BYTES >> 4)), b_desc + uint64_t(j * (MMA_K_BYTES >> 4)),
-                                       IDESC | (uint32_t(j) << 29) | (uint32_t(j) << 4), scale_a_tmem, scale_b_tmem, uint32_t((kb | j) != 0));
+                                       IDESC | (uint32_t(j) << 29) | (uint32_t(j) << 4), scale_a_tmem, scale_b_tmem, uint32_t(kb != item.kb_begin || j != 0));
                     if constexpr (CTA_GROUP == 1) ptx::tcgen05_commit(empty_bar(stage));
                     else ptx::tcgen05_commit_pair(empty_bar(stage), 0x3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -235,7 +243,10 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
         const int quadrant = warp % 4;
         uint32_t acc_phase = 0;
         int acc = 0;
-        for (int tile = cluster_id; tile < tile_count; tile += cluster_count) {
+        WorkWalker<STREAMK> walker(tile_count, k_blocks, cluster_id, cluster_count, p.split_tiles);
+        WorkItem item;
+        while (walker.next(item)) {
+            const int tile = item.tile;
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
             const bool ready = ptx::mbarrier_wait(acc_full_bar(acc), acc_phase, abort_flag);
@@ -246,12 +257,65 @@ __device__ __forceinline__ void gemm_mx_body(const CUtensorMap *map_a, const CUt
             ptx::tcgen05_fence_after();
             const int row = (tile_m * CTA_GROUP + int(cta_rank)) * BLOCK_M + quadrant * 32 + int(lane);
             const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(acc) * BN;
+            constexpr int TILE_ROWS = BLOCK_M * CTA_GROUP;
+            constexpr size_t PART = size_t(TILE_ROWS) * BLOCK_N / 4;      // one part, in 16-byte units (a dense tile's extent)
+            const int row_in_tile = int(cta_rank) * BLOCK_M + quadrant * 32 + int(lane);
+            const bool shared_tile = STREAMK && item.split_tile >= 0;
+            uint4 *parts = shared_tile ? reinterpret_cast<uint4 *>(p.partials) + size_t(item.split_tile) * p.max_contributors * PART + row_in_tile : nullptr;
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; chunk++) {
                 uint32_t values[32];
                 ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values);
                 ptx::tmem_load_wait();
-                store_chunk<OUT>(p, values, row, tile_n * BN + chunk * 32);
+                if (shared_tile) {
+                    // this group's share of the tile's K-blocks: the 32-bit sums go to scratch as they are
+                    uint4 *mine = parts + size_t(item.contributor) * PART;
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        mine[size_t(chunk * 8 + i) * TILE_ROWS] = make_uint4(values[4 * i], values[4 * i + 1], values[4 * i + 2], values[4 * i + 3]);
+                } else {
+                    store_chunk<OUT>(p, values, row, tile_n * BN + chunk * 32);
+                }
+            }
+            if (shared_tile) {
+                // the accumulator goes back first; then whoever brings the last part of these 32 rows adds the parts up in the
+                // contributors' order and stores.  Nobody waits for anybody.
+                ptx::tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (CTA_GROUP == 1 || leader) ptx::mbarrier_arrive(acc_empty_bar(acc));
+                    else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(acc), 0));
+                }
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                unsigned int *counter = p.split_counters + item.split_tile * (4 * CTA_GROUP) + int(cta_rank) * 4 + quadrant;
+                __threadfence();
+                __syncwarp();
+                unsigned int earlier = 0;
+                if (lane == 0) earlier = atomicAdd(counter, 1u);
+                earlier = __shfl_sync(0xffffffffu, earlier, 0);
+                if (earlier == unsigned(item.contributors - 1)) {
+                    __threadfence();
+                    if (lane == 0) *counter = 0;       // ready for the next launch
+#pragma unroll 1
+                    for (int chunk = 0; chunk < BN / 32; chunk++) {
+                        uint32_t sum[32];
+#pragma unroll
+                        for (int i = 0; i < 32; i++) sum[i] = 0;    // +0.0f: the first part is added to it exactly
+                        for (int q = 0; q < item.contributors; q++) {
+                            uint4 loaded[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) loaded[i] = __ldcg(parts + size_t(q) * PART + size_t(chunk * 8 + i) * TILE_ROWS);
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const uint32_t w[4] = {loaded[i].x, loaded[i].y, loaded[i].z, loaded[i].w};
+#pragma unroll
+                                for (int j = 0; j < 4; j++) sum[4 * i + j] = __float_as_uint(__fadd_rn(__uint_as_float(sum[4 * i + j]), __uint_as_float(w[j])));
+                            }
+                        }
+                        store_chunk<OUT>(p, sum, row, tile_n * BN + chunk * 32);
+                    }
+                }
+                continue;
             }
             ptx::tcgen05_fence_before();
             __syncwarp();

@@ -68,6 +68,31 @@ def test_product_matches_the_dequantised_fp64_product(gpu, stream, m, n, k, out,
     assert gpu.status()[0] == 0
 
 
+@pytest.mark.parametrize("algorithm,max_ctas,m,n,k", [(G.ALGO_CTA_PAIR | G.ALGO_SPLIT_LAST_ROUND, 8, 512, 1120, 1024),
+                                                       (G.ALGO_SINGLE_CTA | G.ALGO_SPLIT_LAST_ROUND, 6, 640, 672, 512),
+                                                       (G.ALGO_CTA_PAIR, 0, 256, 448, 8192), (G.ALGO_SINGLE_CTA, 0, 200, 300, 6144)])
+def test_tiles_split_along_k(gpu, stream, algorithm, max_ctas, m, n, k):
+    """The stream-K schedule on the MX kernel: a last round split by force on a small grid, and few tiles with a deep K split
+    among idle groups by default; against the dequantised fp64 product, close to the whole-tile product, same bits on every run."""
+    a, sa, a_codes, a_exp = quantized(gpu, stream, m, k, False, seed=31)
+    b, sb, b_codes, b_exp = quantized(gpu, stream, n, k, True, seed=32)
+    expected = O.mx_dequantize(a_codes, a_exp, m, k) @ O.mx_dequantize(b_codes, b_exp, n, k).T
+
+    def product(flags):
+        c = gpu.allocate(G.F32, m * n)
+        gpu._lib.gpurs_fill_u8(stream._handle, c.pointer, 0x7F, c.nbytes)
+        G.matmul(stream, a, b, c, [m, n, k], G.MatmulOptions(algorithm=flags, max_ctas=max_ctas, scale_a=sa, scale_b=sb, scale_kind=G.SCALES_MX))
+        stream.synchronize()
+        return c.download().reshape(m, n)
+
+    got = product(algorithm)
+    assert (np.abs(got - expected) <= 1e-5 * np.abs(expected) + 1e-5 * np.abs(expected).max()).all()
+    whole = product((algorithm & ~G.ALGO_SPLIT_LAST_ROUND) | G.ALGO_WHOLE_TILES)
+    assert (np.abs(got - whole) <= 1e-5 * np.abs(expected).max()).all()
+    assert np.array_equal(got, product(algorithm))
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_doubling_a_scale_doubles_its_share_exactly(gpu, stream):
     """Raising every exponent of A by one doubles the fp32 result exactly; bias and a row scale ride on top."""
     m, n, k = 256, 448, 512
