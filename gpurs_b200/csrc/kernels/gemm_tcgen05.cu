@@ -83,5 +83,6 @@ GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_f16_f16, ptx::KIND_F16, 0, 1, gemm::OUT_F1
 GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_bf16_f32, ptx::KIND_F16, 1, 1, gemm::OUT_F32)
 GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_bf16_bf16, ptx::KIND_F16, 1, 1, gemm::OUT_BF16)
 GPURS_GEMM_STREAMK_PAIR(gpurs_gemm_i8_i32, ptx::KIND_I8, 1, 2, gemm::OUT_I32)
+GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_tf32_f32, ptx::KIND_TF32, 2, 1, gemm::OUT_F32)
 GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_e4m3_f32, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_F32)
 GPURS_GEMM_STREAMK_PAIR_EP(gpurs_gemm_e4m3_bf16, ptx::KIND_F8F6F4, 0, 1, gemm::OUT_BF16)

@@ -96,3 +96,37 @@ def test_kernel_sources_hold_no_multicast_loads():
         for line in path.read_text().splitlines():
             if "cp.async.bulk" in line:
                 assert "multicast" not in line, f"{path}: {line.strip()}"
+
+
+def test_every_kernel_the_launchers_can_name_is_in_the_image():
+    """The launchers build entry names from a stem and the chosen form; a name without an entry would only fail on a GPU, for
+    the shapes that choose it.  Every combination the host code can produce (csrc/host/matmul.cpp) is looked up here."""
+    image = (ROOT / "gpurs_b200" / "kernels.fatbin").read_bytes()
+    dense = ["f16_f32", "f16_f16", "bf16_f32", "bf16_bf16", "e4m3_f32", "e4m3_bf16", "tf32_f32", "i8_i32"]
+    names = []
+    for stem in dense:
+        algebra = stem != "i8_i32"                      # output algebra is for float outputs
+        for group in (1, 2):
+            names += [f"gpurs_gemm_{stem}_cg{group}", f"gpurs_gemm_{stem}_sk_cg{group}"]
+            if algebra:
+                names += [f"gpurs_gemm_{stem}_ep_cg{group}", f"gpurs_gemm_{stem}_sk_ep_cg{group}"]
+        if stem != "tf32_f32":                          # wide tiles: 16-bit and 8-bit operands
+            names.append(f"gpurs_gemm_{stem}_w512_cg2")
+            if algebra:
+                names.append(f"gpurs_gemm_{stem}_w512_ep_cg2")
+            if stem.endswith("32"):                     # 480-column tiles: 32-bit outputs
+                names.append(f"gpurs_gemm_{stem}_w480_cg2")
+    names += [f"gpurs_gemm_{stem}_push_cg2" for stem in ("bf16_bf16", "f16_f32", "i8_i32", "e4m3_bf16")]
+    names += [f"gpurs_gemm_{stem}_batched_cg{group}" for stem in ("bf16_bf16", "bf16_f32", "f16_f16", "f16_f32") for group in (1, 2)]
+    for stem in ("sparse_bf16_bf16", "sparse_bf16_f32", "sparse_f16_f32"):
+        names += [f"gpurs_gemm_{stem}_cg1", f"gpurs_gemm_{stem}_cg2", f"gpurs_gemm_{stem}_sk_cg1", f"gpurs_gemm_{stem}_sk_cg2", f"gpurs_gemm_{stem}_t512_cg2"]
+    names.append("gpurs_gemm_sparse_bf16_bf16_push_cg2")
+    for stem in ("e4m3_scaled_bf16", "e4m3_scaled_f32", "tf32_promoted_f32", "e4m3_mx_bf16", "e4m3_mx_f32"):
+        names += [f"gpurs_gemm_{stem}_cg{group}" for group in (1, 2)] + [f"gpurs_gemm_{stem}_sk_cg{group}" for group in (1, 2)]
+    names += ["gpurs_gemm_e4m3_blockscaled_bf16_cg2", "gpurs_gemm_e4m3_blockscaled_f32_cg2"]
+    names += [f"gpurs_gemm_skinny_{kind}_f32_t{tokens}" for kind in ("f16", "bf16") for tokens in (16, 32, 64)]
+    names += [f"gpurs_gemm_grouped_{stem}" for stem in ("f16_f16", "f16_f32", "bf16_bf16", "bf16_f32")]
+    names += ["gpurs_split_tf32", "gpurs_split_tf32_pair", "gpurs_split_tf32_transposed", "gpurs_transpose_b8", "gpurs_transpose_b16", "gpurs_transpose_b32",
+              "gpurs_quantize_e4m3_rows", "gpurs_quantize_e4m3_tiles", "gpurs_quantize_mx_e4m3", "gpurs_compress_24", "gpurs_wait_probe"]
+    missing = [name for name in names if (name.encode() + b"\x00") not in image]
+    assert not missing, missing

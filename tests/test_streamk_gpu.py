@@ -123,6 +123,19 @@ def test_promoted_products_split_the_same_way(gpu, stream, algorithm, max_ctas, 
     assert gpu.status() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("m,n,k,flags,max_ctas", [(256, 512, 4096, 0, 0), (512, 1280, 512, G.ALGO_CTA_PAIR | G.ALGO_SPLIT_LAST_ROUND, 8)])
+def test_one_pass_tf32_splits_too(gpu, stream, m, n, k, flags, max_ctas):
+    """fp32 operands in one TF32 pass run the dense kernel: few tiles with a deep K, or a forced split of the last round."""
+    a_bits, b_bits = make_operands("f32", m, n, k)
+    got = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, algorithm=flags, max_ctas=max_ctas, precision=G.PRECISION_TF32)
+    whole = run_matmul(gpu, stream, "f32", "f32", a_bits, b_bits, m, n, k, algorithm=(flags & 0xff) | G.ALGO_WHOLE_TILES, max_ctas=max_ctas,
+                       precision=G.PRECISION_TF32)
+    rows = np.arange(0, m, 17)
+    assert relative_error(got.reshape(m, n)[rows].astype(np.float64), O.matmul_rows(O.FMT_F32, a_bits, b_bits, n, k, rows)) <= 5e-2      # one TF32 pass: the operands keep 10 mantissa bits
+    assert relative_error(got.astype(np.float64), whole.astype(np.float64)) <= 1e-3
+    assert gpu.status() == [0, 0, 0, 0]
+
+
 def test_fp32_split_depth(gpu, stream):
     """The fp32 configuration's shape class: few one-CTA tiles, 3k deep: split among idle CTAs by default."""
     m, n, k = 256, 512, 4096
