@@ -730,8 +730,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int) -> None:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=100)
-    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--steps", type=int, default=20, help="timed launches; 20 is a burst of about 15 ms, 100 or more settle at the power cap's clock")
+    parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--algorithm", type=int, default=0, help="0 auto, 1 single-CTA tiles, 2 CTA-pair tiles")
