@@ -694,8 +694,9 @@ namespace {
 
 // The checks and the dispatch shared by gpurs_matmul and gpurs_matmul_allgather (`gather` non-null: C is this call's
 // block of rows of a matrix that every GPU of the box keeps, and the kernel stores the block to all of them).
+// `checks_only`: return after the checks, before anything is enqueued.
 int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc *desc, gpurs_device_ptr a, gpurs_device_ptr b,
-                   gpurs_device_ptr c, const gpurs_gather_desc *gather) {
+                   gpurs_device_ptr c, const gpurs_gather_desc *gather, bool checks_only = false) {
     if (!stream || !desc) return fail(op, GPURS_E_INVALID_ARGUMENT, "null stream or descriptor");
     gpurs_gpu *gpu = stream->gpu;
     Choice choice;
@@ -776,9 +777,13 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         gpurs_matmul_desc local = *desc;
         local.b_row_major = 0, local.ldb = 0, local.b_len = 0;
         local.algorithm = (local.algorithm & ~GPURS_ALGO_SPLIT_LAST_ROUND) | GPURS_ALGO_WHOLE_TILES;
+        // a rejected call launches nothing: the n x k product is checked before B is copied (B's own address stands in for the
+        // copy's: n * k elements from there lie within B, which has been checked against C above)
+        int result = matmul_checked(op, stream, &local, a, b, c, nullptr, true);
+        if (result != GPURS_OK || checks_only) return result;
         runtime::Enter enter(gpu);
         CUdeviceptr copy = 0;
-        int result = runtime::workspace_acquire(stream, n * k * eb, &copy);
+        result = runtime::workspace_acquire(stream, n * k * eb, &copy);
         if (result != GPURS_OK) return result;
         result = transpose_copy(stream, b, ldb, copy, n, k, eb);
         if (result == GPURS_OK) result = matmul_checked(op, stream, &local, a, copy, c, nullptr);
@@ -796,6 +801,19 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         if (desc->scale_a % 16 || desc->scale_b % 16) return fail(op, GPURS_E_INVALID_VIEW, "MX scale arrays must be 16-byte aligned");
         if (desc->bias % 4 || desc->row_scale % 4 || desc->column_scale % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
         if (desc->alpha != desc->alpha) return fail(op, GPURS_E_INVALID_ARGUMENT, "alpha is not a number");
+        if (desc->row_sum) return fail(op, GPURS_E_INVALID_ARGUMENT, "the row reduction is for single dense products with float outputs on the tile kernels");
+        if (desc->accumulate != 0 && (desc->accumulate != 1 || desc->c_type != GPURS_F32)) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulating into the output needs an fp32 output");
+        if (desc->row_bias % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
+        const uint64_t mx_ldr = desc->ldr ? desc->ldr : n;
+        if (desc->residual) {
+            if (mx_ldr < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
+            if (desc->residual % ob) return fail(op, GPURS_E_INVALID_VIEW, "the residual is not aligned to its element size");
+            if (!(desc->residual == c && mx_ldr == ldc) && overlap(desc->residual, ((m - 1) * mx_ldr + n) * ob, c, c_extent * ob))
+                return fail(op, GPURS_E_ALIASING, "the residual overlaps the output without being the output");
+        }
+        if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
+            return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
+        if (checks_only) return GPURS_OK;
         Gemm mx;
         mx.stem = desc->c_type == GPURS_BF16 ? "gpurs_gemm_e4m3_mx_bf16" : "gpurs_gemm_e4m3_mx_f32";
         mx.element_type = desc->a_type, mx.element_bytes = 1, mx.output_bytes = choice.output_bytes, mx.output_type = desc->c_type;
@@ -807,20 +825,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         mx.raster_rows = desc->raster_rows, mx.max_ctas = desc->max_ctas;
         mx.scale_a = desc->scale_a, mx.scale_b = desc->scale_b;
         mx.bias = desc->bias, mx.row_scale = desc->row_scale, mx.column_scale = desc->column_scale, mx.alpha = desc->alpha;
-        if (desc->row_sum) return fail(op, GPURS_E_INVALID_ARGUMENT, "the row reduction is for single dense products with float outputs on the tile kernels");
-        if (desc->accumulate != 0 && (desc->accumulate != 1 || desc->c_type != GPURS_F32)) return fail(op, GPURS_E_INVALID_ARGUMENT, "accumulating into the output needs an fp32 output");
-        if (desc->row_bias % 4) return fail(op, GPURS_E_INVALID_VIEW, "epilogue vectors must be 4-byte aligned");
-        const uint64_t mx_ldr = desc->ldr ? desc->ldr : n;
-        if (desc->residual) {
-            if (mx_ldr < n) return fail(op, GPURS_E_INVALID_VIEW, "a row pitch is smaller than the row");
-            if (desc->residual % ob) return fail(op, GPURS_E_INVALID_VIEW, "the residual is not aligned to its element size");
-            if (!(desc->residual == c && mx_ldr == ldc) && overlap(desc->residual, ((m - 1) * mx_ldr + n) * ob, c, c_extent * ob))
-                return fail(op, GPURS_E_ALIASING, "the residual overlaps the output without being the output");
-        }
         mx.row_bias = desc->row_bias, mx.residual = desc->residual, mx.ldr = mx_ldr, mx.beta = desc->beta == 0.0f ? 1.0f : desc->beta;
         mx.accumulate = desc->accumulate == 1, mx.launch = desc->launch;
-        if ((desc->algorithm & GPURS_ALGO_WHOLE_TILES) && (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND))
-            return fail(op, GPURS_E_INVALID_ARGUMENT, "whole tiles and a split last round exclude each other");
         mx.whole_tiles = (desc->algorithm & GPURS_ALGO_WHOLE_TILES) != 0, mx.force_split = (desc->algorithm & GPURS_ALGO_SPLIT_LAST_ROUND) != 0;
         return launch_mx(stream, mx);
     }
@@ -922,6 +928,9 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
         if (group == GPURS_ALGO_SKINNY) return fail(op, GPURS_E_INVALID_ARGUMENT, "the skinny algorithm sizes its own grid");
         if (gather) return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product sizes its own grid");
     }
+    if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
+    if (sparse && desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "a sparse product takes no scales");
+    if (checks_only) return GPURS_OK;
     Gemm gemm;
     gemm.stem = choice.stem;
     gemm.element_type = desc->a_type;
@@ -946,10 +955,8 @@ int matmul_checked(const char *op, gpurs_stream *stream, const gpurs_matmul_desc
     gemm.gather = gather;
     gemm.batches = batches, gemm.stride_a = stride_a, gemm.stride_b = stride_b, gemm.stride_c = stride_c;
     if (group == GPURS_ALGO_SKINNY) return launch_skinny(stream, gemm);
-    if (desc->l2_policy < 0 || desc->l2_policy > 4) return fail(op, GPURS_E_INVALID_ARGUMENT, "unknown L2 policy");
     gemm.l2_policy = desc->l2_policy == 4 ? 0 : desc->l2_policy;   // library default: no hints
     if (sparse) {
-        if (desc->scale_a) return fail(op, GPURS_E_INVALID_ARGUMENT, "a sparse product takes no scales");
         gemm.stem = desc->a_type == GPURS_F16 ? "gpurs_gemm_sparse_f16_f32"
                     : desc->c_type == GPURS_BF16 ? "gpurs_gemm_sparse_bf16_bf16" : "gpurs_gemm_sparse_bf16_f32";
         gemm.metadata = desc->metadata;

@@ -39,6 +39,14 @@ def test_rejections_happen_before_any_launch(gpu, stream):
     deep = _ffi.MatmulDesc()
     deep.a_type, deep.c_type, deep.m, deep.n, deep.k = G.F32, G.F32, 1, 1, (0x7FFFFFFF // 3 // 4 + 1) * 4
     assert gpu._lib.gpurs_matmul(stream._handle, C.byref(deep), 1 << 40, 2 << 40, 3 << 40) == _ffi.E_SIZE_OVERFLOW
+    # a k x n right operand of a kernel that reads B K-major is copied transposed first: not before the product has been checked
+    scales = gpu.zeros(G.F32, 256)
+    codes_a, codes_b, out = gpu.zeros(G.E4M3, 128 * 128), gpu.zeros(G.E4M3, 128 * 256), gpu.zeros(G.BF16, 128 * 256)
+    refused = G.MatmulOptions(b_row_major=True, scale_a=scales, scale_b=scales, l2_policy=7)
+    assert code_of(lambda: G.matmul(stream, codes_a, codes_b, out, [128, 256, 128], refused)) == _ffi.E_INVALID_ARGUMENT
+    refused = G.MatmulOptions(b_row_major=True, precision=G.PRECISION_TF32, algorithm=G.ALGO_WHOLE_TILES | G.ALGO_WIDE_TILES | G.ALGO_SQUARE_TILES)
+    single = gpu.zeros(G.F32, 128 * 256)
+    assert code_of(lambda: G.matmul(stream, single, single, c, [128, 256, 128], refused)) == _ffi.E_INVALID_ARGUMENT
     assert gpu.launches == before
     error = pytest.raises(G.GpursError, lambda: G.matmul(stream, a, b, alias, [16, 128, 64])).value
     assert error.operation == "gpurs_matmul" and "overlaps" in error.description
