@@ -1064,8 +1064,6 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
     // this GPU's copy; when a band is complete, one helper stream per peer copies it to that peer over NVLink while the next
     // band is multiplied.  The caller's stream continues after all copies (they are its work).
     local.algorithm &= ~GPURS_ALGO_GATHER_BY_COPIES;
-    if (desc->scale_a && desc->scale_kind != GPURS_SCALES_FP32_BLOCKS)
-        return fail(op, GPURS_E_INVALID_ARGUMENT, "the gather by copies takes fp32 block scales only (tiled MX scales do not split into bands of rows)");
     if (desc->batches > 1) return fail(op, GPURS_E_INVALID_ARGUMENT, "the gathering product takes a single product");
     gpurs_gpu *gpu = stream->gpu;
     runtime::Enter enter(gpu);
@@ -1085,7 +1083,10 @@ extern "C" int gpurs_matmul_allgather(gpurs_stream *stream, const gpurs_matmul_d
         gpurs_matmul_desc part = local;
         part.m = rows;
         if (desc->metadata) part.metadata = desc->metadata + (first / 128) * metadata_per_row_block;
-        if (desc->scale_a) part.scale_a = desc->scale_a + first * ((desc->k + 127) / 128) * sizeof(float);     // one scale per row and 128 of K
+        // fp32 block scales: one per row and 128 of K; MX scales: tiles of 512 bytes per 128 rows and 128 of K (bands are whole tiles)
+        if (desc->scale_a)
+            part.scale_a = desc->scale_a + (desc->scale_kind == GPURS_SCALES_MX ? (first / 128) * ((desc->k + 127) / 128) * 512
+                                                                                 : first * ((desc->k + 127) / 128) * sizeof(float));
         if (desc->row_scale) part.row_scale = desc->row_scale + first * sizeof(float);
         if (desc->row_bias) part.row_bias = desc->row_bias + first * sizeof(float);
         if (desc->row_absmax) part.row_absmax = desc->row_absmax + first * sizeof(float);

@@ -205,7 +205,7 @@ enum {
      * the other GPUs with the copy engines (one helper stream per peer) while the next band is multiplied, instead of storing
      * to all GPUs from the product's epilogue.  The call is stream-ordered as always: work enqueued on `stream` after it sees
      * this GPU's copies sent.  This form takes every single product gpurs_matmul takes (the epilogue form has kernels for four
-     * type pairs), except MX-scaled ones, whose tiled scales do not split into bands of rows. */
+     * type pairs). */
     GPURS_ALGO_GATHER_BY_COPIES = 0x1000
 };
 

@@ -33,8 +33,11 @@ def gather_in_one_process(gpu, stream, kind, out, a_bits, b_bits, m, n, k, world
         desc.algorithm = options.get("algorithm", 0)
         if "row_bias" in options:
             desc.row_bias = options["row_bias"].pointer + 4 * first      # the local product's rows start at the block's first row
-        if "scale_a" in options:                                        # block-scaled E4M3: one scale per row of A and 128 of K
-            desc.scale_a = options["scale_a"].pointer + 4 * first * ((k + 127) // 128)
+        if "scale_a" in options:
+            # block-scaled E4M3: one fp32 scale per row of A and 128 of K, or (MX) a tile of 512 bytes per 128 rows and 128 of K
+            desc.scale_kind = options.get("scale_kind", _ffi.SCALES_FP32_BLOCKS)
+            per_row_block = 512 * ((k + 127) // 128)
+            desc.scale_a = options["scale_a"].pointer + (first // 128 * per_row_block if desc.scale_kind == _ffi.SCALES_MX else 4 * first * ((k + 127) // 128))
             desc.scale_b = options["scale_b"].pointer
         gather = _ffi.GatherDesc()
         gather.world, gather.rank, gather.row_offset, gather.total_rows = world, rank, first, m
@@ -111,6 +114,18 @@ def test_copy_engine_form_offsets_the_scales_of_a_block_scaled_product(gpu, stre
         assert np.array_equal(copy, whole)
 
 
+def test_copy_engine_form_offsets_the_tiled_scales_of_an_mx_product(gpu, stream):
+    m, n, k, world = 2048, 448, 256, 2
+    a_codes, scale_a = G.quantize_mx_e4m3(stream, gpu.upload(O.fill_normal_f32(m * k, 7)), m, k, False)
+    b_codes, scale_b = G.quantize_mx_e4m3(stream, gpu.upload(O.fill_normal_f32(n * k, 8)), n, k, True)
+    stream.synchronize()
+    a_bits, b_bits = a_codes.download(), b_codes.download()
+    scales = dict(scale_a=scale_a, scale_b=scale_b, scale_kind=_ffi.SCALES_MX)
+    whole = run_matmul(gpu, stream, "e4m3", "bf16", a_bits, b_bits, m, n, k, **scales)
+    for copy in gather_in_one_process(gpu, stream, "e4m3", "bf16", a_bits, b_bits, m, n, k, world, algorithm=G.ALGO_GATHER_BY_COPIES, **scales):
+        assert np.array_equal(copy, whole)
+
+
 def test_arguments_the_gathering_product_rejects(gpu, stream):
     lib = gpu._lib
     a, b, full = gpu.zeros(G.BF16, 256 * 64), gpu.zeros(G.BF16, 256 * 64), gpu.zeros(G.BF16, 512 * 256)
@@ -138,15 +153,6 @@ def test_arguments_the_gathering_product_rejects(gpu, stream):
     assert call(n=250) == _ffi.E_INVALID_VIEW                         # pitch of 500 bytes
     assert call(algorithm=G.ALGO_SINGLE_CTA) == _ffi.E_INVALID_ARGUMENT
     assert call(pointer=0) == _ffi.E_INVALID_ARGUMENT
-    # tiled MX scales do not split into bands of rows
-    desc = _ffi.MatmulDesc()
-    desc.a_type, desc.c_type, desc.m, desc.n, desc.k, desc.algorithm = G.E4M3, G.BF16, 256, 256, 64, G.ALGO_GATHER_BY_COPIES
-    desc.scale_a = desc.scale_b = a.pointer
-    desc.scale_kind = _ffi.SCALES_MX
-    gather = _ffi.GatherDesc()
-    gather.world, gather.rank, gather.row_offset, gather.total_rows = 2, 0, 0, 512
-    gather.full[0] = gather.full[1] = full.pointer
-    assert lib.gpurs_matmul_allgather(stream._handle, C.byref(desc), C.byref(gather), a.pointer, b.pointer) == _ffi.E_INVALID_ARGUMENT
     stream.synchronize()
     assert gpu.status()[0] == 0
 
