@@ -20,6 +20,11 @@
 // with four epilogue warps that tail was measured at 6.6 us for 32-bit outputs, which a 1024-row shard of an 8192^3 product
 // cannot afford.)  Epilogue: round, stage, TMA store, with the element-wise output algebra in the `_ep` entries; C with 16-byte aligned
 // rows; row reductions, accumulation into C and everything else take the 256-column kernels.
+//
+// What paces the read-out is the SM's path to L2 for stores, 32 bytes per clock (a tile's 256 KiB of 32-bit outputs: 4.5 us,
+// measured the same with one CTA pair running and with 72).  Between tiles the epilogue therefore empties tensor memory into
+// registers first and stores afterwards, so that the next tile's products do not wait for stores; the last tile of a CTA pair
+// is read out box by box, so that its stores never pause.
 #pragma once
 #include "gemm_tcgen05.cuh"
 
@@ -195,80 +200,145 @@ __device__ __forceinline__ void gemm_wide_body(const CUtensorMap *map_a, const C
         const int side = (warp - 2) / 4;               // 0: the first 128 columns of either half, 1: the last 128
         const uint32_t buffer = staging + uint32_t(warp - 2) * 32 * ROW_BYTES;
         constexpr int COLUMNS_PER_BOX = (OUT == OUT_F32 || OUT == OUT_I32) ? 32 : 64;
-        constexpr int BOXES = 128 / COLUMNS_PER_BOX;   // per warp and half
+        constexpr int BOXES = 128 / COLUMNS_PER_BOX;   // per warp and half: 32 registers each once rounded
         uint32_t tile_phase = 0;
         bool ok = true;
+        // A warp's 128 columns of a half are read from tensor memory in one go and the half is handed back before anything of it
+        // is stored: stores leave an SM at 32 bytes per clock (a 4 KiB box of each of the eight warps: 1024 clocks), and a half
+        // that waited for its staging buffer kept the next tile's products waiting with it (measured on bf16 8192^3: +1.3 %).
+        // With 16-bit outputs the last box of half 0 stays in registers while half 1 is read, so that half 1 waits for one box of
+        // half 0 only; 32-bit outputs fill the registers with one half (128 per lane of the 168 a CTA of ten warps gets).
         for (int tile = cluster_id; tile < tile_count && ok; tile += cluster_count) {
             int tile_m, tile_n;
             tile_position(tile, p, tile_m, tile_n);
             const int warp_row = (tile_m * 2 + int(cta_rank)) * BLOCK_M + quadrant * 32;
-            for (int half = 0; half < 2 && ok; half++) {
+            const int column0 = tile_n * TILE_N + side * 128;
+            // one box: 32 rows x 128 bytes from registers to the warp's staging buffer, then to C
+            auto store_box = [&](const uint32_t (&box)[32], int column) {
+                if (warp_row < p.m && column < p.n) {    // warp-uniform: boxes wholly outside C are skipped
+                    if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous store has read the buffer
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
+                        ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), box[4 * j], box[4 * j + 1],
+                                             box[4 * j + 2], box[4 * j + 3]);
+                    ptx::fence_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(map_c, column, warp_row, buffer);
+                        ptx::tma_store_commit();
+                    }
+                }
+            };
+            // reads the warp's 128 columns of a half (of a 224-column half: the last 32 are columns no product writes and no
+            // box stores), hands the half back and rounds (plain products only: see below)
+            auto read_half = [&](int half, uint32_t (&boxes)[BOXES][32]) -> bool {
                 const bool ready = ptx::mbarrier_wait(acc_full_bar(half), tile_phase, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) {
                     if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, -1 - half);
-                    ok = false;
-                    break;
+                    return false;
                 }
                 ptx::tcgen05_fence_after();
                 const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(half * HALF + side * 128);
-                // boxes this warp reads of this half: 128 columns' worth, or what is left of a 224-column second half
-                const int boxes = (half == 1 && side == 1) ? (SECOND - 128) / COLUMNS_PER_BOX : BOXES;
-                // the read of box b + 1 is in flight while box b is staged and stored
-                uint32_t low[32], high[32];
-                ptx::tmem_load_32x32(lane_base, low);
-                if constexpr (COLUMNS_PER_BOX == 64) ptx::tmem_load_32x32(lane_base + 32, high);
+                if constexpr (COLUMNS_PER_BOX == 32) {
 #pragma unroll
-                for (int box = 0; box < BOXES; box++) {
-                    if (box >= boxes) break;
-                    const int column = tile_n * TILE_N + half * HALF + side * 128 + box * COLUMNS_PER_BOX;
-                    uint32_t packed[32];
+                    for (int chunk = 0; chunk < 4; chunk++) ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), boxes[chunk]);
                     ptx::tmem_load_wait();
-                    if constexpr (COLUMNS_PER_BOX == 32) {
-                        if constexpr (ALGEBRA) apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
+                } else {
+                    uint32_t values[4][32];
 #pragma unroll
-                        for (int i = 0; i < 32; i++) packed[i] = low[i];
-                        if (box + 1 < boxes) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
-                    } else {
-                        if constexpr (ALGEBRA) {
-                            apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
-                            apply_epilogue<OUT>(p, high, warp_row + int(lane), column + 32);
-                        }
+                    for (int chunk = 0; chunk < 4; chunk++) ptx::tmem_load_32x32(lane_base + uint32_t(chunk * 32), values[chunk]);
+                    ptx::tmem_load_wait();
 #pragma unroll
-                        for (int i = 0; i < 16; i++) {
-                            packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
-                            packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
-                        }
-                        if (box + 1 < boxes) {
-                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64), low);
-                            ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64 + 32), high);
-                        }
-                    }
-                    if (box == boxes - 1) {
-                        // this warp's part of the half has left tensor memory: once all sixteen warps of the pair have said so,
-                        // the next tile's products may overwrite it while these boxes are stored
-                        ptx::tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (leader) ptx::mbarrier_arrive(acc_empty_bar(half));
-                            else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(half), 0));
-                        }
-                    }
-                    if (warp_row < p.m && column < p.n) {    // warp-uniform: boxes wholly outside C are skipped
-                        if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous store has read the buffer
-                        __syncwarp();
+                    for (int chunk = 0; chunk < 4; chunk++) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++)                          // lane = row; 16-byte piece j goes to slot j ^ (row % 8)
-                            ptx::store_shared_v4(buffer + lane * ROW_BYTES + uint32_t((j ^ int(lane & 7)) * 16), packed[4 * j], packed[4 * j + 1],
-                                                 packed[4 * j + 2], packed[4 * j + 3]);
-                        ptx::fence_async_shared();
-                        __syncwarp();
-                        if (lane == 0) {
-                            ptx::tma_store_2d(map_c, column, warp_row, buffer);
-                            ptx::tma_store_commit();
-                        }
+                        for (int i = 0; i < 16; i++) boxes[chunk / 2][(chunk % 2) * 16 + i] = pack_pair<OUT>(values[chunk][2 * i], values[chunk][2 * i + 1]);
                     }
                 }
+                // this warp's part of the half has left tensor memory: once all sixteen warps of the pair have said so, the next
+                // tile's products may overwrite it
+                ptx::tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) ptx::mbarrier_arrive(acc_empty_bar(half));
+                    else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(half), 0));
+                }
+                return true;
+            };
+            // boxes of the second half: 128 columns' worth, or what is left of a 224-column second half
+            const int second_boxes = side == 1 ? (SECOND - 128) / COLUMNS_PER_BOX : BOXES;
+            const bool last_tile = tile + cluster_count >= tile_count;
+            if (ALGEBRA || last_tile) {
+                // The pair's last tile: no product waits for tensor memory any more, and what counts is that the stores never
+                // pause (in a launch of one round this read-out is all exposed: 256 KiB at 32 bytes per clock).  Box by box, the
+                // read of the next box in flight while one is staged and stored.  The entries with the output algebra read every
+                // tile this way: the algebra's registers on top of a whole half's spilled (bf16 8192^3 with a bias: -1.2 %).
+                for (int half = 0; half < 2 && ok; half++) {
+                    const bool ready = ptx::mbarrier_wait(acc_full_bar(half), tile_phase, abort_flag);
+                    if (!__all_sync(0xffffffffu, ready)) {
+                        if (lane == 0) report(p, abort_flag, STATUS_EPILOGUE_TIMEOUT, tile, -1 - half);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tcgen05_fence_after();
+                    const uint32_t lane_base = tmem_base + (uint32_t(quadrant * 32) << 16) + uint32_t(half * HALF + side * 128);
+                    const int boxes = half == 1 ? second_boxes : BOXES;
+                    uint32_t low[32], high[32];
+                    ptx::tmem_load_32x32(lane_base, low);
+                    if constexpr (COLUMNS_PER_BOX == 64) ptx::tmem_load_32x32(lane_base + 32, high);
+#pragma unroll
+                    for (int box = 0; box < BOXES; box++) {
+                        if (box >= boxes) break;
+                        const int column = column0 + half * HALF + box * COLUMNS_PER_BOX;
+                        uint32_t packed[32];
+                        ptx::tmem_load_wait();
+                        if constexpr (COLUMNS_PER_BOX == 32) {
+                            if constexpr (ALGEBRA) apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
+#pragma unroll
+                            for (int i = 0; i < 32; i++) packed[i] = low[i];
+                            if (box + 1 < boxes) ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 32), low);
+                        } else {
+                            if constexpr (ALGEBRA) {
+                                apply_epilogue<OUT>(p, low, warp_row + int(lane), column);
+                                apply_epilogue<OUT>(p, high, warp_row + int(lane), column + 32);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; i++) {
+                                packed[i] = pack_pair<OUT>(low[2 * i], low[2 * i + 1]);
+                                packed[16 + i] = pack_pair<OUT>(high[2 * i], high[2 * i + 1]);
+                            }
+                            if (box + 1 < boxes) {
+                                ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64), low);
+                                ptx::tmem_load_32x32(lane_base + uint32_t((box + 1) * 64 + 32), high);
+                            }
+                        }
+                        if (box == boxes - 1) {
+                            ptx::tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) {
+                                if (leader) ptx::mbarrier_arrive(acc_empty_bar(half));
+                                else ptx::mbarrier_arrive_cluster_relaxed(ptx::map_to_cta(acc_empty_bar(half), 0));
+                            }
+                        }
+                        store_box(packed, column);
+                    }
+                }
+                if (last_tile) break;
+                tile_phase ^= 1;
+                continue;
             }
+            uint32_t first[BOXES][32], second[BOXES][32];
+            ok = read_half(0, first);
+            if (!ok) break;
+            constexpr int CARRIED = COLUMNS_PER_BOX == 64 ? 1 : 0;
+#pragma unroll
+            for (int box = 0; box < BOXES - CARRIED; box++) store_box(first[box], column0 + box * COLUMNS_PER_BOX);
+            ok = read_half(1, second);
+            if (!ok) break;
+            if constexpr (CARRIED == 1) store_box(first[BOXES - 1], column0 + (BOXES - 1) * COLUMNS_PER_BOX);
+#pragma unroll
+            for (int box = 0; box < BOXES; box++)
+                if (box < second_boxes) store_box(second[box], column0 + HALF + box * COLUMNS_PER_BOX);
             tile_phase ^= 1;
         }
         // the stores have read their shared-memory source; the grid's completion orders their writes before whatever follows
